@@ -1,0 +1,126 @@
+// Shared host/device helpers of libesmm_b200 (sm_100a only).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/esmm.h"
+
+namespace esmm {
+
+constexpr int BK = 8;    // K offsets per pattern byte (the reference's BK)
+constexpr int PAT_N = 32;  // columns of B per pattern byte (the reference's WN)
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Records a CUDA error for esmm_last_cuda_error() and maps it to ESMM_ERR_CUDA.
+int record_cuda_error(cudaError_t e, const char *what);
+int record_cuda_error_text(const char *text);
+
+#define ESMM_CUDA_TRY(expr)                                              \
+    do {                                                                 \
+        cudaError_t _e = (expr);                                         \
+        if (_e != cudaSuccess) return esmm::record_cuda_error(_e, #expr); \
+    } while (0)
+
+// Device status word shared by all kernels of the library (0 = ok).
+int *device_status_ptr();  // device address, valid after the first call on the current device
+
+#ifdef __CUDACC__
+// ---------------------------------------------------------------------------
+// PTX wrappers: mbarrier, TMA (cp.async.bulk.tensor), timers.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p)
+{
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+
+__device__ __forceinline__ void fence_barrier_init()
+{
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_proxy_async()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar)
+{
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+                 : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+__device__ __forceinline__ uint64_t global_timer_ns()
+{
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+// Every wait in the library is bounded.  The first tries are a plain spin; after that
+// the loop watches a CTA-wide abort flag and a wall-clock budget.  On expiry the flag
+// is raised (so that the CTA's other waiters leave too) and false is returned.
+constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate wait
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+{
+#pragma unroll 1
+    for (int i = 0; i < 128; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > WAIT_BUDGET_NS) {
+            *abort_flag = 1;
+            return false;
+        }
+    }
+}
+
+// 2-D tiled TMA load, completion counted in bytes on an mbarrier of this CTA.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y,
+                                            uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_descriptor(const CUtensorMap *map)
+{
+    asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+#endif  // __CUDACC__
+
+}  // namespace esmm

@@ -1,0 +1,224 @@
+/*
+ * esmm.h - C ABI of libesmm_b200: joint-sparse FP32 SGEMM ("ESMM") for NVIDIA B200 (sm_100a).
+ *
+ * The library replaces one path of the ESMM research harness: the A/B pattern
+ * preprocessor, the joint-sparse SGEMM kernel (kernel id 29) and the runner /
+ * kernel-id dispatch around them.  Every entry point names the reference
+ * interface it stands in for (paths relative to the reference project root).
+ *
+ * Conventions
+ *   - Matrices are dense row-major FP32: A is M x K (ld = K), B is K x N
+ *     (ld = N), C is M x N (ld = N).  The reference names them rows = M,
+ *     cols = N, inners = K.
+ *   - Pointers are DEVICE pointers unless the name starts with h_.
+ *   - Pattern arrays: one byte per (row block x 8-wide K block) of A and per
+ *     (32-column block x 8-deep K block) of B, K-block index fastest; bit k
+ *     (LSB = k 0) is set iff the tile holds a nonzero at K offset k.
+ *   - Every function returns an esmm_status (0 = ESMM_OK) and never exits the
+ *     process.  `stream` is a cudaStream_t passed as void* (NULL = default
+ *     stream).  Launches are asynchronous unless stated otherwise.
+ *   - There is no CPU fallback: without a usable CUDA device every compute
+ *     entry point returns ESMM_ERR_CUDA.
+ */
+#ifndef ESMM_H_
+#define ESMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum esmm_status {
+    ESMM_OK = 0,
+    ESMM_ERR_NULL = 1,        /* a required pointer is NULL */
+    ESMM_ERR_SHAPE = 2,       /* non-positive dimension, or K / N not a multiple of 4 */
+    ESMM_ERR_ALIGN = 3,       /* a matrix pointer is not 16-byte aligned */
+    ESMM_ERR_CUDA = 4,        /* a CUDA runtime / driver call failed (see esmm_last_cuda_error) */
+    ESMM_ERR_TIMEOUT = 5,     /* a bounded device-side wait gave up; results are invalid */
+    ESMM_ERR_IO = 6,          /* file could not be read / written, or has the wrong size */
+    ESMM_ERR_UNSUPPORTED = 7, /* kernel id or granularity this library does not provide */
+    ESMM_ERR_VERIFY = 8,      /* verification against the reference result failed */
+    ESMM_ERR_TOO_LARGE = 9,   /* K exceeds what the kernel's shared-memory masks can hold */
+    ESMM_ERR_MISMATCH = 10    /* cached pattern file does not match the requested shape */
+} esmm_status;
+
+const char *esmm_strerror(int status);
+/* Text of the last CUDA error this library saw on the calling thread ("" if none). */
+const char *esmm_last_cuda_error(void);
+int esmm_version(void);
+
+/* ---- pattern geometry -------------------------------------------------- */
+
+/* ceil(K / 8).  The reference computes K / BK (src/preprocessors/ab_preprocessor.cu:305). */
+int esmm_num_k_blocks(int K);
+/* Bytes of an A pattern array: ceil(M / tile_m) * ceil(K / 8)   (ab_preprocessor.cu:309). */
+size_t esmm_a_pattern_bytes(int M, int K, int tile_m);
+/* Bytes of a B pattern array: ceil(N / 32) * ceil(K / 8)        (ab_preprocessor.cu:310). */
+size_t esmm_b_pattern_bytes(int K, int N);
+/* "11110000" -> 0x0F: string position i is K offset i is bit i (include/utils.cuh:146-147,
+ * ab_preprocessor.cu:70).  Returns -1 unless the string is eight '0'/'1' characters. */
+int esmm_pattern_from_string(const char *pattern);
+/* PatternLUT semantics (include/pattern_lut.cuh:13-19): *count = popcount(pattern),
+ * offsets[0..count) = set bit indices ascending, remaining entries 0. */
+void esmm_pattern_lut(uint8_t pattern, uint8_t *count, uint8_t offsets[8]);
+
+/* ---- pattern preprocessor ---------------------------------------------- */
+
+/*
+ * A patterns: replaces preprocess_a_patterns_kernel<8, TILE_M, 256>
+ * (src/preprocessors/ab_preprocessor.cu:31-84).  d_out[mb * nKB + kb], bit k set
+ * iff any row of row block mb has a nonzero at column kb*8+k.  tile_m is the
+ * rows per block (32 for kernel id 29; any positive value is accepted).
+ * Ragged M or K are covered by a final partial block.  -0.0f is zero, NaN and
+ * denormals are nonzero.
+ */
+int esmm_preprocess_a(const float *d_A, int M, int K, int tile_m, uint8_t *d_out, void *stream);
+
+/*
+ * B patterns: replaces preprocess_b_patterns_kernel<8, 32, 256>
+ * (src/preprocessors/ab_preprocessor.cu:91-144).  d_out[nb * nKB + kb] (N-block
+ * major, :141), bit k set iff any of columns nb*32..nb*32+31 has a nonzero in
+ * row kb*8+k.  B is static in the intended use: compute once, keep or save.
+ */
+int esmm_preprocess_b(const float *d_B, int K, int N, uint8_t *d_out, void *stream);
+
+/*
+ * The reference's ABPatternMetadata (ab_preprocessor.cu:7-17), same fields.
+ * owns_b_patterns is 0 when d_b_patterns was supplied by the caller (cached).
+ */
+typedef struct esmm_ab_pattern_metadata {
+    uint8_t *d_a_patterns;
+    uint8_t *d_b_patterns;
+    int owns_b_patterns;
+    int numMBlocks;
+    int numNBlocks;
+    int numKBlocks;
+    float a_sparsity;
+    float b_sparsity;
+    float joint_sparsity;
+} esmm_ab_pattern_metadata;
+
+/*
+ * Replaces preprocess_ab<8, TILE_M_A, 32> (ab_preprocessor.cu:297-326): allocates
+ * the pattern arrays and launches the pattern kernels on the default stream
+ * without synchronising.  If d_b_cached is not NULL it is used as the B pattern
+ * array (not recomputed, not owned); the reference always recomputes B.
+ */
+int esmm_preprocess_ab(const float *d_A, const float *d_B, int M, int N, int K, int tile_m,
+                       const uint8_t *d_b_cached, esmm_ab_pattern_metadata *meta);
+/* Replaces free_ab_pattern_metadata (ab_preprocessor.cu:19-24). */
+int esmm_free_ab_pattern_metadata(esmm_ab_pattern_metadata *meta);
+
+/* B pattern cache file: 32-byte header (magic, K, N, nNB, nKB) + raw bytes.
+ * Load fails with ESMM_ERR_MISMATCH if the file was written for another K x N.
+ * The reference only reserves the hook for this (owns_b_patterns, ab_preprocessor.cu:10,21). */
+int esmm_bpat_save(const char *path, const uint8_t *h_b_patterns, int K, int N);
+int esmm_bpat_load(const char *path, uint8_t *h_b_patterns, int K, int N);
+
+/* ---- joint-sparse SGEMM ------------------------------------------------- */
+
+/*
+ * C = A * B over the k whose joint bit (a_pat[i/32][k/8] & b_pat[j/32][k/8]) >> (k%8) & 1
+ * is set; one FFMA chain per output in ascending k; C is overwritten.  Replaces
+ * esmm_ab_optimized_v3 + dispatch_v3 (src/kernels/esmm_ab_optimized_v3.cu:18-235,
+ * include/runners.cuh:801-825).  a_tile_m is the row granularity of d_a_pat
+ * (32 for id 29; 8, 16, 64, 128 are accepted and folded to 32-row warp tiles).
+ * Needs K % 4 == 0, N % 4 == 0, 16-byte aligned A, B, C; M is arbitrary.
+ * No hidden allocation; a device-side wait that gives up is reported by
+ * esmm_device_status.
+ */
+int esmm_gemm_ab(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
+                 const uint8_t *d_a_pat, const uint8_t *d_b_pat, int a_tile_m, void *stream);
+
+/*
+ * The per-call path with B patterns cached: A patterns (32-row blocks) are
+ * computed into d_a_pat_scratch (esmm_a_pattern_bytes(M, K, 32) bytes, caller
+ * owned), then the GEMM runs, both on `stream`.
+ */
+int esmm_sgemm_joint(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
+                     const uint8_t *d_b_pat, uint8_t *d_a_pat_scratch, void *stream);
+
+/* Synchronises `stream`, returns and clears the device status word:
+ * ESMM_OK, ESMM_ERR_TIMEOUT (a bounded wait expired) or ESMM_ERR_CUDA. */
+int esmm_device_status(void *stream);
+
+/* ---- host-buffer (end-to-end) path -------------------------------------- */
+
+/*
+ * A plan keeps B and its patterns resident on the device ("B offline") and owns
+ * device buffers for A, C and the A patterns.  esmm_plan_run takes HOST A and C
+ * (pinned memory gives the best copy rate), copies A in row chunks, computes and
+ * copies C back, overlapping the three, and returns when h_C is complete.
+ */
+typedef struct esmm_plan esmm_plan;
+int esmm_plan_create(int M, int N, int K, const float *h_B, int chunks, esmm_plan **plan);
+int esmm_plan_run(esmm_plan *plan, const float *h_A, float *h_C);
+int esmm_plan_destroy(esmm_plan *plan);
+
+/* ---- comparison baselines, measurement helpers ---------------------------- */
+
+/* cuBLAS SGEMM exactly as run_cuBlas calls it (include/runners.cuh:122-123): row-major
+ * trick, alpha 1, beta 0, default math mode.  The handle is created once per device. */
+int esmm_cublas_sgemm(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
+                      void *stream);
+/* Measured FP32 FFMA throughput of the current device in TFLOP/s (dependent-free FFMA
+ * chains on every SM, timed with CUDA events); *sm_count gets the SM count. */
+int esmm_ffma_peak_tflops(double *tflops, int *sm_count);
+
+/* Counter-based N(mean, std) generator with block-structured zeros, on the device.
+ * Element (r, c) of a rows x cols row-major matrix; k = c when k_axis == 0 (matrix A),
+ * k = r when k_axis == 1 (matrix B); the other index is the "outer" index.
+ *   mode 0: dense.
+ *   mode 1: uniform pattern - element is zero unless bit (k % 8) of `pattern` is set.
+ *   mode 2: independent tile patterns - for each (outer / gran, k / 8) tile each of the 8
+ *           k offsets is live with probability p_live (decided by hash(seed2, tile, bit)).
+ * relu != 0 applies max(x, 0) before the zero pattern.  Not part of the reference, whose
+ * generators use rand(); here so that 16384^2 inputs need no host copy. */
+int esmm_fill_normal(float *d_out, long rows, long cols, int k_axis, uint64_t seed, float mean,
+                     float std, int relu, int mode, uint8_t pattern, float p_live, int gran,
+                     uint64_t seed2, void *stream);
+
+/* Interleaves G column shards [g][M][N/G] into row-major M x N (used after an all-gather). */
+int esmm_interleave_shards(const float *d_shards, float *d_C, int M, int N, int G, void *stream);
+
+/* ---- skip statistics ------------------------------------------------------ */
+
+/* compute_and_print_skip_stats arithmetic (include/runners.cuh:636-706) on HOST pattern
+ * arrays for CTA tiles of warps_m x warps_n pattern blocks.
+ * out[6] = block_skips, total_k, warp_skips, total_warp_k, dot_skips, total_dot. */
+int esmm_skip_stats(const uint8_t *h_a_pat, const uint8_t *h_b_pat, int num_cblocks_m,
+                    int num_cblocks_n, int numKBlocks, int warps_m, int warps_n, int bk,
+                    long long out[6]);
+
+/* ---- runners: the kernel-id dispatch -------------------------------------- */
+
+/* Valid ids of the reference driver (driver.cu:20): 14-17, 20, 21, 25-30. */
+int esmm_kernel_id_valid(int kernel_id);
+/* get_kernel_name (include/utils.cuh:48-64). */
+const char *esmm_kernel_name(int kernel_id);
+/* parse_kernel_selection (include/utils.cuh:18-46): "29", "29,15", "14-17", "all".
+ * Writes at most cap ids, returns how many the selection holds (0 = invalid). */
+int esmm_parse_kernel_selection(const char *selection, int *ids, int cap);
+
+/*
+ * One kernel id through its runner, with the reference's loop: per run a memset of
+ * C, pattern allocation + both pattern kernels, the GEMM, a device synchronise and
+ * the frees (include/runners.cuh:852-872); prints "Kernel time: ..." and, when
+ * verify != 0, copies C to h_C and applies verifyResults' absolute tolerance 1e-2
+ * against h_C_ref (include/utils.cuh:222-254).  Stands in for
+ * run_esmm_ab_optimized_v3 / _no_check (runners.cuh:827-897), run_cuBlas
+ * (:109-144) and the `switch` of run_single_kernel (driver.cu:40-129).
+ * Ids served: 15 (cuBLAS), 29, and the joint-sparse ids 20, 21, 25, 26, 27, 28, 30
+ * as aliases of the same kernel at their own A granularity.  Ids 14, 16, 17 return
+ * ESMM_ERR_UNSUPPORTED.  *passed gets 1/0; *avg_ms the average time per run.
+ */
+int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, float *d_B,
+                    float *d_C, float *h_C, const float *h_C_ref, int runs, int verify,
+                    int print_skip_stats, int *passed, float *avg_ms);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ESMM_H_ */

@@ -1,0 +1,123 @@
+// Thin extern "C" shim over the UNMODIFIED reference sources.
+//
+// TEST INFRASTRUCTURE ONLY.  Built by oracle/Makefile with
+// `-I<reference root>` into oracle/_ref/libesmm_ref.so; the reference files are
+// compiled where they lie and never copied.  The shim exposes
+//   * the reference's host functions (CPU SGEMM, verification, rand()-based
+//     generators, kernel selection parser), callable without a GPU, and
+//   * the reference's own GPU pattern preprocessor and kernel id 29, so that the
+//     parity tests can compare this repository's kernels with the real thing on
+//     the same device buffers.
+// Nothing in the product library links or loads this file.
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <string>
+#include <string_view>
+
+#include "include/utils.cuh"
+#include "include/runners.cuh"
+
+extern "C" {
+
+// ---- host-only functions (no GPU needed) -----------------------------------
+
+// include/utils.cuh:208-219
+void ref_matrixMultiplyCPU(const float *A, const float *B, float *C, int M, int N, int K)
+{
+    matrixMultiplyCPU(A, B, C, M, N, K);
+}
+
+// Row range of the same loop nest: pointers shifted to row0 so that the
+// reference function itself runs on a slab (used to thread the CPU baseline).
+void ref_matrixMultiplyCPU_rows(const float *A, const float *B, float *C, int M, int N, int K,
+                                int row0, int row1)
+{
+    (void)M;
+    matrixMultiplyCPU(A + (size_t)row0 * K, B, C + (size_t)row0 * N, row1 - row0, N, K);
+}
+
+// include/utils.cuh:222-254 (prints on mismatch, like the reference)
+int ref_verifyResults(const float *gpu, const float *cpu, int size, float tol)
+{
+    return verifyResults(gpu, cpu, size, tol) ? 1 : 0;
+}
+
+// include/utils.cuh:303-341, :343-381, :142-156, :159-194
+void ref_randomize_A_blocklevel_8_32(float *mat, int M, int K, float sparsity_percent, unsigned seed)
+{
+    randomize_matrix_A_blocklevel<8, 32>(mat, M, K, sparsity_percent, seed);
+}
+void ref_randomize_B_blocklevel_8_32(float *mat, int K, int N, float sparsity_percent, unsigned seed)
+{
+    randomize_matrix_B_blocklevel_fixed<8, 32>(mat, K, N, sparsity_percent, seed);
+}
+void ref_randomize_with_pattern(float *mat, int M, int N, const char *pattern)
+{
+    randomize_matrix_with_pattern(mat, M, N, std::string_view(pattern));
+}
+void ref_randomize_unstructured(float *mat, int M, int N, float sparsity_percent, unsigned seed)
+{
+    randomize_matrix_unstructured(mat, M, N, sparsity_percent, seed);
+}
+void ref_srand(unsigned seed) { srand(seed); }
+
+// include/utils.cuh:18-46; writes up to cap ids, returns the count (-1 if the
+// parser throws, which std::stoi does on non-numeric input).
+int ref_parse_kernel_selection(const char *s, int *out, int cap)
+{
+    try {
+        std::vector<int> v = parse_kernel_selection(std::string(s));
+        int n = 0;
+        for (int k : v)
+            if (n < cap) out[n++] = k;
+        return (int)v.size();
+    } catch (...) {
+        return -1;
+    }
+}
+const char *ref_get_kernel_name(int id) { return get_kernel_name(id); }
+
+// ---- GPU functions (reference kernels on caller-provided device buffers) ----
+
+// preprocess_ab<8,32,32> (src/preprocessors/ab_preprocessor.cu:297-326), the
+// instantiation id 29 uses (include/runners.cuh:859).  Copies the pattern bytes
+// into caller buffers of (M/32)*(K/8) and (N/32)*(K/8) bytes.
+int ref_preprocess_ab_32(const float *dA, const float *dB, int M, int N, int K,
+                         uint8_t *d_a_out, uint8_t *d_b_out)
+{
+    ABPatternMetadata meta = preprocess_ab<8, 32, 32>(dA, dB, M, N, K);
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess && d_a_out)
+        e = cudaMemcpy(d_a_out, meta.d_a_patterns, (size_t)meta.numMBlocks * meta.numKBlocks,
+                       cudaMemcpyDeviceToDevice);
+    if (e == cudaSuccess && d_b_out)
+        e = cudaMemcpy(d_b_out, meta.d_b_patterns, (size_t)meta.numNBlocks * meta.numKBlocks,
+                       cudaMemcpyDeviceToDevice);
+    free_ab_pattern_metadata(meta);
+    return (int)e;
+}
+
+// One launch of esmm_ab_optimized_v3 through dispatch_v3
+// (include/runners.cuh:801-825, 830-841) on caller-provided patterns.
+int ref_esmm_v3_launch(int M, int N, int K, float *dA, float *dB, float *dC,
+                       uint8_t *d_a_pat, uint8_t *d_b_pat)
+{
+    dim3 blockDim(256);
+    dim3 gridDim(CEIL_DIV(N, 128), CEIL_DIV(M, 64));
+    dispatch_v3<64, 128, 8, 32, 32, 2, 1, 8, 256>(gridDim, blockDim, K / 8, M, N, K, dA, dB, dC,
+                                                  d_a_pat, d_b_pat);
+    cudaError_t e = cudaGetLastError();
+    return (int)e;
+}
+
+// The reference's own timed runner (include/runners.cuh:893-897): memset +
+// malloc + both preprocessors + kernel + sync + free per run; prints
+// "Kernel time: ..." on stdout.
+int ref_run_esmm_ab_optimized_v3_no_check(int rows, int cols, int inners, float *dA, float *dB,
+                                          float *dC, int runs)
+{
+    return run_esmm_ab_optimized_v3_no_check(rows, cols, inners, dA, dB, dC, runs) ? 1 : 0;
+}
+
+}  // extern "C"
