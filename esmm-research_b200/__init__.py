@@ -56,6 +56,10 @@ _SIGNATURES = {
     "esmm_bpat_save": (_i, [C.c_char_p, _vp, _i, _i]),
     "esmm_bpat_load": (_i, [C.c_char_p, _vp, _i, _i]),
     "esmm_gemm_ab": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "esmm_a_packed_bytes": (C.c_size_t, [_i, _i]),
+    "esmm_preprocess_a_packed": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
+    "esmm_gemm_ab_packed": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "esmm_sgemm_joint_workspace_bytes": (C.c_size_t, [_i, _i]),
     "esmm_sgemm_joint": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "esmm_device_status": (_i, [_vp]),
     "esmm_plan_create": (_i, [_i, _i, _i, _vp, _i, C.POINTER(_vp)]),
@@ -115,8 +119,26 @@ def gemm_ab(M, N, K, d_A, d_B, d_C, d_a_pat, d_b_pat, a_tile_m: int = 32, stream
     check(lib().esmm_gemm_ab(M, N, K, d_A, d_B, d_C, d_a_pat, d_b_pat, a_tile_m, stream), "esmm_gemm_ab")
 
 
-def sgemm_joint(M, N, K, d_A, d_B, d_C, d_b_pat, d_a_scratch, stream: int = 0) -> None:
-    check(lib().esmm_sgemm_joint(M, N, K, d_A, d_B, d_C, d_b_pat, d_a_scratch, stream), "esmm_sgemm_joint")
+def sgemm_joint(M, N, K, d_A, d_B, d_C, d_b_pat, d_workspace, stream: int = 0) -> None:
+    """Packing preprocess of A + packed GEMM; d_workspace holds sgemm_joint_workspace_bytes(M, K)."""
+    check(lib().esmm_sgemm_joint(M, N, K, d_A, d_B, d_C, d_b_pat, d_workspace, stream), "esmm_sgemm_joint")
+
+
+def sgemm_joint_workspace_bytes(M: int, K: int) -> int:
+    return int(lib().esmm_sgemm_joint_workspace_bytes(M, K))
+
+
+def a_packed_bytes(M: int, K: int) -> int:
+    return int(lib().esmm_a_packed_bytes(M, K))
+
+
+def preprocess_a_packed(d_A: int, M: int, K: int, d_out: int, d_packed: int, stream: int = 0) -> None:
+    check(lib().esmm_preprocess_a_packed(d_A, M, K, d_out, d_packed, stream), "esmm_preprocess_a_packed")
+
+
+def gemm_ab_packed(M, N, K, d_a_packed, d_B, d_C, d_a_pat, d_b_pat, stream: int = 0) -> None:
+    check(lib().esmm_gemm_ab_packed(M, N, K, d_a_packed, d_B, d_C, d_a_pat, d_b_pat, stream),
+          "esmm_gemm_ab_packed")
 
 
 def device_status(stream: int = 0) -> None:

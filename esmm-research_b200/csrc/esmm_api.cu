@@ -17,7 +17,11 @@ namespace esmm {
 
 int gemm_ab_launch(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
                    const uint8_t *d_a_pat, const uint8_t *d_b_pat, int a_tile_m, cudaStream_t stream);
+int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                          const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream);
 int preprocess_a_launch(const float *d_A, int M, int K, int tile_m, uint8_t *d_out, cudaStream_t stream);
+int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, float *d_packed,
+                             cudaStream_t stream);
 int preprocess_b_launch(const float *d_B, int K, int N, uint8_t *d_out, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------
@@ -262,12 +266,28 @@ void esmm_pattern_lut(uint8_t pattern, uint8_t *count, uint8_t offsets[8])
     if (count) *count = c;
 }
 
-int esmm_sgemm_joint(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
-                     const uint8_t *d_b_pat, uint8_t *d_a_pat_scratch, void *stream)
+static size_t pattern_region_bytes(int M, int K)
 {
-    int st = esmm::preprocess_a_launch(d_A, M, K, 32, d_a_pat_scratch, (cudaStream_t)stream);
+    return (esmm_a_pattern_bytes(M, K, 32) + 255) & ~(size_t)255;
+}
+
+size_t esmm_sgemm_joint_workspace_bytes(int M, int K)
+{
+    if (M <= 0 || K <= 0) return 0;
+    return pattern_region_bytes(M, K) + esmm_a_packed_bytes(M, K);
+}
+
+int esmm_sgemm_joint(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
+                     const uint8_t *d_b_pat, void *d_workspace, void *stream)
+{
+    if (!d_workspace) return ESMM_ERR_NULL;
+    if (M <= 0 || N <= 0 || K <= 0 || (K & 3) || (N & 3)) return ESMM_ERR_SHAPE;
+    if ((uintptr_t)d_workspace & 255) return ESMM_ERR_ALIGN;
+    uint8_t *a_pat = static_cast<uint8_t *>(d_workspace);
+    float *a_packed = reinterpret_cast<float *>(a_pat + pattern_region_bytes(M, K));
+    int st = esmm::preprocess_a_pack_launch(d_A, M, K, a_pat, a_packed, (cudaStream_t)stream);
     if (st != ESMM_OK) return st;
-    return esmm::gemm_ab_launch(M, N, K, d_A, d_B, d_C, d_a_pat_scratch, d_b_pat, 32, (cudaStream_t)stream);
+    return esmm::gemm_ab_packed_launch(M, N, K, a_packed, d_B, d_C, a_pat, d_b_pat, (cudaStream_t)stream);
 }
 
 int esmm_device_status(void *stream)
@@ -284,7 +304,7 @@ int esmm_device_status(void *stream)
 // ---- host-buffer plan -------------------------------------------------------
 struct esmm_plan {
     int M, N, K, chunks;
-    float *d_A, *d_B, *d_C;
+    float *d_A, *d_B, *d_C, *d_a_packed;
     uint8_t *d_a_pat, *d_b_pat;
     cudaStream_t streams[3];
     cudaEvent_t up[64], done[64];
@@ -297,6 +317,7 @@ int esmm_plan_destroy(esmm_plan *pl)
     cudaFree(pl->d_B);
     cudaFree(pl->d_C);
     cudaFree(pl->d_a_pat);
+    cudaFree(pl->d_a_packed);
     cudaFree(pl->d_b_pat);
     for (int i = 0; i < 3; ++i)
         if (pl->streams[i]) cudaStreamDestroy(pl->streams[i]);
@@ -337,6 +358,7 @@ int esmm_plan_create(int M, int N, int K, const float *h_B, int chunks, esmm_pla
     PLAN_TRY(cudaMalloc(&pl->d_B, (size_t)K * N * 4));
     PLAN_TRY(cudaMalloc(&pl->d_C, (size_t)M * N * 4));
     PLAN_TRY(cudaMalloc(&pl->d_a_pat, esmm_a_pattern_bytes(M, K, 32)));
+    PLAN_TRY(cudaMalloc(&pl->d_a_packed, esmm_a_packed_bytes(M, K)));
     PLAN_TRY(cudaMalloc(&pl->d_b_pat, esmm_b_pattern_bytes(K, N)));
     for (int i = 0; i < 3; ++i) PLAN_TRY(cudaStreamCreateWithFlags(&pl->streams[i], cudaStreamNonBlocking));
     for (int i = 0; i < chunks; ++i) {
@@ -374,10 +396,11 @@ int esmm_plan_run(esmm_plan *pl, const float *h_A, float *h_C)
         ESMM_CUDA_TRY(cudaEventRecord(pl->up[c], s_up));
         ESMM_CUDA_TRY(cudaStreamWaitEvent(s_run, pl->up[c], 0));
         uint8_t *apat = pl->d_a_pat + (size_t)(r0 / 32) * nKB;
-        int st = esmm::preprocess_a_launch(pl->d_A + a_off, r1 - r0, K, 32, apat, s_run);
+        float *apacked = pl->d_a_packed + (size_t)r0 * nKB * esmm::BK;  // r0 is a multiple of 128
+        int st = esmm::preprocess_a_pack_launch(pl->d_A + a_off, r1 - r0, K, apat, apacked, s_run);
         if (st != ESMM_OK) return st;
-        st = esmm::gemm_ab_launch(r1 - r0, N, K, pl->d_A + a_off, pl->d_B, pl->d_C + c_off, apat, pl->d_b_pat,
-                                  32, s_run);
+        st = esmm::gemm_ab_packed_launch(r1 - r0, N, K, apacked, pl->d_B, pl->d_C + c_off, apat, pl->d_b_pat,
+                                         s_run);
         if (st != ESMM_OK) return st;
         ESMM_CUDA_TRY(cudaEventRecord(pl->done[c], s_run));
         ESMM_CUDA_TRY(cudaStreamWaitEvent(s_down, pl->done[c], 0));
@@ -658,19 +681,35 @@ int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, f
                 esmm_free_ab_pattern_metadata(&meta);
             }
         }
+        // Ids with 32-row A patterns run the packed variant; its k-major copy of A lives in a
+        // buffer allocated once per runner call (the pattern arrays are allocated per run, as
+        // in the reference loop).
+        float *d_packed = nullptr;
+        if (a_tile == 32 && st == ESMM_OK) {
+            cudaError_t e = cudaMalloc(&d_packed, esmm_a_packed_bytes(rows, inners));
+            if (e != cudaSuccess) st = esmm::record_cuda_error(e, "cudaMalloc(packed A)");
+        }
         cudaEventRecord(start);
         for (int i = 0; i < runs && st == ESMM_OK; ++i) {
             cudaMemset(d_C, 0, (size_t)rows * cols * sizeof(float));
             esmm_ab_pattern_metadata meta;
             st = esmm_preprocess_ab(d_A, d_B, rows, cols, inners, a_tile, nullptr, &meta);
             if (st != ESMM_OK) break;
-            st = esmm::gemm_ab_launch(rows, cols, inners, d_A, d_B, d_C, meta.d_a_patterns, meta.d_b_patterns,
-                                      a_tile, 0);
+            if (d_packed) {
+                st = esmm::preprocess_a_pack_launch(d_A, rows, inners, meta.d_a_patterns, d_packed, 0);
+                if (st == ESMM_OK)
+                    st = esmm::gemm_ab_packed_launch(rows, cols, inners, d_packed, d_B, d_C, meta.d_a_patterns,
+                                                     meta.d_b_patterns, 0);
+            } else {
+                st = esmm::gemm_ab_launch(rows, cols, inners, d_A, d_B, d_C, meta.d_a_patterns,
+                                          meta.d_b_patterns, a_tile, 0);
+            }
             cudaDeviceSynchronize();
             esmm_free_ab_pattern_metadata(&meta);
         }
         cudaEventRecord(stop);
         cudaEventSynchronize(stop);
+        if (d_packed) cudaFree(d_packed);
     }
 
     float ms = 0.f;

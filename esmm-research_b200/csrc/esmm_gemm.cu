@@ -6,14 +6,20 @@
 // different machine mapping:
 //
 //   * persistent CTAs, one per SM, each walking 128 x 128 tiles of C;
-//   * 16 consumer warps, each owning one 32 x 32 block of the tile, i.e. exactly one
-//     (A pattern row, B pattern row) pair, so every skip decision is warp-uniform;
+//   * 8 consumer warps, each owning 64 rows x 32 columns of the tile, i.e. two A pattern
+//     rows ("top" and "bottom" 32-row block) and one B pattern row; a thread holds 8 x 8
+//     outputs, 4 rows in each block, so the two joint masks are applied separately and the
+//     executed multiply-adds are exactly those of the reference's 32 x 32 warp tiles;
+//   * lanes are laid out so that every group of 4 consecutive lanes touches 2 rows x 2
+//     column chunks: on this GPU a 16-byte shared load costs 2 wavefronts when each such
+//     group reads at most 32 distinct bytes and 4 otherwise;
 //   * one TMA warp that streams K blocks (A box 128 rows x 8 k, 32-byte swizzled; B box
-//     8 k x 128 columns, or single live k rows when few are live) into a ring of stages
-//     guarded by full/empty mbarriers, and never issues a copy for a K block whose joint
-//     mask is zero for the whole tile;
+//     8 k x 128 columns, or single live k rows when few are live) into a ring of stages of
+//     4 live K blocks guarded by full/empty mbarriers, and never issues a copy for a K block
+//     whose joint mask is zero for the whole tile;
 //   * one mask warp that, one tile ahead, joins the A and B pattern bytes of the tile into
-//     a compacted list of live K blocks with their per-warp-row / per-warp-column masks.
+//     a compacted list of live K blocks with per-stage 32-bit masks (one byte per K block of
+//     the stage) for each 32-row and 32-column block of the tile.
 //
 // Every wait is bounded; a wait that expires raises the device status word and the CTA
 // leaves after waiting (bounded again) for its copies in flight.
@@ -21,25 +27,26 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "esmm_common.cuh"
+#include "esmm_gemm_shared.cuh"
 
 namespace esmm {
 
-constexpr int TILE_M = 128;
-constexpr int TILE_N = 128;
 constexpr int KB_PER_STAGE = 4;                      // live K blocks per pipeline stage
 constexpr int A_SUB_BYTES = TILE_M * BK * 4;         // 4096: one K block of the A tile
 constexpr int B_ROW_BYTES = TILE_N * 4;              // 512: one k row of the B tile
 constexpr int B_SUB_BYTES = BK * B_ROW_BYTES;        // 4096
 constexpr int STAGE_A_BYTES = KB_PER_STAGE * A_SUB_BYTES;
 constexpr int STAGE_BYTES = KB_PER_STAGE * (A_SUB_BYTES + B_SUB_BYTES);  // 32768
-constexpr int CONSUMER_WARPS = 16;
+constexpr int CONSUMER_WARPS = 8;
 constexpr int TMA_WARP = CONSUMER_WARPS;
 constexpr int MASK_WARP = CONSUMER_WARPS + 1;
-constexpr int GEMM_THREADS = (CONSUMER_WARPS + 2) * 32;  // 576
+constexpr int GEMM_THREADS = (CONSUMER_WARPS + 2) * 32;  // 320
 constexpr int MAX_STAGES = 6;
-constexpr int GROUP_M = 8;                           // tile rows per raster group
-constexpr int SMEM_LIMIT = 232448;                   // 227 KB per CTA on sm_100
+constexpr int MASK_STAGE_BYTES = 32;                 // 4 A words + 4 B words per stage
+#ifndef ESMM_DENSE_UNROLL
+#define ESMM_DENSE_UNROLL 1
+#endif
+constexpr int DENSE_UNROLL = ESMM_DENSE_UNROLL;      // K blocks of a dense stage unrolled together
 
 struct GemmParams {
     int M, N, K;
@@ -69,8 +76,8 @@ __host__ __device__ inline SmemLayout smem_layout(int stages, int nKBpad)
     uint32_t o = 0;
     L.stage_off = o;
     o += (uint32_t)stages * STAGE_BYTES;
-    L.cmask_off = o;  // two buffers of (A word, B word) per live K block
-    L.cmask_stride = (uint32_t)nKBpad * 8;
+    L.cmask_off = o;  // two buffers; per stage of 4 live K blocks: A words [4], B words [4]
+    L.cmask_stride = (uint32_t)(nKBpad / KB_PER_STAGE) * MASK_STAGE_BYTES;
     o += 2 * L.cmask_stride;
     L.klist_off = o;  // two buffers of live K block indices
     L.klist_stride = (uint32_t)nKBpad * 2;
@@ -84,39 +91,13 @@ __host__ __device__ inline SmemLayout smem_layout(int stages, int nKBpad)
     return L;
 }
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int &tm, int &tn)
+// Four consecutive k of one K block, live for both 32-row blocks of the warp: each of the
+// thread's 8 rows comes in as one 16-byte load (4 k), each k of B as two.
+__device__ __forceinline__ void dense_nibble(float (&acc)[8][8], const char *ap, const char *bp)
 {
-    const int per_group = GROUP_M * tiles_n;
-    const int group = tile / per_group;
-    const int first_m = group * GROUP_M;
-    const int gsize = min(tiles_m - first_m, GROUP_M);
-    const int r = tile - group * per_group;
-    tm = first_m + r % gsize;
-    tn = r / gsize;
-}
-
-__device__ __forceinline__ void fma8(float (&acc)[8], float a, const float4 &b0, const float4 &b1)
-{
-    acc[0] = fmaf(a, b0.x, acc[0]);
-    acc[1] = fmaf(a, b0.y, acc[1]);
-    acc[2] = fmaf(a, b0.z, acc[2]);
-    acc[3] = fmaf(a, b0.w, acc[3]);
-    acc[4] = fmaf(a, b1.x, acc[4]);
-    acc[5] = fmaf(a, b1.y, acc[5]);
-    acc[6] = fmaf(a, b1.z, acc[6]);
-    acc[7] = fmaf(a, b1.w, acc[7]);
-}
-
-// Four consecutive k (4H .. 4H+3) of one K block, all live: A comes in as one 16-byte load
-// per row (the 32-byte swizzle keeps the 8 rows of a warp on distinct banks).
-template <int H>
-__device__ __forceinline__ void dense_half(float (&acc)[4][8], const char *sA, const char *sB,
-                                           int swoff)
-{
-    const char *ap = sA + ((H << 4) ^ swoff);
-    float a[4][4];
+    float a[8][4];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
+    for (int i = 0; i < 8; ++i) {
         const float4 v = *reinterpret_cast<const float4 *>(ap + i * 256);
         a[i][0] = v.x;
         a[i][1] = v.y;
@@ -125,42 +106,96 @@ __device__ __forceinline__ void dense_half(float (&acc)[4][8], const char *sA, c
     }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
-        const char *bp = sB + (4 * H + kk) * B_ROW_BYTES;
-        const float4 b0 = *reinterpret_cast<const float4 *>(bp);
-        const float4 b1 = *reinterpret_cast<const float4 *>(bp + 64);
+        const float4 b0 = *reinterpret_cast<const float4 *>(bp + kk * B_ROW_BYTES);
+        const float4 b1 = *reinterpret_cast<const float4 *>(bp + kk * B_ROW_BYTES + 64);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) fma8(acc[i], a[i][kk], b0, b1);
+        for (int i = 0; i < 8; ++i) fma8(acc[i], a[i][kk], b0, b1);
     }
 }
 
-// The live k of one nibble (bits of `nib` are k offsets 4H .. 4H+3), one at a time, ascending.
-template <int H>
-__device__ __forceinline__ void sparse_half(float (&acc)[4][8], const char *sA, const char *sB,
-                                            int swoff, unsigned nib)
+// The live k of one nibble, one at a time, ascending; `tn` / `bn` are the nibble's joint bits
+// for the warp's top / bottom 32-row block.
+__device__ __forceinline__ void sparse_nibble(float (&acc)[8][8], const char *ap, const char *bp,
+                                              unsigned tn, unsigned bn)
 {
-    const char *ap = sA + ((H << 4) ^ swoff);
-    const char *bp0 = sB + 4 * H * B_ROW_BYTES;
+    unsigned u = tn | bn;
 #pragma unroll 1
-    while (nib) {
-        const int kk = __ffs(nib) - 1;
-        nib &= nib - 1;
-        const char *bp = bp0 + kk * B_ROW_BYTES;
-        const float4 b0 = *reinterpret_cast<const float4 *>(bp);
-        const float4 b1 = *reinterpret_cast<const float4 *>(bp + 64);
+    while (u) {
+        const int kk = __ffs(u) - 1;
+        u &= u - 1;
+        const float4 b0 = *reinterpret_cast<const float4 *>(bp + kk * B_ROW_BYTES);
+        const float4 b1 = *reinterpret_cast<const float4 *>(bp + kk * B_ROW_BYTES + 64);
         const char *akp = ap + kk * 4;
+        float a[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) fma8(acc[i], *reinterpret_cast<const float *>(akp + i * 256), b0, b1);
+        for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float *>(akp + i * 256);
+        if ((tn >> kk) & 1u) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) fma8(acc[i], a[i], b0, b1);
+        }
+        if ((bn >> kk) & 1u) {
+#pragma unroll
+            for (int i = 4; i < 8; ++i) fma8(acc[i], a[i], b0, b1);
+        }
     }
 }
 
-__device__ __forceinline__ void compute_kblock(float (&acc)[4][8], const char *sA, const char *sB,
-                                               int swoff, unsigned joint)
+// A stage whose 32 k are all live for both row blocks: straight-line code, so that the
+// compiler can issue the loads of a nibble under the multiply-adds of the one before.
+__device__ __forceinline__ void dense_stage(float (&acc)[8][8], const char *sA, const char *sB, int swoff)
 {
-    const unsigned lo = joint & 0xFu, hi = joint >> 4;
-    if (lo == 0xFu) dense_half<0>(acc, sA, sB, swoff);
-    else if (lo) sparse_half<0>(acc, sA, sB, swoff, lo);
-    if (hi == 0xFu) dense_half<1>(acc, sA, sB, swoff);
-    else if (hi) sparse_half<1>(acc, sA, sB, swoff, hi);
+    const char *ap0 = sA + swoff;         // k 0..3 of each K block
+    const char *ap1 = sA + (16 ^ swoff);  // k 4..7
+#pragma unroll DENSE_UNROLL
+    for (int j = 0; j < KB_PER_STAGE; ++j) {
+        dense_nibble(acc, ap0 + j * A_SUB_BYTES, sB + j * B_SUB_BYTES);
+        dense_nibble(acc, ap1 + j * A_SUB_BYTES, sB + j * B_SUB_BYTES + 4 * B_ROW_BYTES);
+    }
+}
+
+// A stage without any fully live nibble: its live k (bits of jt | jb, bit = 8 * K block + k)
+// are taken four at a time, ascending; all loads of a batch are issued before its
+// multiply-adds so that their latency overlaps.
+__device__ __forceinline__ void sparse_stage(float (&acc)[8][8], const char *sA, const char *sB, int swoff,
+                                             unsigned jt, unsigned jb)
+{
+    unsigned u = jt | jb;
+#pragma unroll 1
+    while (u) {
+        int bi[4];
+        bool valid[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            valid[j] = u != 0;
+            bi[j] = valid[j] ? __ffs(u) - 1 : bi[0];
+            u &= u - 1;
+        }
+        float a[4][8];
+        float4 b0[4], b1[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int b = bi[j];
+            const char *ap = sA + ((b >> 3) << 12) + ((((b >> 2) & 1) << 4) ^ swoff) + ((b & 3) << 2);
+            const char *bp = sB + (b << 9);
+            b0[j] = *reinterpret_cast<const float4 *>(bp);
+            b1[j] = *reinterpret_cast<const float4 *>(bp + 64);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) a[j][i] = *reinterpret_cast<const float *>(ap + i * 256);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (valid[j]) {
+                if ((jt >> bi[j]) & 1u) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) fma8(acc[i], a[j][i], b0[j], b1[j]);
+                }
+                if ((jb >> bi[j]) & 1u) {
+#pragma unroll
+                    for (int i = 4; i < 8; ++i) fma8(acc[i], a[j][i], b0[j], b1[j]);
+                }
+            }
+        }
+    }
 }
 
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -209,16 +244,16 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
             if (!ok) break;
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-            uint2 *cmask = reinterpret_cast<uint2 *>(smem + L.cmask_off + buf * L.cmask_stride);
+            uint8_t *cmask = reinterpret_cast<uint8_t *>(smem + L.cmask_off + buf * L.cmask_stride);
             uint16_t *klist = reinterpret_cast<uint16_t *>(smem + L.klist_off + buf * L.klist_stride);
             int base = 0;
             for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
                 const int kb = kb0 + lane;
-                unsigned aw = 0, bw = 0;
+                unsigned aw = 0, bw = 0;  // byte i: pattern of the tile's i-th 32-row / 32-column block
                 if (kb < p.nKB) {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const int mb = tm * 4 + i;  // 32-row block of C
+                        const int mb = tm * 4 + i;
                         unsigned v = 0;
                         const int r0 = (mb / p.a_div) * p.a_mul;
                         for (int t = 0; t < p.a_mul; ++t)
@@ -235,7 +270,12 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
                 const unsigned bal = __ballot_sync(0xFFFFFFFFu, live);
                 if (live) {
                     const int pos = base + __popc(bal & lt_mask);
-                    cmask[pos] = make_uint2(aw, bw);
+                    uint8_t *m = cmask + (pos >> 2) * MASK_STAGE_BYTES + (pos & 3);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        m[4 * i] = (uint8_t)(aw >> (8 * i));
+                        m[16 + 4 * i] = (uint8_t)(bw >> (8 * i));
+                    }
                     klist[pos] = (uint16_t)kb;
                 }
                 base += __popc(bal);
@@ -244,7 +284,9 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
             if (lane < 4) {
                 const int pos = base + lane;
                 if (pos < ((base + 3) & ~3)) {
-                    cmask[pos] = make_uint2(0u, 0u);
+                    uint8_t *m = cmask + (pos >> 2) * MASK_STAGE_BYTES + (pos & 3);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) m[4 * i] = 0;
                     klist[pos] = 0;
                 }
             }
@@ -254,91 +296,81 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
         }
     } else if (warp == TMA_WARP) {
         // ---------------- TMA warp: stream live K blocks into the ring ----------------
+        // All 32 lanes work: lane = 8 * j + kk looks after k row kk of the stage's j-th K block,
+        // so the copies of a stage go out in one or two warp instructions instead of a long
+        // single-thread sequence.
         if (lane == 0) {
             tma_prefetch_descriptor(&map_a);
             tma_prefetch_descriptor(&map_b_box);
             tma_prefetch_descriptor(&map_b_row);
-            int slot = 0;
-            uint32_t phase = 0;
-            uint32_t issued_bits = 0, parity_bits = 0;  // per slot: ever issued / parity of last issue
-            int it = 0;
-            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
-                const int buf = it & 1;
-                ok = mbar_wait(mfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+        }
+        const int j = lane >> 3, kk = lane & 7;
+        int slot = 0;
+        uint32_t phase = 0;
+        uint32_t issued_bits = 0, parity_bits = 0;  // per slot: ever issued / parity of last issue
+        int it = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(mfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const uint4 *cmask = reinterpret_cast<const uint4 *>(smem + L.cmask_off + buf * L.cmask_stride);
+            const uint16_t *klist = reinterpret_cast<const uint16_t *>(smem + L.klist_off + buf * L.klist_stride);
+            const int n = nlive[buf];
+            for (int i0 = 0; i0 < n; i0 += KB_PER_STAGE) {
+                const uint4 ma = cmask[(i0 >> 2) * 2], mb = cmask[(i0 >> 2) * 2 + 1];
+                // byte j: live k of the stage's j-th K block for the tile as a whole
+                const unsigned live = (ma.x | ma.y | ma.z | ma.w) & (mb.x | mb.y | mb.z | mb.w);
+                const bool valid = i0 + j < n;
+                const unsigned mj = (live >> (8 * j)) & 0xFFu;
+                const bool by_row = __popc(mj) <= p.brow_bits;
+                const bool my_row = valid && by_row && ((mj >> kk) & 1u);
+                const bool my_box = valid && !by_row && kk == 0;
+                const int k0 = valid ? (int)klist[i0 + j] * BK : 0;
+                uint32_t my_bytes = (my_row ? B_ROW_BYTES : 0) + (my_box ? B_SUB_BYTES : 0);
+                if (valid && kk == 0) my_bytes += A_SUB_BYTES;
+                const uint32_t bytes = __reduce_add_sync(0xFFFFFFFFu, my_bytes);
+                ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
+                ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
-                int tm, tn;
-                tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-                const uint2 *cmask = reinterpret_cast<const uint2 *>(smem + L.cmask_off + buf * L.cmask_stride);
-                const uint16_t *klist = reinterpret_cast<const uint16_t *>(smem + L.klist_off + buf * L.klist_stride);
-                const int n = nlive[buf];
-                for (int i0 = 0; i0 < n; i0 += KB_PER_STAGE) {
-                    ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
-                    if (!ok) break;
-                    const int cnt = min(KB_PER_STAGE, n - i0);
-                    unsigned live[KB_PER_STAGE];
-                    uint32_t bytes = 0;
-#pragma unroll
-                    for (int j = 0; j < KB_PER_STAGE; ++j) {
-                        live[j] = 0;
-                        if (j < cnt) {
-                            const uint2 m = cmask[i0 + j];
-                            unsigned au = m.x | (m.x >> 16), bu = m.y | (m.y >> 16);
-                            au = (au | (au >> 8)) & 0xFFu;
-                            bu = (bu | (bu >> 8)) & 0xFFu;
-                            live[j] = au & bu;
-                            const int bits = __popc(live[j]);
-                            bytes += A_SUB_BYTES + (bits <= p.brow_bits ? bits * B_ROW_BYTES : B_SUB_BYTES);
-                        }
-                    }
-                    const uint32_t full = full0 + 8 * slot;
-                    mbar_arrive_expect_tx(full, bytes);
-                    const uint32_t sbase = smem_u32(smem + L.stage_off) + (uint32_t)slot * STAGE_BYTES;
-#pragma unroll
-                    for (int j = 0; j < KB_PER_STAGE; ++j) {
-                        if (j < cnt) {
-                            const int k0 = (int)klist[i0 + j] * BK;
-                            tma_load_2d(sbase + j * A_SUB_BYTES, &map_a, k0, tm * TILE_M, full);
-                            const uint32_t sb = sbase + STAGE_A_BYTES + j * B_SUB_BYTES;
-                            unsigned m = live[j];
-                            if (__popc(m) <= p.brow_bits) {
-                                while (m) {
-                                    const int kk = __ffs(m) - 1;
-                                    m &= m - 1;
-                                    tma_load_2d(sb + kk * B_ROW_BYTES, &map_b_row, tn * TILE_N, k0 + kk, full);
-                                }
-                            } else {
-                                tma_load_2d(sb, &map_b_box, tn * TILE_N, k0, full);
-                            }
-                        }
-                    }
-                    issued_bits |= 1u << slot;
-                    parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
-                    if (++slot == p.stages) {
-                        slot = 0;
-                        phase ^= 1;
-                    }
+                const uint32_t full = full0 + 8 * slot;
+                if (lane == 0) mbar_arrive_expect_tx(full, bytes);
+                __syncwarp();
+                const uint32_t sa = smem_u32(smem + L.stage_off) + (uint32_t)slot * STAGE_BYTES + j * A_SUB_BYTES;
+                const uint32_t sb = sa + STAGE_A_BYTES;
+                if (valid && kk == 0) tma_load_2d(sa, &map_a, k0, tm * TILE_M, full);
+                if (my_row) tma_load_2d(sb + kk * B_ROW_BYTES, &map_b_row, tn * TILE_N, k0 + kk, full);
+                if (my_box) tma_load_2d(sb, &map_b_box, tn * TILE_N, k0, full);
+                issued_bits |= 1u << slot;
+                parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
+                if (++slot == p.stages) {
+                    slot = 0;
+                    phase ^= 1;
                 }
-                if (!ok) break;
-                mbar_arrive(mempty0 + 8 * buf);
             }
-            if (!ok) {
-                // leave only after the copies already issued have landed (bounded)
-                for (int s = 0; s < p.stages; ++s) {
-                    if (!(issued_bits & (1u << s))) continue;
-                    const uint32_t par = (parity_bits >> s) & 1u;
-                    for (int tries = 0; tries < (1 << 16); ++tries)
-                        if (mbar_try_wait(full0 + 8 * s, par)) break;
-                }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(mempty0 + 8 * buf);
+        }
+        if (!ok && lane == 0) {
+            // leave only after the copies already issued have landed (bounded)
+            for (int s = 0; s < p.stages; ++s) {
+                if (!(issued_bits & (1u << s))) continue;
+                const uint32_t par = (parity_bits >> s) & 1u;
+                for (int tries = 0; tries < (1 << 16); ++tries)
+                    if (mbar_try_wait(full0 + 8 * s, par)) break;
             }
         }
     } else {
-        // ---------------- consumer warps: 32 x 32 block of the tile each ----------------
-        const int wm = warp >> 2, wn = warp & 3;
-        const int lm = lane >> 2, ln = lane & 3;
+        // ---------------- consumer warps: 64 rows x 32 columns of the tile each ----------------
+        const int wm = warp >> 2, wn = warp & 3;              // 2 x 4 warps
+        const int lm = (lane >> 1) & 7;                       // row (group) within the warp's 32-row blocks
+        const int ln = (lane & 1) | ((lane >> 4) << 1);       // 16-byte column chunk
         const int swoff = p.swizzle ? ((lm >> 2) & 1) << 4 : 0;
-        const uint32_t a_thr = (uint32_t)(wm * 32 + lm) * 32;               // row offset in an A sub-slot
+        // the thread owns rows lm + 8 i of the warp's 64; a row of an A sub-slot is 32 bytes
+        const uint32_t a_thr = (uint32_t)(wm * 64 + lm) * 32;
         const uint32_t b_thr = STAGE_A_BYTES + (uint32_t)(wn * 32 + ln * 4) * 4;  // column offset in a B sub-slot
-        const int ash = 8 * wm, bsh = 8 * wn;
         int slot = 0;
         uint32_t phase = 0;
         int it = 0;
@@ -348,31 +380,49 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
             if (!ok) break;
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-            const uint4 *cmask4 = reinterpret_cast<const uint4 *>(smem + L.cmask_off + buf * L.cmask_stride);
+            const char *cmask = smem + L.cmask_off + buf * L.cmask_stride;
             const int n = nlive[buf];
 
-            float acc[4][8];
+            float acc[8][8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+            for (int i = 0; i < 8; ++i)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
 
             for (int i0 = 0; i0 < n; i0 += KB_PER_STAGE) {
-                const uint4 m01 = cmask4[(i0 >> 1)];
-                const uint4 m23 = cmask4[(i0 >> 1) + 1];
-                const unsigned j0 = ((m01.x >> ash) & (m01.y >> bsh)) & 0xFFu;
-                const unsigned j1 = ((m01.z >> ash) & (m01.w >> bsh)) & 0xFFu;
-                const unsigned j2 = ((m23.x >> ash) & (m23.y >> bsh)) & 0xFFu;
-                const unsigned j3 = ((m23.z >> ash) & (m23.w >> bsh)) & 0xFFu;
+                const char *ms = cmask + (i0 >> 2) * MASK_STAGE_BYTES;
+                const uint2 am = *reinterpret_cast<const uint2 *>(ms + 8 * wm);   // top, bottom 32-row block
+                const unsigned bm = *reinterpret_cast<const unsigned *>(ms + 16 + 4 * wn);
+                const unsigned jt = am.x & bm, jb = am.y & bm;   // byte j: joint mask of the stage's j-th K block
                 ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
                 if (!ok) break;
-                const char *sbase = smem + L.stage_off + (size_t)slot * STAGE_BYTES;
-                const char *sA = sbase + a_thr;
-                const char *sB = sbase + b_thr;
-                if (j0) compute_kblock(acc, sA, sB, swoff, j0);
-                if (j1) compute_kblock(acc, sA + A_SUB_BYTES, sB + B_SUB_BYTES, swoff, j1);
-                if (j2) compute_kblock(acc, sA + 2 * A_SUB_BYTES, sB + 2 * B_SUB_BYTES, swoff, j2);
-                if (j3) compute_kblock(acc, sA + 3 * A_SUB_BYTES, sB + 3 * B_SUB_BYTES, swoff, j3);
+                const char *sA = smem + L.stage_off + (size_t)slot * STAGE_BYTES + a_thr;
+                const char *sB = smem + L.stage_off + (size_t)slot * STAGE_BYTES + b_thr;
+                const unsigned both = jt & jb;
+                unsigned dn = both & (both >> 1);   // bit 4n: nibble n is live for both row blocks
+                dn &= dn >> 2;
+                dn &= 0x11111111u;
+                if (dn == 0x11111111u) {
+                    dense_stage(acc, sA, sB, swoff);
+                } else if (dn == 0u) {
+                    sparse_stage(acc, sA, sB, swoff, jt, jb);
+                } else {
+                    // mixed: nibble by nibble, skipping the dead ones
+                    unsigned z = jt | jb;
+                    z |= z >> 1;
+                    z |= z >> 2;
+                    z &= 0x11111111u;
+#pragma unroll 1
+                    while (z) {
+                        const int nb = (__ffs(z) - 1) >> 2;   // K block nb >> 1, half nb & 1
+                        z &= z - 1;
+                        const unsigned tnib = (jt >> (4 * nb)) & 0xFu, bnib = (jb >> (4 * nb)) & 0xFu;
+                        const char *ap = sA + (nb >> 1) * A_SUB_BYTES + (((nb & 1) << 4) ^ swoff);
+                        const char *bp = sB + nb * (4 * B_ROW_BYTES);
+                        if ((tnib & bnib) == 0xFu) dense_nibble(acc, ap, bp);
+                        else sparse_nibble(acc, ap, bp, tnib, bnib);
+                    }
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * slot);
                 if (++slot == p.stages) {
@@ -385,10 +435,10 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
             if (lane == 0) mbar_arrive(mempty0 + 8 * buf);
 
             // epilogue: C is overwritten (beta = 0)
-            const int row0 = tm * TILE_M + wm * 32 + lm;
+            const int row0 = tm * TILE_M + wm * 64 + lm;
             const int col0 = tn * TILE_N + wn * 32 + ln * 4;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
+            for (int i = 0; i < 8; ++i) {
                 const int row = row0 + 8 * i;
                 if (row < p.M) {
                     float *c = p.C + (size_t)row * p.N + col0;
@@ -403,55 +453,9 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
 
     if (!ok && lane == 0) atomicExch(p.status, (int)ESMM_ERR_TIMEOUT);
 }
-
 // ---------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *,
-                                  const cuuint64_t *, const cuuint64_t *, const cuuint32_t *,
-                                  const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn()
-{
-    static EncodeTiledFn fn = nullptr;
-    if (!fn) {
-        void *ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    }
-    return fn;
-}
-
-// Row-major FP32 matrix of `outer` rows x `inner` columns, box = box_outer x box_inner.
-static int make_map_2d(CUtensorMap *map, const void *base, uint64_t inner, uint64_t outer,
-                       uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz,
-                       CUtensorMapL2promotion l2)
-{
-    EncodeTiledFn enc = encode_tiled_fn();
-    if (!enc) return record_cuda_error_text("cuTensorMapEncodeTiled entry point not available");
-    cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {inner * 4};
-    cuuint32_t box[2] = {box_inner, box_outer};
-    cuuint32_t estr[2] = {1, 1};
-    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void *>(base), dims, strides,
-                     box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz, l2, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) {
-        char buf[96];
-        snprintf(buf, sizeof buf, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-        return record_cuda_error_text(buf);
-    }
-    return ESMM_OK;
-}
-
-static int env_int(const char *name, int dflt)
-{
-    const char *s = getenv(name);
-    return (s && *s) ? atoi(s) : dflt;
-}
-
 int gemm_ab_launch(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
                    const uint8_t *d_a_pat, const uint8_t *d_b_pat, int a_tile_m, cudaStream_t stream)
 {
@@ -497,13 +501,13 @@ int gemm_ab_launch(int M, int N, int K, const float *d_A, const float *d_B, floa
     p.status = device_status_ptr();
     if (!p.status) return ESMM_ERR_CUDA;
 
+    // Boxes keep the full tile shape on every matrix: elements outside the matrix are
+    // zero-filled by the copy engine and still counted in the stage's byte total.
     CUtensorMap map_a, map_b_box, map_b_row;
     int st = make_map_2d(&map_a, d_A, (uint64_t)K, (uint64_t)M, BK, TILE_M,
                          p.swizzle ? CU_TENSOR_MAP_SWIZZLE_32B : CU_TENSOR_MAP_SWIZZLE_NONE,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
     if (st) return st;
-    // Boxes keep the full tile shape on every matrix: elements outside the matrix are
-    // zero-filled by the copy engine and still counted in the stage's byte total.
     st = make_map_2d(&map_b_box, d_B, (uint64_t)N, (uint64_t)K, TILE_N, BK, CU_TENSOR_MAP_SWIZZLE_NONE,
                      CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (st) return st;

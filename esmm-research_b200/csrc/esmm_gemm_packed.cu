@@ -1,0 +1,534 @@
+// Joint-sparse FP32 SGEMM for sm_100a on the packed (k-major) copy of A.
+//
+// Same arithmetic as esmm_ab_optimized_v3 of the reference
+// (src/kernels/esmm_ab_optimized_v3.cu:18-235): for every output one FFMA chain in ascending
+// k over the k whose joint bit (A pattern of its 32-row block AND B pattern of its 32-column
+// block) is set; C is overwritten.  What differs is where the skipping happens.
+//
+// A comes from the packing preprocessor as [128-row tile][k][128 rows]; B is the caller's
+// row-major matrix, i.e. [k][N].  So one k of a 128 x 128 tile of C needs one 512-byte row
+// of each operand, and the pipeline moves exactly such rows:
+//
+//   * a mask warp walks the tile's K blocks one tile ahead and appends, for every K block,
+//     the k rows that are live for the tile as a whole (the OR over its four 32-row blocks
+//     AND the OR over its four 32-column blocks) to a row list, with one byte per row saying
+//     for which row blocks and which column blocks the row is live.  K blocks with more
+//     than `brow_bits` live k are appended whole (8 rows), so that they can be fetched as
+//     one box;
+//   * a TMA warp cuts the row list into stages of 32 rows and fetches each stage's rows into
+//     a ring slot ([32][512 B] of A, [32][512 B] of B), guarded by full / empty mbarriers.
+//     Both operands are also described to the copy engine as 3-D tensors (column, k % 8,
+//     k / 8), so a stage whose rows are "the same c consecutive k offsets of 32 / c
+//     consecutive K blocks" (c = 1, 2, 4, 8: what uniform patterns such as 10000000,
+//     11000000, 11110000 and 11111111 produce) is ONE box per operand, landing in ascending
+//     k.  Other stages are fetched K block by K block (8-row boxes) and row by row, every
+//     lane issuing its own row.  A k that is dead for the whole tile costs neither a copy
+//     nor shared memory nor a slot in any loop;
+//   * 8 consumer warps own 64 rows x 32 columns of the tile each (two A pattern rows, one B
+//     pattern row; a thread holds 8 x 8 outputs, 4 rows in each 32-row block).  Per stage a
+//     warp forms its two 32-bit joint masks with two ballots.  If every row of the stage is
+//     live for both row blocks - always the case for uniform patterns, at any density - it
+//     runs straight-line code (4 sixteen-byte loads and 64 FFMA per k).  Otherwise it walks
+//     the indices of its live rows, two at a time, loading the next pair under the
+//     multiply-adds of the current one.
+//
+// Lanes are laid out so that every group of 4 consecutive lanes touches 2 row chunks x 2
+// column chunks: on this GPU a 16-byte shared load costs 2 wavefronts when each such group
+// reads at most 32 distinct bytes and 4 otherwise.
+//
+// Every wait is bounded; a wait that expires raises the device status word and the CTA
+// leaves after waiting (bounded again) for its copies in flight.
+#include <cstring>
+
+#include "esmm_gemm_shared.cuh"
+
+namespace esmm {
+
+constexpr int ROW_BYTES = TILE_N * 4;            // 512: one k of an operand tile
+constexpr int ROWS_PER_STAGE = 32;
+constexpr int STAGE_HALF_BYTES = ROWS_PER_STAGE * ROW_BYTES;   // 16384: A rows, then B rows
+constexpr int PSTAGE_BYTES = 2 * STAGE_HALF_BYTES;             // 32768
+constexpr int P_CONSUMER_WARPS = 8;
+constexpr int P_TMA_WARP = P_CONSUMER_WARPS;
+constexpr int P_MASK_WARP = P_CONSUMER_WARPS + 1;
+constexpr int P_THREADS = (P_CONSUMER_WARPS + 2) * 32;         // 320
+constexpr int P_MAX_STAGES = 6;
+
+struct PackedParams {
+    int M, N, K;
+    int nKB;         // ceil(K / 8)
+    int kp;          // rows of the packed A matrix per 128-row tile (nKB * 8)
+    int cap;         // capacity of a tile's row list (multiple of 32)
+    int a_rows;      // rows of the A pattern array (ceil(M / 32))
+    int b_rows;      // rows of the B pattern array (ceil(N / 32))
+    int tiles_m, tiles_n, num_tiles;
+    int stages;
+    int brow_bits;   // K blocks with more live k than this are fetched whole
+    int b_runs_ok;   // K % 8 == 0: the 3-D view of B stays inside the matrix
+    const uint8_t *a_pat;
+    const uint8_t *b_pat;
+    float *C;
+    int *status;
+};
+
+// Tensor maps of one launch.  *_row / *_kb: 2-D, 1 and 8 rows of 128 columns.  *_run[i]: 3-D
+// (column, k % 8, k / 8) boxes of 128 x c x 32/c with c = 1 << i.
+struct PackedMaps {
+    CUtensorMap a_row, a_kb, a_run[4];
+    CUtensorMap b_row, b_kb, b_run[4];
+};
+
+struct PackedSmem {
+    uint32_t stage_off, krow_off, krow_stride, rmask_off, rmask_stride, wlist_off, bar_off, misc_off, total;
+};
+
+__host__ __device__ inline PackedSmem packed_smem_layout(int stages, int cap)
+{
+    PackedSmem L;
+    uint32_t o = 0;
+    L.stage_off = o;
+    o += (uint32_t)stages * PSTAGE_BYTES;
+    L.krow_off = o;   // two buffers: k index of every listed row
+    L.krow_stride = (uint32_t)cap * 2;
+    o += 2 * L.krow_stride;
+    L.rmask_off = o;  // two buffers: per row, bits 0-3 live row blocks, bits 4-7 live column blocks
+    L.rmask_stride = (uint32_t)cap;
+    o += 2 * L.rmask_stride;
+    o = (o + 15u) & ~15u;
+    L.wlist_off = o;  // per consumer warp: indices of its live rows of the current stage
+    o += P_CONSUMER_WARPS * 32;
+    L.bar_off = o;    // full[P_MAX_STAGES], empty[P_MAX_STAGES], list_full[2], list_empty[2]
+    o += (2 * P_MAX_STAGES + 4) * 8;
+    L.misc_off = o;   // nrows[2], abort
+    o += 16;
+    L.total = o;
+    return L;
+}
+
+// One k of the tile for one thread: its 4 rows of the top block, 4 rows of the bottom block
+// and 2 x 4 columns are one 16-byte load each.
+struct KFrag {
+    float4 at, ab, b0, b1;
+};
+
+__device__ __forceinline__ KFrag load_kfrag(const char *pa, const char *pb)
+{
+    KFrag f;
+    f.at = *reinterpret_cast<const float4 *>(pa);
+    f.ab = *reinterpret_cast<const float4 *>(pa + 128);
+    f.b0 = *reinterpret_cast<const float4 *>(pb);
+    f.b1 = *reinterpret_cast<const float4 *>(pb + 64);
+    return f;
+}
+
+__device__ __forceinline__ void fma_top(float (&acc)[8][8], const KFrag &f)
+{
+    fma8(acc[0], f.at.x, f.b0, f.b1);
+    fma8(acc[1], f.at.y, f.b0, f.b1);
+    fma8(acc[2], f.at.z, f.b0, f.b1);
+    fma8(acc[3], f.at.w, f.b0, f.b1);
+}
+
+__device__ __forceinline__ void fma_bottom(float (&acc)[8][8], const KFrag &f)
+{
+    fma8(acc[4], f.ab.x, f.b0, f.b1);
+    fma8(acc[5], f.ab.y, f.b0, f.b1);
+    fma8(acc[6], f.ab.z, f.b0, f.b1);
+    fma8(acc[7], f.ab.w, f.b0, f.b1);
+}
+
+// A stage whose 32 rows are all live for both row blocks: 8 rows of straight-line code per
+// loop trip, so that the compiler can issue the loads of a row under the multiply-adds of
+// the row before.
+__device__ __forceinline__ void dense_rows(float (&acc)[8][8], const char *sA, const char *sB)
+{
+#pragma unroll 1
+    for (int r0 = 0; r0 < ROWS_PER_STAGE; r0 += 8) {
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const KFrag f = load_kfrag(sA + (r0 + r) * ROW_BYTES, sB + (r0 + r) * ROW_BYTES);
+            fma_top(acc, f);
+            fma_bottom(acc, f);
+        }
+    }
+}
+
+__device__ __forceinline__ void fma_masked(float (&acc)[8][8], const KFrag &f, unsigned jt, unsigned jb, int row)
+{
+    if ((jt >> row) & 1u) fma_top(acc, f);
+    if ((jb >> row) & 1u) fma_bottom(acc, f);
+}
+
+// Any other stage: `list` holds the indices (one byte each, ascending) of the `cnt` rows that
+// are live for at least one of the warp's two row blocks.  Two rows per step, the next pair
+// loaded before the current pair is multiplied.
+__device__ __forceinline__ void listed_rows(float (&acc)[8][8], const char *sA, const char *sB, unsigned jt,
+                                            unsigned jb, const unsigned *list, int cnt)
+{
+    if (cnt == 0) return;
+    const int first = (int)(list[0] & 0xFFu);
+    auto row_at = [&](int i) -> int {
+        // index of the i-th listed row, or the first one past the end (loaded, never multiplied)
+        return i < cnt ? (int)((list[i >> 2] >> (8 * (i & 3))) & 0xFFu) : first;
+    };
+    int r0 = first, r1 = row_at(1);
+    KFrag f0 = load_kfrag(sA + (r0 << 9), sB + (r0 << 9));
+    KFrag f1 = load_kfrag(sA + (r1 << 9), sB + (r1 << 9));
+#pragma unroll 1
+    for (int i = 0; i < cnt; i += 4) {
+        const int r2 = row_at(i + 2), r3 = row_at(i + 3);
+        const KFrag g0 = load_kfrag(sA + (r2 << 9), sB + (r2 << 9));
+        const KFrag g1 = load_kfrag(sA + (r3 << 9), sB + (r3 << 9));
+        fma_masked(acc, f0, jt, jb, r0);
+        if (i + 1 < cnt) fma_masked(acc, f1, jt, jb, r1);
+        r0 = row_at(i + 4);
+        r1 = row_at(i + 5);
+        f0 = load_kfrag(sA + (r0 << 9), sB + (r0 << 9));
+        f1 = load_kfrag(sA + (r1 << 9), sB + (r1 << 9));
+        if (i + 2 < cnt) fma_masked(acc, g0, jt, jb, r2);
+        if (i + 3 < cnt) fma_masked(acc, g1, jt, jb, r3);
+    }
+}
+
+__global__ void __launch_bounds__(P_THREADS, 1)
+esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const PackedParams p)
+{
+    extern __shared__ __align__(1024) char smem[];
+    const PackedSmem L = packed_smem_layout(p.stages, p.cap);
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + L.bar_off);
+    const uint32_t full0 = smem_u32(bars);
+    const uint32_t empty0 = smem_u32(bars + P_MAX_STAGES);
+    const uint32_t lfull0 = smem_u32(bars + 2 * P_MAX_STAGES);
+    const uint32_t lempty0 = smem_u32(bars + 2 * P_MAX_STAGES + 2);
+    volatile int *nrows = reinterpret_cast<volatile int *>(smem + L.misc_off);
+    volatile int *abort_flag = nrows + 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, P_CONSUMER_WARPS);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(lfull0 + 8 * b, 1);
+            mbar_init(lempty0 + 8 * b, P_CONSUMER_WARPS + 1);
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    __syncthreads();
+
+    bool ok = true;
+
+    if (warp == P_MASK_WARP) {
+        // ---------------- mask warp: the tile's list of live k rows ----------------
+        int it = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(lempty0 + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            uint16_t *krow = reinterpret_cast<uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
+            uint8_t *rmask = reinterpret_cast<uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
+            int pos = 0;
+            for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
+                const int kb = kb0 + lane;
+                unsigned aw = 0, bw = 0;  // byte i: pattern of the tile's i-th 32-row / 32-column block
+                if (kb < p.nKB) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int mb = tm * 4 + i, nb = tn * 4 + i;
+                        if (mb < p.a_rows) aw |= (unsigned)p.a_pat[(size_t)mb * p.nKB + kb] << (8 * i);
+                        if (nb < p.b_rows) bw |= (unsigned)p.b_pat[(size_t)nb * p.nKB + kb] << (8 * i);
+                    }
+                }
+                unsigned au = aw | (aw >> 16), bu = bw | (bw >> 16);
+                au = (au | (au >> 8)) & 0xFFu;
+                bu = (bu | (bu >> 8)) & 0xFFu;
+                const unsigned live = au & bu;                       // k live for the tile as a whole
+                unsigned rows = __popc(live) > p.brow_bits ? 0xFFu : live;  // k rows to list
+                if (live == 0u) rows = 0u;
+                const int c = __popc(rows);
+                int incl = c;                                        // inclusive scan over the lanes
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
+                    if (lane >= d) incl += v;
+                }
+                int q = pos + incl - c;
+                while (rows) {
+                    const int kk = __ffs(rows) - 1;
+                    rows &= rows - 1;
+                    const unsigned as = aw >> kk, bs = bw >> kk;
+                    const unsigned abits = (as & 1u) | ((as >> 7) & 2u) | ((as >> 14) & 4u) | ((as >> 21) & 8u);
+                    const unsigned bbits = (bs & 1u) | ((bs >> 7) & 2u) | ((bs >> 14) & 4u) | ((bs >> 21) & 8u);
+                    krow[q] = (uint16_t)(kb * BK + kk);
+                    rmask[q] = (uint8_t)(abits | (bbits << 4));
+                    ++q;
+                }
+                pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
+            }
+            // rows past the end of the last stage read as dead
+            {
+                const int q = pos + lane;
+                if (q < ((pos + 31) & ~31)) {
+                    krow[q] = 0;
+                    rmask[q] = 0;
+                }
+            }
+            if (lane == 0) nrows[buf] = pos;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
+        }
+    } else if (warp == P_TMA_WARP) {
+        // ---------------- TMA warp: one lane per row of the stage ----------------
+        if (lane < 12) tma_prefetch_descriptor(&maps.a_row + lane);
+        int slot = 0;
+        uint32_t phase = 0;
+        uint32_t issued_bits = 0, parity_bits = 0;  // per slot: ever issued / parity of last issue
+        int it = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const uint16_t *krow = reinterpret_cast<const uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
+            const int n = nrows[buf];
+            const int a_row0 = tm * p.kp, b_col0 = tn * TILE_N;
+            for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
+                const int cnt = min(ROWS_PER_STAGE, n - r0);
+                const bool valid = lane < cnt;
+                const int k = valid ? (int)krow[r0 + lane] : -1;
+                // a uniform run?  rows = k offsets kk0 .. kk0 + c - 1 of 32 / c consecutive K blocks
+                const int k_first = __shfl_sync(0xFFFFFFFFu, k, 0);
+                const int kb0 = k_first >> 3, kk0 = k_first & 7;
+                int run = -1;  // log2(c)
+                if (cnt == ROWS_PER_STAGE && p.b_runs_ok) {
+#pragma unroll
+                    for (int lc = 3; lc >= 0; --lc) {
+                        const int c = 1 << lc;
+                        const int expect = ((kb0 + (lane >> lc)) << 3) + kk0 + (lane & (c - 1));
+                        if (run < 0 && kk0 + c <= BK && __all_sync(0xFFFFFFFFu, k == expect)) run = lc;
+                    }
+                }
+                // otherwise: rows lane .. lane + 7 are the 8 k of one K block?  (the list is ascending)
+                const int k7 = __shfl_down_sync(0xFFFFFFFFu, k, 7);
+                const bool lead8 = valid && (k & 7) == 0 && lane + 7 < cnt && k7 == k + 7;
+                const unsigned lead_mask = __ballot_sync(0xFFFFFFFFu, lead8);
+                unsigned cover = lead_mask | (lead_mask << 1);
+                cover |= cover << 2;
+                cover |= cover << 4;                                  // rows fetched by some 8-row box
+                ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                const uint32_t full = full0 + 8 * slot;
+                if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * 2u * ROW_BYTES);
+                __syncwarp();
+                const uint32_t sa = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES + lane * ROW_BYTES;
+                const uint32_t sb = sa + STAGE_HALF_BYTES;
+                if (run >= 0) {
+                    if (lane == 0) {
+                        tma_load_3d(sa, &maps.a_run[run], 0, kk0, tm * p.nKB + kb0, full);
+                        tma_load_3d(sb, &maps.b_run[run], b_col0, kk0, kb0, full);
+                    }
+                } else if (lead8) {
+                    tma_load_2d(sa, &maps.a_kb, 0, a_row0 + k, full);
+                    tma_load_2d(sb, &maps.b_kb, b_col0, k, full);
+                } else if (valid && !((cover >> lane) & 1u)) {
+                    tma_load_2d(sa, &maps.a_row, 0, a_row0 + k, full);
+                    tma_load_2d(sb, &maps.b_row, b_col0, k, full);
+                }
+                issued_bits |= 1u << slot;
+                parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
+                if (++slot == p.stages) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+        }
+        if (!ok && lane == 0) {
+            // leave only after the copies already issued have landed (bounded)
+            for (int s = 0; s < p.stages; ++s) {
+                if (!(issued_bits & (1u << s))) continue;
+                const uint32_t par = (parity_bits >> s) & 1u;
+                for (int tries = 0; tries < (1 << 16); ++tries)
+                    if (mbar_try_wait(full0 + 8 * s, par)) break;
+            }
+        }
+    } else {
+        // ---------------- consumer warps: 64 rows x 32 columns of the tile each ----------------
+        const int wm = warp >> 2, wn = warp & 3;              // 2 x 4 warps
+        const int lm = (lane >> 1) & 7;                       // group of 4 rows within a 32-row block
+        const int ln = (lane & 1) | ((lane >> 4) << 1);       // 16-byte column chunk
+        const uint32_t a_thr = (uint32_t)(wm * 64 + lm * 4) * 4;                      // within a row of A
+        const uint32_t b_thr = STAGE_HALF_BYTES + (uint32_t)(wn * 32 + ln * 4) * 4;  // within a row of B
+        const int t_shift = 2 * wm, b_shift = 4 + wn;
+        unsigned *wlist = reinterpret_cast<unsigned *>(smem + L.wlist_off) + warp * 8;  // 32 bytes per warp
+        int slot = 0;
+        uint32_t phase = 0;
+        int it = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const uint8_t *rmask = reinterpret_cast<const uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
+            const int n = nrows[buf];
+
+            float acc[8][8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+
+            for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
+                // joint masks of the stage: bit r = row r is live for (top | bottom) block x my columns
+                const unsigned rm = rmask[r0 + lane];
+                const unsigned colb = (rm >> b_shift) & 1u;
+                const unsigned jt = __ballot_sync(0xFFFFFFFFu, ((rm >> t_shift) & colb) != 0u);
+                const unsigned jb = __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u);
+                const bool dense = (jt & jb) == 0xFFFFFFFFu;
+                int live_cnt = 0;
+                if (!dense) {
+                    // indices of my live rows, written by the lanes in parallel while the stage's
+                    // data may still be in flight
+                    const unsigned u = jt | jb;
+                    live_cnt = __popc(u);
+                    if ((u >> lane) & 1u)
+                        reinterpret_cast<uint8_t *>(wlist)[__popc(u & ((1u << lane) - 1u))] = (uint8_t)lane;
+                    __syncwarp();
+                }
+                ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
+                if (!ok) break;
+                const char *sA = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + a_thr;
+                const char *sB = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + b_thr;
+                if (dense) dense_rows(acc, sA, sB);
+                else listed_rows(acc, sA, sB, jt, jb, wlist, live_cnt);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * slot);
+                if (++slot == p.stages) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+
+            // epilogue: C is overwritten (beta = 0)
+            const int row0 = tm * TILE_M + wm * 64 + lm * 4;
+            const int col0 = tn * TILE_N + wn * 32 + ln * 4;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int row = row0 + (i & 3) + 32 * (i >> 2);
+                if (row < p.M) {
+                    float *c = p.C + (size_t)row * p.N + col0;
+                    if (col0 < p.N)
+                        *reinterpret_cast<float4 *>(c) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+                    if (col0 + 16 < p.N)
+                        *reinterpret_cast<float4 *>(c + 16) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+                }
+            }
+        }
+    }
+
+    if (!ok && lane == 0) atomicExch(p.status, (int)ESMM_ERR_TIMEOUT);
+}
+
+int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                          const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream)
+{
+    if (!d_a_packed || !d_B || !d_C || !d_a_pat || !d_b_pat) return ESMM_ERR_NULL;
+    if (M <= 0 || N <= 0 || K <= 0 || (K & 3) || (N & 3)) return ESMM_ERR_SHAPE;
+    if (((uintptr_t)d_a_packed | (uintptr_t)d_B | (uintptr_t)d_C) & 15) return ESMM_ERR_ALIGN;
+
+    PackedParams p;
+    memset(&p, 0, sizeof p);
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.nKB = ceil_div(K, BK);
+    p.kp = p.nKB * BK;
+    if (p.kp > 65535) return ESMM_ERR_TOO_LARGE;  // row list entries are 16-bit k indices
+    p.cap = ((p.kp + 31) & ~31) + 32;
+    p.a_rows = ceil_div(M, 32);
+    p.b_rows = ceil_div(N, PAT_N);
+    p.tiles_m = ceil_div(M, TILE_M);
+    p.tiles_n = ceil_div(N, TILE_N);
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.brow_bits = env_int("ESMM_BROW_BITS", 7);
+    if (p.brow_bits < 0) p.brow_bits = 0;
+    if (p.brow_bits > 8) p.brow_bits = 8;
+    p.a_pat = d_a_pat;
+    p.b_pat = d_b_pat;
+    p.C = d_C;
+
+    int stages = env_int("ESMM_STAGES", P_MAX_STAGES);
+    if (stages > P_MAX_STAGES) stages = P_MAX_STAGES;
+    if (stages < 2) stages = 2;
+    while (stages > 2 && packed_smem_layout(stages, p.cap).total > SMEM_LIMIT) --stages;
+    const PackedSmem L = packed_smem_layout(stages, p.cap);
+    if (L.total > SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
+    p.stages = stages;
+
+    int dev = 0, sms = 0;
+    ESMM_CUDA_TRY(cudaGetDevice(&dev));
+    ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    p.status = device_status_ptr();
+    if (!p.status) return ESMM_ERR_CUDA;
+
+    // Packed A is a matrix of 128 columns and tiles_m * kp rows; B is K rows of N columns.  Rows
+    // (or columns of B) outside the matrices are zero-filled by the copy engine and still counted
+    // in the stage's byte total.  The 3-D views split the row index into (k % 8, k / 8); for B
+    // that is only valid when K is a multiple of 8 (otherwise the view would reach past row K).
+    p.b_runs_ok = (K % BK) == 0;
+    PackedMaps maps;
+    const uint64_t a_rows_total = (uint64_t)p.tiles_m * p.kp;
+    int st = make_map_2d(&maps.a_row, d_a_packed, TILE_M, a_rows_total, TILE_M, 1, CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (!st) st = make_map_2d(&maps.a_kb, d_a_packed, TILE_M, a_rows_total, TILE_M, BK, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (!st) st = make_map_2d(&maps.b_row, d_B, (uint64_t)N, (uint64_t)K, TILE_N, 1, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    if (!st) st = make_map_2d(&maps.b_kb, d_B, (uint64_t)N, (uint64_t)K, TILE_N, BK, CU_TENSOR_MAP_SWIZZLE_NONE,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    for (int i = 0; i < 4 && !st; ++i) {
+        const uint32_t c = 1u << i;
+        st = make_map_3d(&maps.a_run[i], d_a_packed, TILE_M, BK, (uint64_t)p.tiles_m * p.nKB, (uint64_t)TILE_M * 4,
+                         (uint64_t)TILE_M * 4 * BK, TILE_M, c, ROWS_PER_STAGE / c);
+        if (!st) {
+            if (p.b_runs_ok)
+                st = make_map_3d(&maps.b_run[i], d_B, (uint64_t)N, BK, (uint64_t)p.nKB, (uint64_t)N * 4,
+                                 (uint64_t)N * 4 * BK, TILE_N, c, ROWS_PER_STAGE / c);
+            else
+                maps.b_run[i] = maps.b_row;  // never used
+        }
+    }
+    if (st) return st;
+
+    ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)L.total));
+    int grid = env_int("ESMM_GRID", sms);
+    if (grid > p.num_tiles) grid = p.num_tiles;
+    if (grid < 1) grid = 1;
+    esmm_joint_sgemm_packed_kernel<<<grid, P_THREADS, L.total, stream>>>(maps, p);
+    ESMM_CUDA_TRY(cudaGetLastError());
+    return ESMM_OK;
+}
+
+}  // namespace esmm
+
+extern "C" int esmm_gemm_ab_packed(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                                   const uint8_t *d_a_pat, const uint8_t *d_b_pat, void *stream)
+{
+    return esmm::gemm_ab_packed_launch(M, N, K, d_a_packed, d_B, d_C, d_a_pat, d_b_pat, (cudaStream_t)stream);
+}

@@ -60,6 +60,72 @@ esmm_preprocess_a_patterns_kernel(const float *__restrict__ A, int M, int K, int
     }
 }
 
+// Pattern scan fused with the re-layout the packed GEMM variant reads: besides the pattern
+// bytes the warp writes its 32 rows x 128 columns transposed into
+//   packed[((tile * nKB + kb) * 8 + k) * 128 + row_in_tile],   tile = row / 128,
+// i.e. k-major rows of 128 floats per 128-row tile, so that one K block of a tile is 4 KB of
+// contiguous memory.  The transpose goes through a skewed shared-memory tile (conflict-free
+// both ways).  A k whose pattern bit is clear for the warp's 32-row block is not written: the
+// GEMM never multiplies it, so whatever the buffer holds there is harmless.
+constexpr int PACK_WARPS = 4;
+constexpr int PACK_SMEM_PER_WARP = 128 * 32 * 4;  // 16 KB
+
+__global__ void __launch_bounds__(PACK_WARPS * 32)
+esmm_preprocess_a_pack_kernel(const float *__restrict__ A, int M, int K, int nMB, int nKB, int k_chunks,
+                              uint8_t *__restrict__ out, float *__restrict__ packed)
+{
+    extern __shared__ __align__(16) float pack_smem[];
+    float *tile = pack_smem + (threadIdx.x >> 5) * (PACK_SMEM_PER_WARP / 4);
+    const int lane = threadIdx.x & 31;
+    const long warps_total = (long)gridDim.x * PACK_WARPS;
+    const long tasks = (long)nMB * k_chunks;
+    for (long task = (long)blockIdx.x * PACK_WARPS + (threadIdx.x >> 5); task < tasks; task += warps_total) {
+        const int mb = (int)(task / k_chunks);
+        const int kc = (int)(task - (long)mb * k_chunks);
+        const int col = kc * 128 + lane * 4;
+        const bool col_ok = col < K;
+        const int row0 = mb * 32;
+        const float *src = A + (size_t)row0 * K + col;
+        unsigned nib = 0;
+#pragma unroll
+        for (int r0 = 0; r0 < 32; r0 += 8) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (col_ok && row0 + r0 + u < M) v[u] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)(r0 + u) * K));
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                nib |= nz4(v[u]);
+                const int r = r0 + u;
+                // element (r, c) lives at c * 32 + ((r + (c >> 2)) & 31); here c >> 2 == lane
+                const int pos = (r + lane) & 31;
+                tile[(lane * 4 + 0) * 32 + pos] = v[u].x;
+                tile[(lane * 4 + 1) * 32 + pos] = v[u].y;
+                tile[(lane * 4 + 2) * 32 + pos] = v[u].z;
+                tile[(lane * 4 + 3) * 32 + pos] = v[u].w;
+            }
+        }
+        // live columns of the chunk: bit l of liveq[q] says column 4 l + q has a nonzero
+        unsigned liveq[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) liveq[q] = __ballot_sync(0xFFFFFFFFu, (nib >> q) & 1u);
+        const unsigned other = __shfl_xor_sync(0xFFFFFFFFu, nib, 1);
+        const int kb_lane = kc * 16 + (lane >> 1);
+        if (!(lane & 1) && kb_lane < nKB) out[(size_t)mb * nKB + kb_lane] = (uint8_t)(nib | (other << 4));
+        __syncwarp();
+        float *dst = packed + (size_t)(mb >> 2) * nKB * BK * 128 + (mb & 3) * 32 + lane;
+#pragma unroll 8
+        for (int c = 0; c < 128; ++c) {
+            const int k = kc * 128 + c;  // global k = kb * 8 + kk
+            if (((liveq[c & 3] >> (c >> 2)) & 1u) && k < nKB * BK)
+                dst[(size_t)k * 128] = tile[c * 32 + ((lane + (c >> 2)) & 31)];
+        }
+        __syncwarp();
+    }
+}
+
 // Any K, any alignment: one thread per pattern byte.  Only used when the fast kernel's
 // alignment conditions do not hold.
 __global__ void esmm_preprocess_a_patterns_generic_kernel(const float *__restrict__ A, int M, int K,
@@ -175,6 +241,34 @@ int preprocess_a_launch(const float *d_A, int M, int K, int tile_m, uint8_t *d_o
     return ESMM_OK;
 }
 
+int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, float *d_packed,
+                             cudaStream_t stream)
+{
+    if (!d_A || !d_out || !d_packed) return ESMM_ERR_NULL;
+    if (M <= 0 || K <= 0 || (K & 3)) return ESMM_ERR_SHAPE;
+    if (((uintptr_t)d_A | (uintptr_t)d_packed) & 15) return ESMM_ERR_ALIGN;
+    const int nMB = ceil_div(M, 32), nKB = ceil_div(K, BK), k_chunks = ceil_div(K, 128);
+    const long tasks = (long)nMB * k_chunks;
+    const int sms = sm_count();
+    if (sms <= 0) return record_cuda_error_text("no CUDA device");
+    static bool attr_set[64] = {false};
+    int dev = 0;
+    ESMM_CUDA_TRY(cudaGetDevice(&dev));
+    const int smem = PACK_WARPS * PACK_SMEM_PER_WARP;
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_preprocess_a_pack_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_set[dev] = true;
+    }
+    long blocks = (tasks + PACK_WARPS - 1) / PACK_WARPS;
+    const long cap = (long)sms * 3 * 8;
+    if (blocks > cap) blocks = cap;
+    esmm_preprocess_a_pack_kernel<<<(unsigned)blocks, PACK_WARPS * 32, smem, stream>>>(
+        d_A, M, K, nMB, nKB, k_chunks, d_out, d_packed);
+    ESMM_CUDA_TRY(cudaGetLastError());
+    return ESMM_OK;
+}
+
 int preprocess_b_launch(const float *d_B, int K, int N, uint8_t *d_out, cudaStream_t stream)
 {
     if (!d_B || !d_out) return ESMM_ERR_NULL;
@@ -220,6 +314,17 @@ size_t esmm_b_pattern_bytes(int K, int N)
 int esmm_preprocess_a(const float *d_A, int M, int K, int tile_m, uint8_t *d_out, void *stream)
 {
     return esmm::preprocess_a_launch(d_A, M, K, tile_m, d_out, (cudaStream_t)stream);
+}
+
+size_t esmm_a_packed_bytes(int M, int K)
+{
+    if (M <= 0 || K <= 0) return 0;
+    return (size_t)esmm::ceil_div(M, 128) * 128 * (size_t)esmm::ceil_div(K, esmm::BK) * esmm::BK * sizeof(float);
+}
+
+int esmm_preprocess_a_packed(const float *d_A, int M, int K, uint8_t *d_out, float *d_packed, void *stream)
+{
+    return esmm::preprocess_a_pack_launch(d_A, M, K, d_out, d_packed, (cudaStream_t)stream);
 }
 
 int esmm_preprocess_b(const float *d_B, int K, int N, uint8_t *d_out, void *stream)

@@ -133,12 +133,31 @@ int esmm_gemm_ab(int M, int N, int K, const float *d_A, const float *d_B, float 
                  const uint8_t *d_a_pat, const uint8_t *d_b_pat, int a_tile_m, void *stream);
 
 /*
- * The per-call path with B patterns cached: A patterns (32-row blocks) are
- * computed into d_a_pat_scratch (esmm_a_pattern_bytes(M, K, 32) bytes, caller
- * owned), then the GEMM runs, both on `stream`.
+ * Packing variant of the A preprocessor: one pass over A writes the 32-row pattern
+ * bytes (same bytes as esmm_preprocess_a with tile_m = 32) and a k-major copy of A,
+ *   packed[((row / 128) * nKB * 8 + k) * 128 + row % 128],
+ * esmm_a_packed_bytes(M, K) bytes, which esmm_gemm_ab_packed reads instead of A.
+ * Entries whose pattern bit is clear are left unwritten (they are never multiplied).
+ * Needs K % 4 == 0 and 16-byte aligned pointers.  No counterpart in the reference,
+ * whose kernel transposes A tiles in shared memory on every K step
+ * (src/kernels/esmm_ab_optimized_v3.cu:126-132).
  */
+size_t esmm_a_packed_bytes(int M, int K);
+int esmm_preprocess_a_packed(const float *d_A, int M, int K, uint8_t *d_out, float *d_packed,
+                             void *stream);
+/* Same contract as esmm_gemm_ab (32-row A patterns) with the packed copy in place of A. */
+int esmm_gemm_ab_packed(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                        const uint8_t *d_a_pat, const uint8_t *d_b_pat, void *stream);
+
+/*
+ * The per-call path with B patterns cached ("B offline, A per call"): the packing
+ * preprocessor and the packed GEMM, both on `stream`.  d_workspace is caller-owned
+ * device memory of esmm_sgemm_joint_workspace_bytes(M, K) bytes, 256-byte aligned
+ * (A patterns followed by the packed copy); nothing is allocated here.
+ */
+size_t esmm_sgemm_joint_workspace_bytes(int M, int K);
 int esmm_sgemm_joint(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
-                     const uint8_t *d_b_pat, uint8_t *d_a_pat_scratch, void *stream);
+                     const uint8_t *d_b_pat, void *d_workspace, void *stream);
 
 /* Synchronises `stream`, returns and clears the device status word:
  * ESMM_OK, ESMM_ERR_TIMEOUT (a bounded wait expired) or ESMM_ERR_CUDA. */
