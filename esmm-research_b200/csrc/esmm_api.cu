@@ -743,6 +743,7 @@ int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, f
         ok = verify_results_host(h_C, h_C_ref, (long)rows * cols, 1e-2f, cols);
     }
     if (passed) *passed = ok ? 1 : 0;
+    fflush(stdout);
     return ok ? ESMM_OK : ESMM_ERR_VERIFY;
 }
 
