@@ -1,0 +1,417 @@
+#!/usr/bin/env python
+"""Benchmark of the joint-sparse SGEMM hot path (A-pattern preprocess + GEMM) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c5]
+
+One JSON line on stdout (rank 0).  Metric: dense-equivalent TFLOP/s (2 M N K / t), including the
+per-call A preprocessing, B patterns cached.
+
+N = 1 (default): workload "c2" - M = N = K = 4096 FP32, N(0,1) inputs, uniform blockwise patterns
+  11111111 / 11110000 / 11000000 / 10000000 (100 / 50 / 25 / 12.5 % joint density) applied to A's K
+  columns and B's K rows.  One step = the four densities once, each = packing preprocess of A +
+  GEMM.  `value` is the sweep's aggregate (4 * 2 * 4096^3 flops / step time); the per-density
+  figures, cuBLAS SGEMM on the same inputs and the roofline fractions are in "sweep".
+N > 1 (torchrun, one process per GPU): workload "c5" - M = N = K = 16384, pattern 11000000, B and
+  C column-sharded over the ranks, A and its preprocessing replicated, no data-path collective.
+  `value` = 2 * 16384^3 / (max over ranks of the device time); strong scaling.
+
+--impl reference times the reference's own CPU SGEMM (matrixMultiplyCPU, compiled from the reference
+tree into oracle/_ref, else the oracle's restatement of it) on all host cores over a bounded row
+sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PATTERNS = [("11111111", 0xFF), ("11110000", 0x0F), ("11000000", 0x03), ("10000000", 0x01)]
+NOMINAL_FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12  # 74.4: 148 SMs x 128 lanes x 2 flop x max SM clock
+
+
+def measured_peaks() -> dict:
+    try:
+        return json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except Exception:
+        return {}
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.stop_flag, self.rows = index, threading.Event(), []
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [p.strip() for p in out.strip().split(",")]
+                if len(parts) >= 6:
+                    self.rows.append(parts)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
+
+    def summary(self) -> dict:
+        self.stop_flag.set()
+        self.join(timeout=6)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
+        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
+        reasons = sorted({n for r in self.rows for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.rows)}
+
+
+def host_threads() -> int:
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except Exception:
+        return max(1, os.cpu_count() or 1)
+
+
+# ---------------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the reference's CPU SGEMM on a bounded row sample
+# ---------------------------------------------------------------------------------------------------
+class CpuSgemm:
+    def __init__(self, M: int, N: int, K: int, pattern: int, seed: int = 0):
+        import numpy as np
+        import oracle
+        self.oracle, self.np = oracle, np
+        self.M, self.N, self.K = M, N, K
+        self.threads = host_threads()
+        self.kind = "reference" if oracle.have_ref() else "port"
+        rng = np.random.default_rng(seed)
+        live = np.array([(pattern >> (k & 7)) & 1 for k in range(K)], dtype=np.float32)
+        self.B = rng.standard_normal((K, N), dtype=np.float32) * live[:, None]
+        self.A_rows = None
+        self.live = live
+        self.rng = rng
+
+    def run(self, rows: int) -> float:
+        """Seconds for `rows` rows of C (all N columns), split over all host threads."""
+        np = self.np
+        if self.A_rows is None or self.A_rows.shape[0] != rows:
+            self.A_rows = self.rng.standard_normal((rows, self.K), dtype=np.float32) * self.live[None, :]
+        t0 = time.perf_counter()
+        if self.kind == "reference":
+            self.oracle.ref_sgemm_cpu(self.A_rows, self.B, threads=self.threads)
+        else:
+            self.oracle.sgemm_naive(self.A_rows, self.B, threads=self.threads)
+        return time.perf_counter() - t0
+
+    def calibrate(self, target_s: float) -> int:
+        rows = self.threads
+        dt = self.run(rows)
+        per_row = max(dt / rows, 1e-6)
+        want = int(target_s / per_row)
+        want = max(self.threads, min(want, self.M))
+        return (want // self.threads) * self.threads or self.threads
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    if args.gpus > 1 or args.workload == "c5":
+        M = N = K = 16384
+        wl, pat = "c5: 16384^3 FP32, pattern 11000000 (25% joint density)", 0x03
+    else:
+        M = N = K = 4096
+        wl, pat = "c2: 4096^3 FP32, uniform pattern sweep 100/50/25/12.5% (CPU SGEMM is dense: time is density independent)", 0xFF
+    cpu = CpuSgemm(M, N, K, pat)
+    rows = cpu.calibrate(target_s=2.0 if M <= 4096 else 4.0)
+    for _ in range(args.warmup):
+        cpu.run(rows)
+    t = 0.0
+    for _ in range(args.steps):
+        t += cpu.run(rows)
+    per_step = t / args.steps
+    tflops = 2.0 * rows * N * K / per_step / 1e12
+    sample = f"{rows} of {M} rows of C (all {N} columns, full K) per step; time scales linearly in rows"
+    line = {
+        "impl": "reference", "metric": "dense-equivalent TFLOP/s incl. A-pattern preprocess", "value": tflops,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": per_step * 1e3, "higher_is_better": True, "scaling": "strong" if args.gpus > 1 else "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": wl, "M": M, "N": N, "K": K, "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": cpu.threads, "kind": cpu.kind, "sample": sample},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------------------
+def run_ours(args) -> None:
+    import numpy as np
+    import torch
+    import __graft_entry__ as g
+
+    pkg = g.load_package()  # raises if the CUDA library is missing: there is no fallback
+    L = pkg.lib()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the product path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    import importlib
+    sharding = importlib.import_module("esmm_research_b200.sharding")
+
+    workload = args.workload or ("c5" if world > 1 else "c2")
+    peaks = measured_peaks()
+    ffma_peak, sms = pkg.ffma_peak_tflops()
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    hbm_src = "measured" if "hbm_gbs" in peaks else "fallback"
+
+    def ev():
+        return torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- problem set-up (untimed) ----
+    if workload == "c2":
+        M = N = K = args.size or 4096
+        pats = PATTERNS
+        shard = sharding.shard_columns(N, world, rank) if world > 1 else sharding.ColumnShard(0, 1, N, 0, N)
+    else:
+        M = N = K = args.size or 16384
+        pats = [("11000000", 0x03)]
+        shard = sharding.shard_columns(N, world, rank)
+    Nl = shard.width
+    cases = []
+    for name, pat in pats:
+        A = torch.empty((M, K), device=dev)
+        B = torch.empty((K, Nl), device=dev)
+        pkg.fill_normal(A.data_ptr(), M, K, 0, 1, mode=1, pattern=pat)               # same A on every rank
+        pkg.fill_normal(B.data_ptr(), K, Nl, 1, 1000 + rank, mode=1, pattern=pat)    # this rank's columns
+        bp = torch.empty(L.esmm_b_pattern_bytes(K, Nl), dtype=torch.uint8, device=dev)
+        pkg.preprocess_b(B.data_ptr(), K, Nl, bp.data_ptr())                         # offline: B patterns cached
+        cases.append(dict(name=name, pat=pat, A=A, B=B, bp=bp))
+    Cd = torch.empty((M, Nl), device=dev)
+    ws = torch.empty(pkg.sgemm_joint_workspace_bytes(M, K), dtype=torch.uint8, device=dev)
+    ap_bytes = int(L.esmm_a_pattern_bytes(M, K, 32))
+    ap_region = (ap_bytes + 255) & ~255
+    flops_dense = 2.0 * M * N * K           # whole job, per density
+    flops_dense_local = 2.0 * M * Nl * K
+    torch.cuda.synchronize()
+
+    def step():
+        for c in cases:
+            pkg.sgemm_joint(M, Nl, K, c["A"].data_ptr(), c["B"].data_ptr(), Cd.data_ptr(), c["bp"].data_ptr(),
+                            ws.data_ptr())
+
+    # ---- timed region: W warm-up + K steps, device time, max over ranks ----
+    for _ in range(max(args.warmup, 3)):
+        step()
+    pkg.device_status()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    barrier()
+    e0, e1 = ev(), ev()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    pkg.device_status()
+    ms_total = sharding.max_over_ranks(e0.elapsed_time(e1), dist, dev) if dist is not None else e0.elapsed_time(e1)
+    clocks = sampler.summary() if rank == 0 else {}
+    ms_step = ms_total / args.steps
+    value = len(cases) * flops_dense / (ms_step * 1e-3) / 1e12
+
+    # ---- per-kernel durations (separate loop, same stream) for the roofline and the sweep table ----
+    def time_each(fn, reps):
+        for _ in range(2):
+            fn()
+        ts = []
+        for _ in range(reps):
+            a, b = ev(), ev()
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            ts.append(a.elapsed_time(b))
+        return float(np.mean(ts)), float(np.min(ts))
+
+    reps = max(5, min(20, args.steps))
+    sweep = {}
+    gemm_ms_sum = 0.0
+    exec_flops_sum = 0.0
+    pre_ms_sum = 0.0
+    pack = ws[ap_region:]
+    for c in cases:
+        pre_ms, _ = time_each(lambda: pkg.preprocess_a_packed(c["A"].data_ptr(), M, K, ws.data_ptr(),
+                                                              pack.data_ptr()), reps)
+        gemm_ms, gemm_min = time_each(lambda: pkg.gemm_ab_packed(M, Nl, K, pack.data_ptr(), c["B"].data_ptr(),
+                                                                 Cd.data_ptr(), ws.data_ptr(), c["bp"].data_ptr()), reps)
+        both_ms, _ = time_each(lambda: pkg.sgemm_joint(M, Nl, K, c["A"].data_ptr(), c["B"].data_ptr(), Cd.data_ptr(),
+                                                       c["bp"].data_ptr(), ws.data_ptr()), reps)
+        cub_ms, _ = time_each(lambda: pkg.cublas_sgemm(M, Nl, K, c["A"].data_ptr(), c["B"].data_ptr(),
+                                                       Cd.data_ptr()), reps)
+        density = bin(c["pat"]).count("1") / 8.0
+        exec_flops = flops_dense_local * density           # uniform pattern: joint density = pattern density
+        pre_bytes = 4.0 * M * K + ap_bytes + 4.0 * M * K * density   # read A, write patterns, write live packed rows
+        sweep[c["name"]] = {
+            "joint_density": density,
+            "ms_preprocess_a": pre_ms, "ms_gemm": gemm_ms, "ms_total": both_ms, "ms_cublas": cub_ms,
+            "dense_equiv_tflops_incl_pre": flops_dense_local / (both_ms * 1e-3) / 1e12,
+            "dense_equiv_tflops_gemm_only": flops_dense_local / (gemm_ms * 1e-3) / 1e12,
+            "cublas_tflops": flops_dense_local / (cub_ms * 1e-3) / 1e12,
+            "speedup_vs_cublas_incl_pre": cub_ms / both_ms,
+            "executed_tflops": exec_flops / (gemm_ms * 1e-3) / 1e12,
+            "frac_of_measured_ffma_peak": exec_flops / (gemm_ms * 1e-3) / 1e12 / ffma_peak,
+            "frac_of_nominal_fp32_peak": exec_flops / (gemm_ms * 1e-3) / 1e12 / NOMINAL_FP32_TFLOPS,
+            "preprocess_gbs": pre_bytes / (pre_ms * 1e-3) / 1e9,
+            "preprocess_frac_of_hbm": pre_bytes / (pre_ms * 1e-3) / 1e9 / hbm_peak,
+        }
+        gemm_ms_sum += gemm_ms
+        pre_ms_sum += pre_ms
+        exec_flops_sum += exec_flops
+    pkg.device_status()
+    achieved = exec_flops_sum / (gemm_ms_sum * 1e-3) / 1e12
+    roofline = {
+        "kernel": "esmm_joint_sgemm_packed_kernel", "bound": "fp32",
+        "achieved": achieved, "peak": ffma_peak, "unit": "TFLOP/s", "frac": achieved / ffma_peak,
+        "peak_source": "FFMA microbenchmark in this run (of measured); nominal 74.4 TFLOP/s at 1965 MHz",
+        "flops_per_step": exec_flops_sum, "launches_per_step": len(cases),
+        "traffic": TRAFFIC_BYTES_PER_LAUNCH.get((workload, M)),
+        "traffic_note": "dram read+write bytes of the 100%-density launch from the ncu capture in profiles/",
+        "share_of_step": gemm_ms_sum / (gemm_ms_sum + pre_ms_sum),
+    }
+
+    # ---- end to end through the host-buffer entry point (pinned host A and C, copies inside) ----
+    e2e = None
+    if rank == 0 or dist is not None:
+        import ctypes as C
+        hC = torch.empty((M, Nl), pin_memory=True)
+        plans = []
+        for c in cases:
+            hB = c["B"].cpu()
+            plan = C.c_void_p()
+            pkg.check(L.esmm_plan_create(M, Nl, K, hB.data_ptr(), args.chunks, C.byref(plan)), "esmm_plan_create")
+            hA = torch.empty((M, K), pin_memory=True)
+            hA.copy_(c["A"])
+            plans.append((plan, hA))
+            del hB
+        for plan, hA in plans:
+            pkg.check(L.esmm_plan_run(plan, hA.data_ptr(), hC.data_ptr()), "esmm_plan_run")
+        barrier()
+        e2e_steps = max(1, min(args.steps, 5))
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            for plan, hA in plans:
+                pkg.check(L.esmm_plan_run(plan, hA.data_ptr(), hC.data_ptr()), "esmm_plan_run")
+        barrier()
+        dt = time.perf_counter() - t0
+        if dist is not None:
+            dt = sharding.max_over_ranks(dt, dist, dev)
+        for plan, _ in plans:
+            L.esmm_plan_destroy(plan)
+        e2e = {"value": len(cases) * flops_dense * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(len(cases) * 4 * M * K), "d2h_bytes_per_step": int(len(cases) * 4 * M * Nl),
+               "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps, "chunks": args.chunks,
+               "note": "esmm_plan_run: pinned host A in, pinned host C out, B and its patterns resident"}
+
+    # ---- optional gather of C to every rank, timed separately ----
+    gather = None
+    if dist is not None:
+        def interleave(staging, out, m, n, w):
+            pkg.check(L.esmm_interleave_shards(staging.data_ptr(), out.data_ptr(), m, n, w, 0), "interleave")
+        sharding.gather_columns(Cd, shard, dist, interleave)
+        barrier()
+        a, b = ev(), ev()
+        a.record()
+        full = sharding.gather_columns(Cd, shard, dist, interleave)
+        b.record()
+        barrier()
+        gather = {"ms": sharding.max_over_ranks(a.elapsed_time(b), dist, dev), "bytes": int(4 * M * N)}
+        del full
+
+    # ---- CPU baseline (rank 0, N = 1 only): bounded row sample ----
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        cpu = CpuSgemm(M, N, K, 0xFF)
+        rows = cpu.calibrate(target_s=12.0)
+        dt = cpu.run(rows)
+        sample = f"{rows} of {M} rows of C (all {N} columns, full K), once; extrapolates linearly in rows"
+        cpu_baseline = {"value": 2.0 * rows * N * K / dt / 1e12, "unit": "TFLOP/s", "cores": cpu.threads,
+                        "kind": cpu.kind, "sample": sample, "seconds": dt}
+
+    if rank == 0:
+        line = {
+            "metric": "dense-equivalent TFLOP/s at 4096^3 FP32 vs block density, incl. A-pattern preprocess"
+            if workload == "c2" else "dense-equivalent TFLOP/s at 16384^3 FP32, 25% joint density, incl. A-pattern preprocess",
+            "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong" if world > 1 else "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {
+                "workload": ("c2: M=N=K=%d FP32, N(0,1), uniform patterns 11111111/11110000/11000000/10000000 on A's "
+                             "K columns and B's K rows; step = the 4 densities once" % M) if workload == "c2" else
+                            ("c5: M=N=K=%d FP32, N(0,1), uniform pattern 11000000; B, its cached patterns and C "
+                             "column-sharded over %d GPUs, A and its preprocessing replicated" % (M, world)),
+                "M": M, "N": N, "K": K, "patterns": [p for p, _ in pats], "b_patterns": "cached (offline)",
+                "a_patterns": "per call (packing preprocess inside the timed region)",
+                "l2": "inputs larger than L2: %.0f MB of A/B/C/packed-A touched per step vs 126 MB L2"
+                      % (len(cases) * (2 * 4.0 * M * K + 4.0 * K * Nl) / 1e6 + 4.0 * M * Nl / 1e6),
+                "parallelism": "N-column shards, no collective" if world > 1 else "1 GPU",
+            },
+            "sweep": sweep, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "gpu_launches": int(args.steps * len(cases) * 2), "clocks": clocks,
+            "ffma_peak_tflops_measured": ffma_peak, "hbm_peak_gbs": hbm_peak, "hbm_peak_source": hbm_src,
+            "sm_count": sms, "gather_c": gather,
+        }
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
+# capture summarised under profiles/ (None until captured for that workload).
+TRAFFIC_BYTES_PER_LAUNCH = {}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=None, choices=["c2", "c5"])
+    ap.add_argument("--size", type=int, default=None, help="override M = N = K (experiments only)")
+    ap.add_argument("--chunks", type=int, default=4, help="row chunks of the host-buffer pipeline")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
