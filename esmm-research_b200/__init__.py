@@ -61,6 +61,7 @@ _SIGNATURES = {
     "esmm_gemm_ab_packed": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "esmm_sgemm_joint_workspace_bytes": (C.c_size_t, [_i, _i]),
     "esmm_sgemm_joint": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "esmm_sgemm_joint_static": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "esmm_device_status": (_i, [_vp]),
     "esmm_plan_create": (_i, [_i, _i, _i, _vp, _i, C.POINTER(_vp)]),
     "esmm_plan_run": (_i, [_vp, _vp, _vp]),

@@ -159,6 +159,29 @@ size_t esmm_sgemm_joint_workspace_bytes(int M, int K);
 int esmm_sgemm_joint(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
                      const uint8_t *d_b_pat, void *d_workspace, void *stream);
 
+/*
+ * esmm_sgemm_joint for callers that cannot allocate and cannot pass scratch memory: hosts whose
+ * operator contract forbids allocation at call time, processes whose allocator already owns the
+ * whole GPU, loops that cannot afford the device-wide synchronisation of a cudaMalloc.  Same
+ * inputs, outputs and results as esmm_sgemm_joint, but the scratch (A patterns + packed copy of A)
+ * is a fixed array inside the library image: the call performs no cudaMalloc / cudaFree and uses
+ * no allocating library routine.  It has no counterpart in the reference, whose runner allocates
+ * and frees its pattern buffers on every run.
+ *   - Limit: esmm_a_packed_bytes(M, K) <= ESMM_STATIC_MAX_PACKED_FLOATS * 4 (32 MiB, e.g. A of
+ *     2048 x 4096) and esmm_a_pattern_bytes(M, K, 32) <= ESMM_STATIC_MAX_PATTERN_BYTES; larger A
+ *     returns ESMM_ERR_TOO_LARGE with the sizes in esmm_last_cuda_error().
+ *   - Cost: every GPU that loads the library holds the 32 MiB + 64 KiB array until the library
+ *     is unloaded.
+ *   - The first call on each device looks up the array's device address (with that device
+ *     current); make that first call before any stream capture begins.
+ *   - All calls on a GPU share the array and it keeps the previous call's contents (nothing in it
+ *     needs clearing).  Calls whose kernels overlap on one GPU race on it: serialise them.
+ */
+#define ESMM_STATIC_MAX_PACKED_FLOATS (8u << 20)
+#define ESMM_STATIC_MAX_PATTERN_BYTES (64u << 10)
+int esmm_sgemm_joint_static(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
+                            const uint8_t *d_b_pat, void *stream);
+
 /* Synchronises `stream`, returns and clears the device status word:
  * ESMM_OK, ESMM_ERR_TIMEOUT (a bounded wait expired) or ESMM_ERR_CUDA. */
 int esmm_device_status(void *stream);
