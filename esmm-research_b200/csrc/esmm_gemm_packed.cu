@@ -121,26 +121,45 @@ __device__ __forceinline__ KFrag load_kfrag(const char *pa, const char *pb)
     return f;
 }
 
-__device__ __forceinline__ void fma_top(float (&acc)[8][8], const KFrag &f)
+// The thread's 8 x 8 outputs are held as 2 x 2 blocks for the packed FP32 multiply-add of sm_100
+// (fma.rn.f32x2: two independent IEEE FMAs per instruction, half the issue slots of scalar FFMA).
+// Block (p, q) covers rows 2p, 2p+1 and columns 2q, 2q+1 of the thread tile:
+//   diag[p][q] = (c[2p][2q],   c[2p+1][2q+1])        anti[p][q] = (c[2p][2q+1], c[2p+1][2q])
+// so both use the row pair (a[2p], a[2p+1]) as it comes from shared memory, with the column pair
+// (b[2q], b[2q+1]) as loaded for diag and swapped for anti.  Row pairs 0, 1 are the top 32-row
+// block, 2, 3 the bottom one.  Every output still sees one FMA per live k, in ascending k.
+struct Acc {
+    float2 diag[4][4], anti[4][4];
+};
+
+__device__ __forceinline__ void fma_pair_row(Acc &c, int p, float2 ar, const KFrag &f)
 {
-    fma8(acc[0], f.at.x, f.b0, f.b1);
-    fma8(acc[1], f.at.y, f.b0, f.b1);
-    fma8(acc[2], f.at.z, f.b0, f.b1);
-    fma8(acc[3], f.at.w, f.b0, f.b1);
+    c.diag[p][0] = __ffma2_rn(ar, make_float2(f.b0.x, f.b0.y), c.diag[p][0]);
+    c.anti[p][0] = __ffma2_rn(ar, make_float2(f.b0.y, f.b0.x), c.anti[p][0]);
+    c.diag[p][1] = __ffma2_rn(ar, make_float2(f.b0.z, f.b0.w), c.diag[p][1]);
+    c.anti[p][1] = __ffma2_rn(ar, make_float2(f.b0.w, f.b0.z), c.anti[p][1]);
+    c.diag[p][2] = __ffma2_rn(ar, make_float2(f.b1.x, f.b1.y), c.diag[p][2]);
+    c.anti[p][2] = __ffma2_rn(ar, make_float2(f.b1.y, f.b1.x), c.anti[p][2]);
+    c.diag[p][3] = __ffma2_rn(ar, make_float2(f.b1.z, f.b1.w), c.diag[p][3]);
+    c.anti[p][3] = __ffma2_rn(ar, make_float2(f.b1.w, f.b1.z), c.anti[p][3]);
 }
 
-__device__ __forceinline__ void fma_bottom(float (&acc)[8][8], const KFrag &f)
+__device__ __forceinline__ void fma_top(Acc &c, const KFrag &f)
 {
-    fma8(acc[4], f.ab.x, f.b0, f.b1);
-    fma8(acc[5], f.ab.y, f.b0, f.b1);
-    fma8(acc[6], f.ab.z, f.b0, f.b1);
-    fma8(acc[7], f.ab.w, f.b0, f.b1);
+    fma_pair_row(c, 0, make_float2(f.at.x, f.at.y), f);
+    fma_pair_row(c, 1, make_float2(f.at.z, f.at.w), f);
+}
+
+__device__ __forceinline__ void fma_bottom(Acc &c, const KFrag &f)
+{
+    fma_pair_row(c, 2, make_float2(f.ab.x, f.ab.y), f);
+    fma_pair_row(c, 3, make_float2(f.ab.z, f.ab.w), f);
 }
 
 // A stage whose 32 rows are all live for both row blocks: 8 rows of straight-line code per
 // loop trip, so that the compiler can issue the loads of a row under the multiply-adds of
 // the row before.
-__device__ __forceinline__ void dense_rows(float (&acc)[8][8], const char *sA, const char *sB)
+__device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char *sB)
 {
 #pragma unroll 1
     for (int r0 = 0; r0 < ROWS_PER_STAGE; r0 += 8) {
@@ -153,7 +172,7 @@ __device__ __forceinline__ void dense_rows(float (&acc)[8][8], const char *sA, c
     }
 }
 
-__device__ __forceinline__ void fma_masked(float (&acc)[8][8], const KFrag &f, unsigned jt, unsigned jb, int row)
+__device__ __forceinline__ void fma_masked(Acc &acc, const KFrag &f, unsigned jt, unsigned jb, int row)
 {
     if ((jt >> row) & 1u) fma_top(acc, f);
     if ((jb >> row) & 1u) fma_bottom(acc, f);
@@ -162,7 +181,7 @@ __device__ __forceinline__ void fma_masked(float (&acc)[8][8], const KFrag &f, u
 // Any other stage: `list` holds the indices (one byte each, ascending) of the `cnt` rows that
 // are live for at least one of the warp's two row blocks.  Two rows per step, the next pair
 // loaded before the current pair is multiplied.
-__device__ __forceinline__ void listed_rows(float (&acc)[8][8], const char *sA, const char *sB, unsigned jt,
+__device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char *sB, unsigned jt,
                                             unsigned jb, const unsigned *list, int cnt)
 {
     if (cnt == 0) return;
@@ -384,11 +403,14 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             const uint8_t *rmask = reinterpret_cast<const uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
             const int n = nrows[buf];
 
-            float acc[8][8];
+            Acc acc;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
+            for (int i = 0; i < 4; ++i)
 #pragma unroll
-                for (int j = 0; j < 8; ++j) acc[i][j] = 0.0f;
+                for (int j = 0; j < 4; ++j) {
+                    acc.diag[i][j] = make_float2(0.0f, 0.0f);
+                    acc.anti[i][j] = make_float2(0.0f, 0.0f);
+                }
 
             for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
                 // joint masks of the stage: bit r = row r is live for (top | bottom) block x my columns
@@ -424,18 +446,26 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             __syncwarp();
             if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
 
-            // epilogue: C is overwritten (beta = 0)
+            // epilogue: C is overwritten (beta = 0); un-scramble the 2 x 2 blocks into rows
             const int row0 = tm * TILE_M + wm * 64 + lm * 4;
             const int col0 = tn * TILE_N + wn * 32 + ln * 4;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                const int row = row0 + (i & 3) + 32 * (i >> 2);
-                if (row < p.M) {
-                    float *c = p.C + (size_t)row * p.N + col0;
-                    if (col0 < p.N)
-                        *reinterpret_cast<float4 *>(c) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-                    if (col0 + 16 < p.N)
-                        *reinterpret_cast<float4 *>(c + 16) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+            for (int pr = 0; pr < 4; ++pr) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int i = 2 * pr + e;                        // row of the thread tile
+                    const int row = row0 + (i & 3) + 32 * (i >> 2);
+                    float v[8];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        v[2 * q] = e == 0 ? acc.diag[pr][q].x : acc.anti[pr][q].y;
+                        v[2 * q + 1] = e == 0 ? acc.anti[pr][q].x : acc.diag[pr][q].y;
+                    }
+                    if (row < p.M) {
+                        float *c = p.C + (size_t)row * p.N + col0;
+                        if (col0 < p.N) *reinterpret_cast<float4 *>(c) = make_float4(v[0], v[1], v[2], v[3]);
+                        if (col0 + 16 < p.N) *reinterpret_cast<float4 *>(c + 16) = make_float4(v[4], v[5], v[6], v[7]);
+                    }
                 }
             }
         }
