@@ -12,9 +12,9 @@
 //   * a mask warp walks the tile's K blocks one tile ahead and appends, for every K block,
 //     the k rows that are live for the tile as a whole (the OR over its four 32-row blocks
 //     AND the OR over its four 32-column blocks) to a row list, with one byte per row saying
-//     for which row blocks and which column blocks the row is live.  K blocks with more
-//     than `brow_bits` live k are appended whole (8 rows), so that they can be fetched as
-//     one box;
+//     for which row blocks and which column blocks the row is live.  On a tile whose K
+//     blocks do not all share one live byte, K blocks with more than `brow_bits` live k are
+//     appended whole (8 rows), so that they can be fetched as one box;
 //   * a TMA warp cuts the row list into stages of 32 rows and fetches each stage's rows into
 //     a ring slot ([32][512 B] of A, [32][512 B] of B), guarded by full / empty mbarriers.
 //     Both operands are also described to the copy engine as 3-D tensors (column, k % 8,
@@ -65,6 +65,7 @@ struct PackedParams {
     int stages;
     int brow_bits;   // K blocks with more live k than this are fetched whole
     int b_runs_ok;   // K % 8 == 0: the 3-D view of B stays inside the matrix
+    int force_listed;  // tuning aid: take the index-list path even for all-live stages
     const uint8_t *a_pat;
     const uint8_t *b_pat;
     float *C;
@@ -172,10 +173,25 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
     }
 }
 
-__device__ __forceinline__ void fma_masked(Acc &acc, const KFrag &f, unsigned jt, unsigned jb, int row)
+// Two listed rows.  When both are live for both row blocks (always, when the top and bottom block
+// share their pattern) the four half-rows form one straight-line block of 64 packed FMAs;
+// otherwise each half-row is taken or skipped on its own.
+__device__ __forceinline__ void fma_listed_pair(Acc &acc, const KFrag &f0, const KFrag &f1, unsigned jt, unsigned jb,
+                                                int r0, int r1, bool have1)
 {
-    if ((jt >> row) & 1u) fma_top(acc, f);
-    if ((jb >> row) & 1u) fma_bottom(acc, f);
+    const unsigned m0 = ((jt >> r0) & 1u) | (((jb >> r0) & 1u) << 1);
+    const unsigned m1 = have1 ? ((jt >> r1) & 1u) | (((jb >> r1) & 1u) << 1) : 0u;
+    if ((m0 & m1) == 3u) {
+        fma_top(acc, f0);
+        fma_bottom(acc, f0);
+        fma_top(acc, f1);
+        fma_bottom(acc, f1);
+    } else {
+        if (m0 & 1u) fma_top(acc, f0);
+        if (m0 & 2u) fma_bottom(acc, f0);
+        if (m1 & 1u) fma_top(acc, f1);
+        if (m1 & 2u) fma_bottom(acc, f1);
+    }
 }
 
 // Any other stage: `list` holds the indices (one byte each, ascending) of the `cnt` rows that
@@ -198,14 +214,12 @@ __device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char
         const int r2 = row_at(i + 2), r3 = row_at(i + 3);
         const KFrag g0 = load_kfrag(sA + (r2 << 9), sB + (r2 << 9));
         const KFrag g1 = load_kfrag(sA + (r3 << 9), sB + (r3 << 9));
-        fma_masked(acc, f0, jt, jb, r0);
-        if (i + 1 < cnt) fma_masked(acc, f1, jt, jb, r1);
+        fma_listed_pair(acc, f0, f1, jt, jb, r0, r1, i + 1 < cnt);
         r0 = row_at(i + 4);
         r1 = row_at(i + 5);
         f0 = load_kfrag(sA + (r0 << 9), sB + (r0 << 9));
         f1 = load_kfrag(sA + (r1 << 9), sB + (r1 << 9));
-        if (i + 2 < cnt) fma_masked(acc, g0, jt, jb, r2);
-        if (i + 3 < cnt) fma_masked(acc, g1, jt, jb, r3);
+        if (i + 2 < cnt) fma_listed_pair(acc, g0, g1, jt, jb, r2, r3, i + 3 < cnt);
     }
 }
 
@@ -253,6 +267,27 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             uint16_t *krow = reinterpret_cast<uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
             uint8_t *rmask = reinterpret_cast<uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
+            // A first pass over the tile's pattern bytes decides the listing policy: if every K block has the same live byte (a uniform
+            // pattern) only live k are listed at any density - the TMA warp then finds its
+            // one-box runs; otherwise K blocks with more than brow_bits live k are listed whole.
+            unsigned live_first = 0;
+            bool uniform = true;
+            for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
+                const int kb = kb0 + lane;
+                unsigned au = 0, bu = 0;
+                if (kb < p.nKB) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int mb = tm * 4 + i, nb = tn * 4 + i;
+                        if (mb < p.a_rows) au |= p.a_pat[(size_t)mb * p.nKB + kb];
+                        if (nb < p.b_rows) bu |= p.b_pat[(size_t)nb * p.nKB + kb];
+                    }
+                }
+                const unsigned live = au & bu;
+                if (kb0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, live, 0);
+                uniform = uniform && __all_sync(0xFFFFFFFFu, kb >= p.nKB || live == live_first);
+            }
+            const int whole_above = uniform ? BK : p.brow_bits;
             int pos = 0;
             for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
                 const int kb = kb0 + lane;
@@ -269,7 +304,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 au = (au | (au >> 8)) & 0xFFu;
                 bu = (bu | (bu >> 8)) & 0xFFu;
                 const unsigned live = au & bu;                       // k live for the tile as a whole
-                unsigned rows = __popc(live) > p.brow_bits ? 0xFFu : live;  // k rows to list
+                unsigned rows = __popc(live) > whole_above ? 0xFFu : live;  // k rows to list
                 if (live == 0u) rows = 0u;
                 const int c = __popc(rows);
                 int incl = c;                                        // inclusive scan over the lanes
@@ -418,7 +453,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 const unsigned colb = (rm >> b_shift) & 1u;
                 const unsigned jt = __ballot_sync(0xFFFFFFFFu, ((rm >> t_shift) & colb) != 0u);
                 const unsigned jb = __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u);
-                const bool dense = (jt & jb) == 0xFFFFFFFFu;
+                const bool dense = (jt & jb) == 0xFFFFFFFFu && !p.force_listed;
                 int live_cnt = 0;
                 if (!dense) {
                     // indices of my live rows, written by the lanes in parallel while the stage's
@@ -495,9 +530,10 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     p.tiles_m = ceil_div(M, TILE_M);
     p.tiles_n = ceil_div(N, TILE_N);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.brow_bits = env_int("ESMM_BROW_BITS", 7);
+    p.brow_bits = env_int("ESMM_BROW_BITS", 3);
     if (p.brow_bits < 0) p.brow_bits = 0;
     if (p.brow_bits > 8) p.brow_bits = 8;
+    p.force_listed = env_int("ESMM_FORCE_LISTED", 0);
     p.a_pat = d_a_pat;
     p.b_pat = d_b_pat;
     p.C = d_C;

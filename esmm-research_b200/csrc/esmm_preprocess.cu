@@ -87,30 +87,31 @@ esmm_preprocess_a_pack_kernel(const float *__restrict__ A, int M, int K, int nMB
         const int row0 = mb * 32;
         const float *src = A + (size_t)row0 * K + col;
         unsigned nib = 0;
+        // all 32 rows of the lane's 4 columns are requested before anything is consumed: 16 KB in
+        // flight per warp, which is what keeps HBM busy at the occupancy the 16 KB tile allows
+        float4 v[32];
 #pragma unroll
-        for (int r0 = 0; r0 < 32; r0 += 8) {
-            float4 v[8];
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (col_ok && row0 + r0 + u < M) v[u] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)(r0 + u) * K));
-            }
-#pragma unroll
-            for (int u = 0; u < 8; ++u) {
-                nib |= nz4(v[u]);
-                const int r = r0 + u;
-                // element (r, c) lives at c * 32 + ((r + (c >> 2)) & 31); here c >> 2 == lane
-                const int pos = (r + lane) & 31;
-                tile[(lane * 4 + 0) * 32 + pos] = v[u].x;
-                tile[(lane * 4 + 1) * 32 + pos] = v[u].y;
-                tile[(lane * 4 + 2) * 32 + pos] = v[u].z;
-                tile[(lane * 4 + 3) * 32 + pos] = v[u].w;
-            }
+        for (int r = 0; r < 32; ++r) {
+            v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (col_ok && row0 + r < M) v[r] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K));
         }
+#pragma unroll
+        for (int r = 0; r < 32; ++r) nib |= nz4(v[r]);
         // live columns of the chunk: bit l of liveq[q] says column 4 l + q has a nonzero
         unsigned liveq[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) liveq[q] = __ballot_sync(0xFFFFFFFFu, (nib >> q) & 1u);
+        // Only live columns go through the tile.  (This also makes every store depend on all 32
+        // loads, so the loads are all in flight together.)
+#pragma unroll
+        for (int r = 0; r < 32; ++r) {
+            // element (r, c) lives at c * 32 + ((r + (c >> 2)) & 31); here c >> 2 == lane
+            const int pos = (r + lane) & 31;
+            if (nib & 1u) tile[(lane * 4 + 0) * 32 + pos] = v[r].x;
+            if (nib & 2u) tile[(lane * 4 + 1) * 32 + pos] = v[r].y;
+            if (nib & 4u) tile[(lane * 4 + 2) * 32 + pos] = v[r].z;
+            if (nib & 8u) tile[(lane * 4 + 3) * 32 + pos] = v[r].w;
+        }
         const unsigned other = __shfl_xor_sync(0xFFFFFFFFu, nib, 1);
         const int kb_lane = kc * 16 + (lane >> 1);
         if (!(lane & 1) && kb_lane < nKB) out[(size_t)mb * nKB + kb_lane] = (uint8_t)(nib | (other << 4));
