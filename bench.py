@@ -391,9 +391,10 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, from the ncu
-# capture summarised under profiles/ (None until captured for that workload).
-TRAFFIC_BYTES_PER_LAUNCH = {}
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (the
+# 100%-density launch of the sweep), from the ncu capture summarised in
+# profiles/packed_gemm_4096_density100.txt; None for workloads without a capture.
+TRAFFIC_BYTES_PER_LAUNCH = {("c2", 4096): 337598464 + 53974784}
 
 
 def main() -> None:
