@@ -63,6 +63,7 @@ _SIGNATURES = {
     "esmm_sgemm_joint": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "esmm_sgemm_joint_static": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "esmm_device_status": (_i, [_vp]),
+    "esmm_selftest_bounded_wait": (_i, [C.c_uint, _vp]),
     "esmm_plan_create": (_i, [_i, _i, _i, _vp, _i, C.POINTER(_vp)]),
     "esmm_plan_run": (_i, [_vp, _vp, _vp]),
     "esmm_plan_destroy": (_i, [_vp]),

@@ -144,6 +144,23 @@ __global__ void esmm_ffma_peak_kernel(float *out, int iters, float a, float b)
     if (s == 123.456f) out[0] = s;  // keeps the chain alive; practically never true
 }
 
+// One CTA waits, with the library's bounded wait and a caller-chosen budget, on an mbarrier that
+// nothing ever arrives on; the wait runs out, the kernel records ESMM_ERR_TIMEOUT in the status
+// word and returns normally.  Exercises the failure path of the GEMM kernels without a fault.
+__global__ void esmm_selftest_bounded_wait_kernel(int *status, unsigned long long budget_ns)
+{
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_barrier_init();
+    }
+    __syncthreads();
+    const bool ok = mbar_wait_budget(smem_u32(&bar), 0, &abort_flag, budget_ns);
+    if (!ok && (threadIdx.x & 31) == 0) atomicExch(status, (int)ESMM_ERR_TIMEOUT);
+}
+
 static cublasHandle_t cublas_handle_for_device()
 {
     static cublasHandle_t handles[64] = {nullptr};
@@ -299,6 +316,16 @@ int esmm_device_status(void *stream)
     ESMM_CUDA_TRY(cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost));
     if (v != 0) ESMM_CUDA_TRY(cudaMemset(p, 0, sizeof v));
     return v;
+}
+
+int esmm_selftest_bounded_wait(unsigned budget_us, void *stream)
+{
+    if (budget_us == 0 || budget_us > 1000000u) return ESMM_ERR_SHAPE;  // at most one second
+    int *status = esmm::device_status_ptr();
+    if (!status) return ESMM_ERR_CUDA;
+    esmm::esmm_selftest_bounded_wait_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(status, (unsigned long long)budget_us * 1000ull);
+    ESMM_CUDA_TRY(cudaGetLastError());
+    return ESMM_OK;
 }
 
 // ---- host-buffer plan -------------------------------------------------------

@@ -89,7 +89,8 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 // is raised (so that the CTA's other waiters leave too) and false is returned.
 constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate wait
 
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                                 uint64_t budget_ns)
 {
 #pragma unroll 1
     for (int i = 0; i < 128; ++i)
@@ -99,11 +100,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     while (true) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (global_timer_ns() - t0 > WAIT_BUDGET_NS) {
+        if (global_timer_ns() - t0 > budget_ns) {
             *abort_flag = 1;
             return false;
         }
     }
+}
+
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+{
+    return mbar_wait_budget(bar, parity, abort_flag, WAIT_BUDGET_NS);
 }
 
 // 2-D tiled TMA load, completion counted in bytes on an mbarrier of this CTA.

@@ -186,6 +186,14 @@ int esmm_sgemm_joint_static(int M, int N, int K, const float *d_A, const float *
  * ESMM_OK, ESMM_ERR_TIMEOUT (a bounded wait expired) or ESMM_ERR_CUDA. */
 int esmm_device_status(void *stream);
 
+/*
+ * Failure-path self test: launches one CTA that waits (bounded, `budget_us` microseconds, at most
+ * one second) on a barrier nothing arrives on.  The wait gives up, the kernel returns normally and
+ * the next esmm_device_status() reports ESMM_ERR_TIMEOUT; the context stays usable.  The reference
+ * has no device-side waits and no counterpart.
+ */
+int esmm_selftest_bounded_wait(unsigned budget_us, void *stream);
+
 /* ---- host-buffer (end-to-end) path -------------------------------------- */
 
 /*

@@ -1,0 +1,89 @@
+"""The exec_b200 command line: same grammar, messages and exit codes as the reference driver
+(driver.cu:142-487), plus the additive generator flags."""
+import json
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+
+def run(pkg, *args):
+    if not os.path.exists(pkg.EXE_PATH):
+        import __graft_entry__ as g
+        g.build()
+    p = subprocess.run([pkg.EXE_PATH, *args], capture_output=True, text=True, timeout=600)
+    return p.returncode, p.stdout + p.stderr
+
+
+# ---- argument handling: no GPU needed ---------------------------------------------------------
+def test_help_and_argument_errors(pkg):
+    rc, out = run(pkg, "--help")
+    assert rc == 0 and "Usage:" in out and "--blockwise" in out and "29:" in out
+    rc, out = run(pkg, "99", "1")
+    assert rc == 1 and "Error: Invalid kernel selection '99'" in out
+    rc, out = run(pkg, "29", "1", "--pattern", "1100")
+    assert rc == 1 and "Pattern must be exactly 8 characters" in out
+    rc, out = run(pkg, "29", "1", "--pattern", "1100000x")
+    assert rc == 1 and "Pattern must contain only '0' and '1' characters" in out
+    rc, out = run(pkg, "29", "0")
+    assert rc == 1 and "Number of runs must be positive" in out
+    rc, out = run(pkg, "29", "1", "--size", "-4")
+    assert rc == 1 and "Size must be positive" in out
+    rc, out = run(pkg, "29", "1", "--size")
+    assert rc == 1 and "--size requires an argument" in out
+    rc, out = run(pkg, "29", "1", "--load-b", "w.bin")
+    assert rc == 1 and "--dims M K N required with --load-a / --load-b" in out
+
+
+# ---- runs ---------------------------------------------------------------------------------------
+@pytest.mark.gpu
+def test_blockwise_run_with_cublas_check(pkg, cuda):
+    rc, out = run(pkg, "29,15", "2", "--blockwise", "--pattern", "11110000", "--size", "512", "--skip-stats")
+    assert rc == 0, out
+    assert out.count("PASSED") == 2 and "Summary: 2/2 kernels passed" in out
+    assert out.count("Kernel time:") == 2 and "=== Skip Stats: K29 ===" in out
+    assert "Kernel 29 (ESMM A+B Optimized V3 (K26 + templated smem + float2 A-loads)): PASSED" in out
+
+
+@pytest.mark.gpu
+def test_uniform_cpu_check_json(pkg, cuda):
+    rc, out = run(pkg, "29", "2", "--uniform", "--pattern", "10000000", "--size", "512", "--cpu-check", "--json")
+    assert rc == 0, out
+    line = json.loads([l for l in out.splitlines() if l.startswith("{")][0])
+    assert line["kernel"] == 29 and line["passed"] is True and 0 <= line["cpu_rel_inf"] <= 1e-4
+    assert "CPU SGEMM check" in out
+
+
+@pytest.mark.gpu
+def test_default_pattern_random_and_verbose_modes(pkg, cuda):
+    rc, out = run(pkg, "29", "1", "--size", "256", "--pattern", "11110000", "--verbose")
+    assert rc == 0 and "Sparsity mode: PATTERN-BASED (column-wise)" in out and "Status: PASSED" in out
+    rc, out = run(pkg, "25-29", "1", "--size", "256", "--random", "--no-check")
+    assert rc == 0 and out.count("COMPLETED (no verification)") == 5
+    assert "Summary: 5/5 kernels completed (no verification)" in out
+    rc, out = run(pkg, "29", "1", "--size", "256", "--tile-random", "0.3", "0.7", "--seed", "7")
+    assert rc == 0 and "PASSED" in out
+
+
+@pytest.mark.gpu
+def test_load_raw_weights(pkg, cuda, tmp_path):
+    M, K, N = 128, 256, 384
+    rng = np.random.default_rng(0)
+    B = rng.standard_normal((K, N), dtype=np.float32)
+    B[(np.arange(K) % 8) >= 2] = 0.0
+    path = tmp_path / "w.bin"
+    B.tofile(path)
+    rc, out = run(pkg, "29,15", "1", "--load-b", str(path), "--dims", str(M), str(K), str(N))
+    assert rc == 0 and "Summary: 2/2 kernels passed" in out
+    (tmp_path / "short.bin").write_bytes(b"\0" * 100)
+    rc, out = run(pkg, "29", "1", "--load-b", str(tmp_path / "short.bin"), "--dims", str(M), str(K), str(N))
+    assert rc == 1 and "Error: expected" in out
+    rc, out = run(pkg, "29", "1", "--load-b", str(tmp_path / "none.bin"), "--dims", str(M), str(K), str(N))
+    assert rc == 1 and "Error: cannot open" in out
+
+
+@pytest.mark.gpu
+def test_single_operand_ids_fail_cleanly(pkg, cuda):
+    rc, out = run(pkg, "17,29", "1", "--size", "256")
+    assert rc == 1 and "Summary: 1/2 kernels passed" in out and "not provided by this library" in out

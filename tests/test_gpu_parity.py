@@ -411,3 +411,17 @@ def test_ffma_peak_is_plausible(pkg, cuda):
 def test_smoke_entry(cuda):
     import __graft_entry__ as g
     g.smoke()
+
+
+def test_bounded_wait_reports_timeout_and_context_survives(cuda, pkg, oracle_mod):
+    """A device-side wait that nothing satisfies gives up after its budget, the kernel returns and
+    the host reads ESMM_ERR_TIMEOUT; the next call works and the status is clean again."""
+    L = pkg.lib()
+    assert L.esmm_device_status(None) == 0
+    assert L.esmm_selftest_bounded_wait(2000, None) == 0          # 2 ms budget
+    assert L.esmm_device_status(None) == pkg.ERR_TIMEOUT
+    assert L.esmm_device_status(None) == 0                        # reading clears it
+    assert L.esmm_selftest_bounded_wait(0, None) == pkg.ERR_SHAPE
+    assert L.esmm_selftest_bounded_wait(2_000_000, None) == pkg.ERR_SHAPE
+    A, B = workloads.uniform_pattern(128, 128, 64, 0x0F, seed=3)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
