@@ -97,7 +97,7 @@ __host__ __device__ inline PackedSmem packed_smem_layout(int stages, int cap)
     o += 2 * L.rmask_stride;
     o = (o + 15u) & ~15u;
     L.wlist_off = o;  // per consumer warp: indices of its live rows of the current stage
-    o += P_CONSUMER_WARPS * 32;
+    o += P_CONSUMER_WARPS * 96;  // WLIST_BYTES each
     L.bar_off = o;    // full[P_MAX_STAGES], empty[P_MAX_STAGES], list_full[2], list_empty[2]
     o += (2 * P_MAX_STAGES + 4) * 8;
     L.misc_off = o;   // nrows[2], abort
@@ -174,14 +174,33 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
     }
 }
 
+// ---- stages that are not all-live: per-warp index list ------------------------------------------
+// One 16-bit entry per row that is live for at least one of the warp's two row blocks, ascending:
+// bits 0-13 the row's byte offset in the stage (row * 512), bit 14 "live for the top block",
+// bit 15 "live for the bottom block".  The list is padded with 8 zero entries (offset 0, no
+// flags: loaded, never multiplied) so that the loop below needs no bounds checks.
+constexpr int WLIST_ENTRIES = ROWS_PER_STAGE + 8;
+constexpr int WLIST_BYTES = 96;   // WLIST_ENTRIES * 2, rounded up to a multiple of 16
+static_assert(WLIST_ENTRIES * 2 <= WLIST_BYTES, "per-warp list does not fit");
+
+__device__ __forceinline__ unsigned entry_of(const uint2 &w, int j)
+{
+    const unsigned word = (j & 2) ? w.y : w.x;
+    return (j & 1) ? (word >> 16) : (word & 0xFFFFu);
+}
+
+__device__ __forceinline__ KFrag load_entry(const char *sA, const char *sB, unsigned e)
+{
+    const unsigned off = e & 0x3FFFu;
+    return load_kfrag(sA + off, sB + off);
+}
+
 // Two listed rows.  When both are live for both row blocks (always, when the top and bottom block
 // share their pattern) the four half-rows form one straight-line block of 64 packed FMAs;
 // otherwise each half-row is taken or skipped on its own.
-__device__ __forceinline__ void fma_listed_pair(Acc &acc, const KFrag &f0, const KFrag &f1, unsigned jt, unsigned jb,
-                                                int r0, int r1, bool have1)
+__device__ __forceinline__ void fma_listed_pair(Acc &acc, const KFrag &f0, const KFrag &f1, unsigned e0, unsigned e1)
 {
-    const unsigned m0 = ((jt >> r0) & 1u) | (((jb >> r0) & 1u) << 1);
-    const unsigned m1 = have1 ? ((jt >> r1) & 1u) | (((jb >> r1) & 1u) << 1) : 0u;
+    const unsigned m0 = e0 >> 14, m1 = e1 >> 14;
     if ((m0 & m1) == 3u) {
         fma_top(acc, f0);
         fma_bottom(acc, f0);
@@ -195,32 +214,22 @@ __device__ __forceinline__ void fma_listed_pair(Acc &acc, const KFrag &f0, const
     }
 }
 
-// Any other stage: `list` holds the indices (one byte each, ascending) of the `cnt` rows that
-// are live for at least one of the warp's two row blocks.  Two rows per step, the next pair
-// loaded before the current pair is multiplied.
-__device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char *sB, unsigned jt,
-                                            unsigned jb, const unsigned *list, int cnt)
+// Two rows per step, the next pair loaded before the current pair is multiplied.
+__device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char *sB, const uint16_t *list, int cnt)
 {
-    if (cnt == 0) return;
-    const int first = (int)(list[0] & 0xFFu);
-    auto row_at = [&](int i) -> int {
-        // index of the i-th listed row, or the first one past the end (loaded, never multiplied)
-        return i < cnt ? (int)((list[i >> 2] >> (8 * (i & 3))) & 0xFFu) : first;
-    };
-    int r0 = first, r1 = row_at(1);
-    KFrag f0 = load_kfrag(sA + (r0 << 9), sB + (r0 << 9));
-    KFrag f1 = load_kfrag(sA + (r1 << 9), sB + (r1 << 9));
+    uint2 ew = *reinterpret_cast<const uint2 *>(list);   // entries 0..3
+    KFrag f0 = load_entry(sA, sB, entry_of(ew, 0));
+    KFrag f1 = load_entry(sA, sB, entry_of(ew, 1));
 #pragma unroll 1
     for (int i = 0; i < cnt; i += 4) {
-        const int r2 = row_at(i + 2), r3 = row_at(i + 3);
-        const KFrag g0 = load_kfrag(sA + (r2 << 9), sB + (r2 << 9));
-        const KFrag g1 = load_kfrag(sA + (r3 << 9), sB + (r3 << 9));
-        fma_listed_pair(acc, f0, f1, jt, jb, r0, r1, i + 1 < cnt);
-        r0 = row_at(i + 4);
-        r1 = row_at(i + 5);
-        f0 = load_kfrag(sA + (r0 << 9), sB + (r0 << 9));
-        f1 = load_kfrag(sA + (r1 << 9), sB + (r1 << 9));
-        if (i + 2 < cnt) fma_listed_pair(acc, g0, g1, jt, jb, r2, r3, i + 3 < cnt);
+        const KFrag g0 = load_entry(sA, sB, entry_of(ew, 2));
+        const KFrag g1 = load_entry(sA, sB, entry_of(ew, 3));
+        fma_listed_pair(acc, f0, f1, entry_of(ew, 0), entry_of(ew, 1));
+        const uint2 en = *reinterpret_cast<const uint2 *>(list + i + 4);   // padded: always readable
+        f0 = load_entry(sA, sB, entry_of(en, 0));
+        f1 = load_entry(sA, sB, entry_of(en, 1));
+        fma_listed_pair(acc, g0, g1, entry_of(ew, 2), entry_of(ew, 3));
+        ew = en;
     }
 }
 
@@ -268,11 +277,10 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             uint16_t *krow = reinterpret_cast<uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
             uint8_t *rmask = reinterpret_cast<uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
-            // A first pass over the tile's pattern bytes decides the listing policy: if every K block has the same live byte (a uniform
-            // pattern) only live k are listed at any density - the TMA warp then finds its
-            // one-box runs; otherwise K blocks with more than brow_bits live k are listed whole.
+            // A first pass over the tile's pattern bytes decides the listing policy.
             unsigned live_first = 0;
             bool uniform = true;
+            int live_total = 0;
             for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
                 const int kb = kb0 + lane;
                 unsigned au = 0, bu = 0;
@@ -287,8 +295,12 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 const unsigned live = au & bu;
                 if (kb0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, live, 0);
                 uniform = uniform && __all_sync(0xFFFFFFFFu, kb >= p.nKB || live == live_first);
+                live_total += __reduce_add_sync(0xFFFFFFFFu, __popc(live));
             }
-            const int whole_above = uniform ? BK : p.brow_bits;
+            // uniform tile: list live k only.  Otherwise single rows cost a copy each, which pays
+            // only on sparse tiles (on average at most 2 live k per K block); denser tiles list
+            // every live K block whole.
+            const int whole_above = uniform ? BK : (live_total <= 2 * p.nKB ? p.brow_bits : 0);
             int pos = 0;
             for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
                 const int kb = kb0 + lane;
@@ -426,7 +438,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
         const uint32_t a_thr = (uint32_t)(wm * 64 + lm * 4) * 4;                      // within a row of A
         const uint32_t b_thr = STAGE_HALF_BYTES + (uint32_t)(wn * 32 + ln * 4) * 4;  // within a row of B
         const int t_shift = 2 * wm, b_shift = 4 + wn;
-        unsigned *wlist = reinterpret_cast<unsigned *>(smem + L.wlist_off) + warp * 8;  // 32 bytes per warp
+        uint16_t *wlist = reinterpret_cast<uint16_t *>(smem + L.wlist_off + warp * WLIST_BYTES);
         int slot = 0;
         uint32_t phase = 0;
         int it = 0;
@@ -457,12 +469,14 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 const bool dense = (jt & jb) == 0xFFFFFFFFu && !p.force_listed;
                 int live_cnt = 0;
                 if (!dense) {
-                    // indices of my live rows, written by the lanes in parallel while the stage's
-                    // data may still be in flight
+                    // my live rows as list entries, written by the lanes in parallel while the
+                    // stage's data may still be in flight
                     const unsigned u = jt | jb;
                     live_cnt = __popc(u);
                     if ((u >> lane) & 1u)
-                        reinterpret_cast<uint8_t *>(wlist)[__popc(u & ((1u << lane) - 1u))] = (uint8_t)lane;
+                        wlist[__popc(u & ((1u << lane) - 1u))] =
+                            (uint16_t)((lane << 9) | (((jt >> lane) & 1u) << 14) | (((jb >> lane) & 1u) << 15));
+                    if (lane < 8) wlist[live_cnt + lane] = 0;
                     __syncwarp();
                 }
                 ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
@@ -470,7 +484,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 const char *sA = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + a_thr;
                 const char *sB = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + b_thr;
                 if (dense) dense_rows(acc, sA, sB);
-                else listed_rows(acc, sA, sB, jt, jb, wlist, live_cnt);
+                else listed_rows(acc, sA, sB, wlist, live_cnt);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * slot);
                 if (++slot == p.stages) {
