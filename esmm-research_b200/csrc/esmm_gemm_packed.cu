@@ -54,6 +54,20 @@ constexpr int P_MASK_WARP = P_CONSUMER_WARPS + 1;
 constexpr int P_THREADS = (P_CONSUMER_WARPS + 2) * 32;         // 320
 constexpr int P_MAX_STAGES = 6;
 
+// Optional timeline for tuning (build with -DESMM_TRACE): CTA 0 stamps %globaltimer at a few points
+// into a device array that esmm_trace_read copies out.  Not part of the product build or of the ABI.
+#ifdef ESMM_TRACE
+__device__ unsigned long long g_esmm_trace[1024];
+#define ESMM_STAMP(idx)                                                                   \
+    do {                                                                                  \
+        if (blockIdx.x == 0 && lane == 0 && (idx) < 1024) g_esmm_trace[(idx)] = global_timer_ns(); \
+    } while (0)
+#else
+#define ESMM_STAMP(idx) \
+    do {                \
+    } while (0)
+#endif
+
 struct PackedParams {
     int M, N, K;
     int nKB;         // ceil(K / 8)
@@ -66,6 +80,7 @@ struct PackedParams {
     int brow_bits;   // K blocks with more live k than this are fetched whole
     int b_runs_ok;   // K % 8 == 0: the 3-D view of B stays inside the matrix
     int force_listed;  // tuning aid: take the index-list path even for all-live stages
+    int vec_patterns;  // nKB % 16 == 0 and 16-byte aligned pattern arrays: 16 K blocks per lane and load
     const uint8_t *a_pat;
     const uint8_t *b_pat;
     float *C;
@@ -97,7 +112,7 @@ __host__ __device__ inline PackedSmem packed_smem_layout(int stages, int cap)
     o += 2 * L.rmask_stride;
     o = (o + 15u) & ~15u;
     L.wlist_off = o;  // per consumer warp: indices of its live rows of the current stage
-    o += P_CONSUMER_WARPS * 96;  // WLIST_BYTES each
+    o += P_CONSUMER_WARPS * 2 * 96;  // two lists of WLIST_BYTES per warp
     L.bar_off = o;    // full[P_MAX_STAGES], empty[P_MAX_STAGES], list_full[2], list_empty[2]
     o += (2 * P_MAX_STAGES + 4) * 8;
     L.misc_off = o;   // nrows[2], abort
@@ -174,14 +189,18 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
     }
 }
 
-// ---- stages that are not all-live: per-warp index list ------------------------------------------
-// One 16-bit entry per row that is live for at least one of the warp's two row blocks, ascending:
-// bits 0-13 the row's byte offset in the stage (row * 512), bit 14 "live for the top block",
-// bit 15 "live for the bottom block".  The list is padded with 8 zero entries (offset 0, no
-// flags: loaded, never multiplied) so that the loop below needs no bounds checks.
+// ---- stages that are not all-live: per-warp index lists ------------------------------------------
+// A list holds, ascending, the byte offset in the stage (row * 512, 16 bits) of every row that is
+// live for the warp, padded with 8 zero entries so that look-ahead loads need no bounds checks.
+// When the warp's two 32-row blocks have the same live rows (jt == jb) there is one list and every
+// listed row is multiplied into all 8 x 8 outputs (mode BOTH).  Otherwise the top and the bottom
+// block get a list each and are processed one after the other (modes TOP, BOTTOM): each
+// accumulator still sees its own live k in ascending order, no multiply-add is predicated, and the
+// only price is that B rows live for both blocks are read from shared memory twice.
 constexpr int WLIST_ENTRIES = ROWS_PER_STAGE + 8;
 constexpr int WLIST_BYTES = 96;   // WLIST_ENTRIES * 2, rounded up to a multiple of 16
 static_assert(WLIST_ENTRIES * 2 <= WLIST_BYTES, "per-warp list does not fit");
+enum { MODE_BOTH = 0, MODE_TOP = 1, MODE_BOTTOM = 2 };
 
 __device__ __forceinline__ unsigned entry_of(const uint2 &w, int j)
 {
@@ -189,48 +208,126 @@ __device__ __forceinline__ unsigned entry_of(const uint2 &w, int j)
     return (j & 1) ? (word >> 16) : (word & 0xFFFFu);
 }
 
-__device__ __forceinline__ KFrag load_entry(const char *sA, const char *sB, unsigned e)
+template <int MODE>
+__device__ __forceinline__ KFrag load_entry(const char *sA, const char *sB, unsigned off)
 {
-    const unsigned off = e & 0x3FFFu;
-    return load_kfrag(sA + off, sB + off);
+    KFrag f;
+    if (MODE != MODE_BOTTOM) f.at = *reinterpret_cast<const float4 *>(sA + off);
+    if (MODE != MODE_TOP) f.ab = *reinterpret_cast<const float4 *>(sA + off + 128);
+    f.b0 = *reinterpret_cast<const float4 *>(sB + off);
+    f.b1 = *reinterpret_cast<const float4 *>(sB + off + 64);
+    return f;
 }
 
-// Two listed rows.  When both are live for both row blocks (always, when the top and bottom block
-// share their pattern) the four half-rows form one straight-line block of 64 packed FMAs;
-// otherwise each half-row is taken or skipped on its own.
-__device__ __forceinline__ void fma_listed_pair(Acc &acc, const KFrag &f0, const KFrag &f1, unsigned e0, unsigned e1)
+template <int MODE>
+__device__ __forceinline__ void fma_entry(Acc &acc, const KFrag &f)
 {
-    const unsigned m0 = e0 >> 14, m1 = e1 >> 14;
-    if ((m0 & m1) == 3u) {
-        fma_top(acc, f0);
-        fma_bottom(acc, f0);
-        fma_top(acc, f1);
-        fma_bottom(acc, f1);
-    } else {
-        if (m0 & 1u) fma_top(acc, f0);
-        if (m0 & 2u) fma_bottom(acc, f0);
-        if (m1 & 1u) fma_top(acc, f1);
-        if (m1 & 2u) fma_bottom(acc, f1);
-    }
+    if (MODE != MODE_BOTTOM) fma_top(acc, f);
+    if (MODE != MODE_TOP) fma_bottom(acc, f);
 }
 
 // Two rows per step, the next pair loaded before the current pair is multiplied.
+template <int MODE>
 __device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char *sB, const uint16_t *list, int cnt)
 {
+    const int n4 = cnt & ~3;
     uint2 ew = *reinterpret_cast<const uint2 *>(list);   // entries 0..3
-    KFrag f0 = load_entry(sA, sB, entry_of(ew, 0));
-    KFrag f1 = load_entry(sA, sB, entry_of(ew, 1));
+    KFrag f0 = load_entry<MODE>(sA, sB, entry_of(ew, 0));
+    KFrag f1 = load_entry<MODE>(sA, sB, entry_of(ew, 1));
 #pragma unroll 1
-    for (int i = 0; i < cnt; i += 4) {
-        const KFrag g0 = load_entry(sA, sB, entry_of(ew, 2));
-        const KFrag g1 = load_entry(sA, sB, entry_of(ew, 3));
-        fma_listed_pair(acc, f0, f1, entry_of(ew, 0), entry_of(ew, 1));
-        const uint2 en = *reinterpret_cast<const uint2 *>(list + i + 4);   // padded: always readable
-        f0 = load_entry(sA, sB, entry_of(en, 0));
-        f1 = load_entry(sA, sB, entry_of(en, 1));
-        fma_listed_pair(acc, g0, g1, entry_of(ew, 2), entry_of(ew, 3));
-        ew = en;
+    for (int i = 0; i < n4; i += 4) {
+        const KFrag g0 = load_entry<MODE>(sA, sB, entry_of(ew, 2));
+        const KFrag g1 = load_entry<MODE>(sA, sB, entry_of(ew, 3));
+        fma_entry<MODE>(acc, f0);
+        fma_entry<MODE>(acc, f1);
+        ew = *reinterpret_cast<const uint2 *>(list + i + 4);   // padded: always readable
+        f0 = load_entry<MODE>(sA, sB, entry_of(ew, 0));
+        f1 = load_entry<MODE>(sA, sB, entry_of(ew, 1));
+        fma_entry<MODE>(acc, g0);
+        fma_entry<MODE>(acc, g1);
     }
+    // up to three rows are left; f0, f1 already hold the first two of them (or padding)
+    const int rem = cnt - n4;
+    if (rem >= 1) fma_entry<MODE>(acc, f0);
+    if (rem >= 2) fma_entry<MODE>(acc, f1);
+    if (rem == 3) fma_entry<MODE>(acc, load_entry<MODE>(sA, sB, entry_of(ew, 2)));
+}
+
+// Lanes write the list of the rows whose bit is set in `m`; returns the count.
+__device__ __forceinline__ int build_list(uint16_t *list, unsigned m, int lane)
+{
+    const int cnt = __popc(m);
+    if ((m >> lane) & 1u) list[__popc(m & ((1u << lane) - 1u))] = (uint16_t)(lane << 9);
+    if (lane < 8) list[cnt + lane] = 0;
+    return cnt;
+}
+
+// ---- mask warp helpers ---------------------------------------------------------------------------
+// Pattern bytes of 16 consecutive K blocks (kb0 .. kb0 + 15, all inside the matrix) for the tile's four
+// 32-row blocks and four 32-column blocks: one 16-byte load per pattern row.  aw[j] / bw[j] get the
+// four bytes of K block kb0 + j (byte i = block i).
+__device__ __forceinline__ void load_patterns16(const PackedParams &p, int tm, int tn, int kb0, bool valid,
+                                                unsigned (&aw)[16], unsigned (&bw)[16])
+{
+    uint4 ra[4], rb[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int mb = tm * 4 + i, nb = tn * 4 + i;
+        ra[i] = make_uint4(0u, 0u, 0u, 0u);
+        rb[i] = make_uint4(0u, 0u, 0u, 0u);
+        if (valid && mb < p.a_rows) ra[i] = *reinterpret_cast<const uint4 *>(p.a_pat + (size_t)mb * p.nKB + kb0);
+        if (valid && nb < p.b_rows) rb[i] = *reinterpret_cast<const uint4 *>(p.b_pat + (size_t)nb * p.nKB + kb0);
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+        const int sh = 8 * (j & 3);
+        unsigned a = 0, b = 0;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const unsigned wa = (j >> 2) == 0 ? ra[i].x : (j >> 2) == 1 ? ra[i].y : (j >> 2) == 2 ? ra[i].z : ra[i].w;
+            const unsigned wb = (j >> 2) == 0 ? rb[i].x : (j >> 2) == 1 ? rb[i].y : (j >> 2) == 2 ? rb[i].z : rb[i].w;
+            a |= ((wa >> sh) & 0xFFu) << (8 * i);
+            b |= ((wb >> sh) & 0xFFu) << (8 * i);
+        }
+        aw[j] = a;
+        bw[j] = b;
+    }
+}
+
+// k offsets of one K block that are live for the tile as a whole: (OR of the A bytes) & (OR of the B bytes)
+__device__ __forceinline__ unsigned tile_live(unsigned aw, unsigned bw)
+{
+    unsigned au = aw | (aw >> 16), bu = bw | (bw >> 16);
+    au = (au | (au >> 8)) & 0xFFu;
+    bu = (bu | (bu >> 8)) & 0xFFu;
+    return au & bu;
+}
+
+// Appends the listed rows of one K block at position q; returns the new position.
+__device__ __forceinline__ int append_rows(uint16_t *krow, uint8_t *rmask, int q, int kb, unsigned rows,
+                                           unsigned aw, unsigned bw)
+{
+    while (rows) {
+        const int kk = __ffs(rows) - 1;
+        rows &= rows - 1;
+        const unsigned as = aw >> kk, bs = bw >> kk;
+        const unsigned abits = (as & 1u) | ((as >> 7) & 2u) | ((as >> 14) & 4u) | ((as >> 21) & 8u);
+        const unsigned bbits = (bs & 1u) | ((bs >> 7) & 2u) | ((bs >> 14) & 4u) | ((bs >> 21) & 8u);
+        krow[q] = (uint16_t)(kb * BK + kk);
+        rmask[q] = (uint8_t)(abits | (bbits << 4));
+        ++q;
+    }
+    return q;
+}
+
+__device__ __forceinline__ int warp_inclusive_scan(int v, int lane)
+{
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int t = __shfl_up_sync(0xFFFFFFFFu, v, d);
+        if (lane >= d) v += t;
+    }
+    return v;
 }
 
 __global__ void __launch_bounds__(P_THREADS, 1)
@@ -265,6 +362,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
     __syncthreads();
 
     bool ok = true;
+    if (warp == 0) ESMM_STAMP(0);
 
     if (warp == P_MASK_WARP) {
         // ---------------- mask warp: the tile's list of live k rows ----------------
@@ -281,63 +379,85 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             unsigned live_first = 0;
             bool uniform = true;
             int live_total = 0;
-            for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
-                const int kb = kb0 + lane;
-                unsigned au = 0, bu = 0;
-                if (kb < p.nKB) {
+            if (p.vec_patterns) {
+                for (int c0 = 0; c0 < p.nKB; c0 += 512) {
+                    const int kb0 = c0 + 16 * lane;
+                    unsigned aw[16], bw[16];
+                    load_patterns16(p, tm, tn, kb0, kb0 < p.nKB, aw, bw);
+                    if (c0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, tile_live(aw[0], bw[0]), 0);
+                    bool same = true;
+                    int cnt = 0;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int mb = tm * 4 + i, nb = tn * 4 + i;
-                        if (mb < p.a_rows) au |= p.a_pat[(size_t)mb * p.nKB + kb];
-                        if (nb < p.b_rows) bu |= p.b_pat[(size_t)nb * p.nKB + kb];
+                    for (int j = 0; j < 16; ++j) {
+                        const unsigned live = tile_live(aw[j], bw[j]);
+                        same = same && live == live_first;
+                        cnt += __popc(live);
                     }
+                    uniform = uniform && __all_sync(0xFFFFFFFFu, kb0 >= p.nKB || same);
+                    live_total += __reduce_add_sync(0xFFFFFFFFu, cnt);
                 }
-                const unsigned live = au & bu;
-                if (kb0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, live, 0);
-                uniform = uniform && __all_sync(0xFFFFFFFFu, kb >= p.nKB || live == live_first);
-                live_total += __reduce_add_sync(0xFFFFFFFFu, __popc(live));
+            } else {
+                for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
+                    const int kb = kb0 + lane;
+                    unsigned au = 0, bu = 0;
+                    if (kb < p.nKB) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int mb = tm * 4 + i, nb = tn * 4 + i;
+                            if (mb < p.a_rows) au |= p.a_pat[(size_t)mb * p.nKB + kb];
+                            if (nb < p.b_rows) bu |= p.b_pat[(size_t)nb * p.nKB + kb];
+                        }
+                    }
+                    const unsigned live = au & bu;
+                    if (kb0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, live, 0);
+                    uniform = uniform && __all_sync(0xFFFFFFFFu, kb >= p.nKB || live == live_first);
+                    live_total += __reduce_add_sync(0xFFFFFFFFu, __popc(live));
+                }
             }
             // uniform tile: list live k only.  Otherwise single rows cost a copy each, which pays
             // only on sparse tiles (on average at most 2 live k per K block); denser tiles list
             // every live K block whole.
             const int whole_above = uniform ? BK : (live_total <= 2 * p.nKB ? p.brow_bits : 0);
             int pos = 0;
-            for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
-                const int kb = kb0 + lane;
-                unsigned aw = 0, bw = 0;  // byte i: pattern of the tile's i-th 32-row / 32-column block
-                if (kb < p.nKB) {
+            if (p.vec_patterns) {
+                // lane l owns K blocks c0 + 16 l .. c0 + 16 l + 15: consecutive lanes, consecutive K
+                for (int c0 = 0; c0 < p.nKB; c0 += 512) {
+                    const int kb0 = c0 + 16 * lane;
+                    unsigned aw[16], bw[16];
+                    load_patterns16(p, tm, tn, kb0, kb0 < p.nKB, aw, bw);
+                    unsigned rows[16];
+                    int c = 0;
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) {
-                        const int mb = tm * 4 + i, nb = tn * 4 + i;
-                        if (mb < p.a_rows) aw |= (unsigned)p.a_pat[(size_t)mb * p.nKB + kb] << (8 * i);
-                        if (nb < p.b_rows) bw |= (unsigned)p.b_pat[(size_t)nb * p.nKB + kb] << (8 * i);
+                    for (int j = 0; j < 16; ++j) {
+                        const unsigned live = tile_live(aw[j], bw[j]);
+                        rows[j] = live == 0u ? 0u : (__popc(live) > whole_above ? 0xFFu : live);
+                        c += __popc(rows[j]);
                     }
-                }
-                unsigned au = aw | (aw >> 16), bu = bw | (bw >> 16);
-                au = (au | (au >> 8)) & 0xFFu;
-                bu = (bu | (bu >> 8)) & 0xFFu;
-                const unsigned live = au & bu;                       // k live for the tile as a whole
-                unsigned rows = __popc(live) > whole_above ? 0xFFu : live;  // k rows to list
-                if (live == 0u) rows = 0u;
-                const int c = __popc(rows);
-                int incl = c;                                        // inclusive scan over the lanes
+                    const int incl = warp_inclusive_scan(c, lane);
+                    int q = pos + incl - c;
 #pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const int v = __shfl_up_sync(0xFFFFFFFFu, incl, d);
-                    if (lane >= d) incl += v;
+                    for (int j = 0; j < 16; ++j) q = append_rows(krow, rmask, q, kb0 + j, rows[j], aw[j], bw[j]);
+                    pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
                 }
-                int q = pos + incl - c;
-                while (rows) {
-                    const int kk = __ffs(rows) - 1;
-                    rows &= rows - 1;
-                    const unsigned as = aw >> kk, bs = bw >> kk;
-                    const unsigned abits = (as & 1u) | ((as >> 7) & 2u) | ((as >> 14) & 4u) | ((as >> 21) & 8u);
-                    const unsigned bbits = (bs & 1u) | ((bs >> 7) & 2u) | ((bs >> 14) & 4u) | ((bs >> 21) & 8u);
-                    krow[q] = (uint16_t)(kb * BK + kk);
-                    rmask[q] = (uint8_t)(abits | (bbits << 4));
-                    ++q;
+            } else {
+                for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
+                    const int kb = kb0 + lane;
+                    unsigned aw = 0, bw = 0;  // byte i: pattern of the tile's i-th 32-row / 32-column block
+                    if (kb < p.nKB) {
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int mb = tm * 4 + i, nb = tn * 4 + i;
+                            if (mb < p.a_rows) aw |= (unsigned)p.a_pat[(size_t)mb * p.nKB + kb] << (8 * i);
+                            if (nb < p.b_rows) bw |= (unsigned)p.b_pat[(size_t)nb * p.nKB + kb] << (8 * i);
+                        }
+                    }
+                    const unsigned live = tile_live(aw, bw);            // k live for the tile as a whole
+                    const unsigned rows = live == 0u ? 0u : (__popc(live) > whole_above ? 0xFFu : live);
+                    const int c = __popc(rows);
+                    const int incl = warp_inclusive_scan(c, lane);
+                    append_rows(krow, rmask, pos + incl - c, kb, rows, aw, bw);
+                    pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
                 }
-                pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
             }
             // rows past the end of the last stage read as dead
             {
@@ -350,6 +470,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             if (lane == 0) nrows[buf] = pos;
             __syncwarp();
             if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
+            if (it == 0) ESMM_STAMP(1);
         }
     } else if (warp == P_TMA_WARP) {
         // ---------------- TMA warp: one lane per row of the stage ----------------
@@ -412,6 +533,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 }
                 issued_bits |= 1u << slot;
                 parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
+                if (it == 0) ESMM_STAMP(400 + r0 / ROWS_PER_STAGE);
                 if (++slot == p.stages) {
                     slot = 0;
                     phase ^= 1;
@@ -438,7 +560,8 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
         const uint32_t a_thr = (uint32_t)(wm * 64 + lm * 4) * 4;                      // within a row of A
         const uint32_t b_thr = STAGE_HALF_BYTES + (uint32_t)(wn * 32 + ln * 4) * 4;  // within a row of B
         const int t_shift = 2 * wm, b_shift = 4 + wn;
-        uint16_t *wlist = reinterpret_cast<uint16_t *>(smem + L.wlist_off + warp * WLIST_BYTES);
+        uint16_t *wlist_t = reinterpret_cast<uint16_t *>(smem + L.wlist_off + warp * 2 * WLIST_BYTES);
+        uint16_t *wlist_b = wlist_t + WLIST_BYTES / 2;
         int slot = 0;
         uint32_t phase = 0;
         int it = 0;
@@ -467,24 +590,28 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 const unsigned jt = __ballot_sync(0xFFFFFFFFu, ((rm >> t_shift) & colb) != 0u);
                 const unsigned jb = __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u);
                 const bool dense = (jt & jb) == 0xFFFFFFFFu && !p.force_listed;
-                int live_cnt = 0;
+                int cnt_t = 0, cnt_b = 0;
                 if (!dense) {
-                    // my live rows as list entries, written by the lanes in parallel while the
-                    // stage's data may still be in flight
-                    const unsigned u = jt | jb;
-                    live_cnt = __popc(u);
-                    if ((u >> lane) & 1u)
-                        wlist[__popc(u & ((1u << lane) - 1u))] =
-                            (uint16_t)((lane << 9) | (((jt >> lane) & 1u) << 14) | (((jb >> lane) & 1u) << 15));
-                    if (lane < 8) wlist[live_cnt + lane] = 0;
+                    // my live rows as lists, written by the lanes in parallel while the stage's data
+                    // may still be in flight
+                    cnt_t = build_list(wlist_t, jt, lane);
+                    if (jt != jb) cnt_b = build_list(wlist_b, jb, lane);
                     __syncwarp();
                 }
                 ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
                 if (!ok) break;
                 const char *sA = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + a_thr;
                 const char *sB = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + b_thr;
-                if (dense) dense_rows(acc, sA, sB);
-                else listed_rows(acc, sA, sB, wlist, live_cnt);
+                if (warp == 0 && it == 0) ESMM_STAMP(10 + r0 / ROWS_PER_STAGE);
+                if (dense) {
+                    dense_rows(acc, sA, sB);
+                } else if (jt == jb) {
+                    listed_rows<MODE_BOTH>(acc, sA, sB, wlist_t, cnt_t);
+                } else {
+                    listed_rows<MODE_TOP>(acc, sA, sB, wlist_t, cnt_t);
+                    listed_rows<MODE_BOTTOM>(acc, sA, sB, wlist_b, cnt_b);
+                }
+                if (warp == 0 && it == 0) ESMM_STAMP(200 + r0 / ROWS_PER_STAGE);
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * slot);
                 if (++slot == p.stages) {
@@ -521,8 +648,16 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
         }
     }
 
+    if (warp == 0) ESMM_STAMP(5);
     if (!ok && lane == 0) atomicExch(p.status, (int)ESMM_ERR_TIMEOUT);
 }
+
+#ifdef ESMM_TRACE
+extern "C" int esmm_trace_read(unsigned long long *host, int n)
+{
+    return (int)cudaMemcpyFromSymbol(host, g_esmm_trace, sizeof(unsigned long long) * (n < 1024 ? n : 1024));
+}
+#endif
 
 int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                           const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream)
@@ -549,6 +684,8 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     if (p.brow_bits < 0) p.brow_bits = 0;
     if (p.brow_bits > 8) p.brow_bits = 8;
     p.force_listed = env_int("ESMM_FORCE_LISTED", 0);
+    p.vec_patterns = (p.nKB % 16 == 0) && (((uintptr_t)d_a_pat | (uintptr_t)d_b_pat) & 15) == 0 &&
+                     env_int("ESMM_VEC_PATTERNS", 1);
     p.a_pat = d_a_pat;
     p.b_pat = d_b_pat;
     p.C = d_C;

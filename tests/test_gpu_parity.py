@@ -425,3 +425,13 @@ def test_bounded_wait_reports_timeout_and_context_survives(cuda, pkg, oracle_mod
     assert L.esmm_selftest_bounded_wait(2_000_000, None) == pkg.ERR_SHAPE
     A, B = workloads.uniform_pattern(128, 128, 64, 0x0F, seed=3)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
+def test_gemm_mask_builder_paths_agree(cuda, pkg, oracle_mod, monkeypatch):
+    """The tile's row list is built from 16-byte pattern loads when the pattern rows allow it and
+    byte by byte otherwise; both must give the same C."""
+    A, B = workloads.tile_random(256, 384, 8192 + 128, 0.3, 0.5, seed=17, gran_a=32, gran_b=32)  # 1040 K blocks
+    monkeypatch.setenv("ESMM_VEC_PATTERNS", "0")
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    monkeypatch.setenv("ESMM_VEC_PATTERNS", "1")
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
