@@ -78,6 +78,8 @@ _SIGNATURES = {
     "esmm_parse_kernel_selection": (_i, [C.c_char_p, C.POINTER(_i), _i]),
     "esmm_run_kernel": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, C.POINTER(_i),
                              C.POINTER(_f)]),
+    "esmm_run_kernel_cached_b": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, C.POINTER(_i),
+                                      C.POINTER(_f)]),
 }
 
 _lib = None

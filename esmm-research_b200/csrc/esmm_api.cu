@@ -660,6 +660,14 @@ int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, f
                     float *h_C, const float *h_C_ref, int runs, int verify, int print_stats, int *passed,
                     float *avg_ms)
 {
+    return esmm_run_kernel_cached_b(kernel_id, rows, cols, inners, d_A, d_B, d_C, h_C, h_C_ref, runs, verify,
+                                    print_stats, nullptr, passed, avg_ms);
+}
+
+int esmm_run_kernel_cached_b(int kernel_id, int rows, int cols, int inners, float *d_A, float *d_B, float *d_C,
+                             float *h_C, const float *h_C_ref, int runs, int verify, int print_stats,
+                             const uint8_t *d_b_pat_cached, int *passed, float *avg_ms)
+{
     if (passed) *passed = 0;
     if (avg_ms) *avg_ms = 0.f;
     if (!esmm_kernel_id_valid(kernel_id)) return ESMM_ERR_UNSUPPORTED;
@@ -689,7 +697,7 @@ int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, f
     } else {
         if (print_stats) {
             esmm_ab_pattern_metadata meta;
-            st = esmm_preprocess_ab(d_A, d_B, rows, cols, inners, a_tile, nullptr, &meta);
+            st = esmm_preprocess_ab(d_A, d_B, rows, cols, inners, a_tile, d_b_pat_cached, &meta);
             if (st == ESMM_OK) {
                 std::vector<uint8_t> ha((size_t)meta.numMBlocks * meta.numKBlocks),
                     hb((size_t)meta.numNBlocks * meta.numKBlocks);
@@ -720,7 +728,7 @@ int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, f
         for (int i = 0; i < runs && st == ESMM_OK; ++i) {
             cudaMemset(d_C, 0, (size_t)rows * cols * sizeof(float));
             esmm_ab_pattern_metadata meta;
-            st = esmm_preprocess_ab(d_A, d_B, rows, cols, inners, a_tile, nullptr, &meta);
+            st = esmm_preprocess_ab(d_A, d_B, rows, cols, inners, a_tile, d_b_pat_cached, &meta);
             if (st != ESMM_OK) break;
             if (d_packed) {
                 st = esmm::preprocess_a_pack_launch(d_A, rows, inners, meta.d_a_patterns, d_packed, 0);

@@ -18,6 +18,9 @@
 //   --seed S             seed of the two modes above (A uses S, B uses S + 1)
 //   --cpu-check          also compare C with the driver's CPU SGEMM (matrixMultiplyCPU, all host
 //                        threads, relative inf-norm tolerance 1e-4)
+//   --cache-b            keep B's pattern bytes in "<load-b file>.bpat" (or the file given with
+//                        --cache-b-file): loaded when present and matching, else computed once
+//                        and saved; the timed loop then preprocesses A only ("B offline")
 //   --json               one machine-readable line per kernel
 #include <algorithm>
 #include <cctype>
@@ -70,6 +73,8 @@ void print_usage(const char *prog)
     cout << "  --tile-random pA pB N(0,1) values, independent 64-row / 64-column tile patterns" << endl;
     cout << "  --seed <S>          Seed for --uniform / --tile-random" << endl;
     cout << "  --cpu-check         Also verify against the CPU SGEMM (rel-inf tolerance 1e-4)" << endl;
+    cout << "  --cache-b           Cache B's pattern bytes next to the --load-b file (<file>.bpat)" << endl;
+    cout << "  --cache-b-file <f>  Cache B's pattern bytes in <f>" << endl;
     cout << "  --json              One JSON line per kernel" << endl;
     cout << "  --help, -h          Show this help message" << endl;
     cout << "\nExamples:" << endl;
@@ -166,7 +171,8 @@ struct Options {
     std::vector<int> kernels = {29};
     int runs = 1;
     bool verbose = false, check = true, random_mode = false, blockwise = false, skip_stats = false;
-    bool uniform = false, tile_random = false, cpu_check = false, json = false;
+    bool uniform = false, tile_random = false, cpu_check = false, json = false, cache_b = false;
+    std::string cache_b_file;
     float p_a = 0.5f, p_b = 0.5f;
     unsigned seed = 12345;
     float random_sparsity = 37.5f;
@@ -199,6 +205,12 @@ int parse_args(int argc, char **argv, Options &o)
         else if (a == "--uniform") o.uniform = true;
         else if (a == "--cpu-check") o.cpu_check = true;
         else if (a == "--json") o.json = true;
+        else if (a == "--cache-b") o.cache_b = true;
+        else if (a == "--cache-b-file") {
+            if (!need(i, 1, "--cache-b-file requires a path")) return 1;
+            o.cache_b = true;
+            o.cache_b_file = argv[++i];
+        }
         else if (a == "--size" || a == "-s") {
             if (!need(i, 1, "--size requires an argument")) {
                 print_usage(argv[0]);
@@ -382,6 +394,35 @@ int main(int argc, char **argv)
         cout << "Skipping reference solution (no-check mode)..." << endl;
     }
 
+    // B pattern cache: the patterns of a static B are computed once and reused.
+    uint8_t *d_b_cached = nullptr;
+    if (o.cache_b) {
+        std::string path = o.cache_b_file;
+        if (path.empty() && !o.load_b.empty()) path = o.load_b + ".bpat";
+        if (path.empty()) {
+            cout << "Error: --cache-b needs --load-b or --cache-b-file" << endl;
+            return 1;
+        }
+        const size_t nb = esmm_b_pattern_bytes(K, N);
+        std::vector<uint8_t> h_bpat(nb);
+        cudaCheckError(cudaMalloc(&d_b_cached, nb));
+        int st = esmm_bpat_load(path.c_str(), h_bpat.data(), K, N);
+        if (st == ESMM_OK) {
+            cudaCheckError(cudaMemcpy(d_b_cached, h_bpat.data(), nb, cudaMemcpyHostToDevice));
+            cout << "B patterns: loaded from " << path << endl;
+        } else {
+            if (st == ESMM_ERR_MISMATCH) cout << "B patterns: " << path << " was written for another shape, recomputing" << endl;
+            st = esmm_preprocess_b(d_B, K, N, d_b_cached, nullptr);
+            if (st != ESMM_OK || cudaDeviceSynchronize() != cudaSuccess) {
+                cout << "Error: B preprocessing failed: " << esmm_strerror(st) << endl;
+                return 1;
+            }
+            cudaCheckError(cudaMemcpy(h_bpat.data(), d_b_cached, nb, cudaMemcpyDeviceToHost));
+            st = esmm_bpat_save(path.c_str(), h_bpat.data(), K, N);
+            cout << "B patterns: computed" << (st == ESMM_OK ? " and saved to " : "; could not write ") << path << endl;
+        }
+    }
+
     std::vector<float> h_cpu;
     if (o.cpu_check) {
         h_cpu.resize(nC);
@@ -396,8 +437,9 @@ int main(int argc, char **argv)
         int ok_flag = 0;
         float avg_ms = 0.f;
         const bool need_c = o.check || o.cpu_check;
-        int st = esmm_run_kernel(id, M, N, K, d_A, d_B, d_C, need_c ? h_C : nullptr, o.check ? h_C_ref : nullptr, o.runs,
-                                 o.check && id != 15 ? 1 : 0, o.skip_stats ? 1 : 0, &ok_flag, &avg_ms);
+        int st = esmm_run_kernel_cached_b(id, M, N, K, d_A, d_B, d_C, need_c ? h_C : nullptr, o.check ? h_C_ref : nullptr,
+                                          o.runs, o.check && id != 15 ? 1 : 0, o.skip_stats ? 1 : 0, d_b_cached, &ok_flag,
+                                          &avg_ms);
         bool res = (st == ESMM_OK) && ok_flag;
         if (st == ESMM_ERR_UNSUPPORTED) cout << "Kernel " << id << " is not provided by this library (joint-sparse ids and cuBLAS only)" << endl;
         double cpu_rel = -1.0;
@@ -436,5 +478,6 @@ int main(int argc, char **argv)
     cudaFree(d_A);
     cudaFree(d_B);
     cudaFree(d_C);
+    if (d_b_cached) cudaFree(d_b_cached);
     return passed == total ? 0 : 1;
 }

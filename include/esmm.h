@@ -268,6 +268,17 @@ int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, f
                     float *d_C, float *h_C, const float *h_C_ref, int runs, int verify,
                     int print_skip_stats, int *passed, float *avg_ms);
 
+/*
+ * Same runner with the B patterns supplied by the caller (device array of esmm_b_pattern_bytes(K, N)
+ * bytes, e.g. uploaded from an esmm_bpat_load() file): the timed loop then preprocesses A only.  This
+ * is the "B offline, A per call" mode the reference describes (README.md:46,103) but never runs - its
+ * runner recomputes B patterns in every iteration (include/runners.cuh:859).  NULL = recompute.
+ */
+int esmm_run_kernel_cached_b(int kernel_id, int rows, int cols, int inners, float *d_A, float *d_B,
+                             float *d_C, float *h_C, const float *h_C_ref, int runs, int verify,
+                             int print_skip_stats, const uint8_t *d_b_pat_cached, int *passed,
+                             float *avg_ms);
+
 #ifdef __cplusplus
 }
 #endif

@@ -87,3 +87,26 @@ def test_load_raw_weights(pkg, cuda, tmp_path):
 def test_single_operand_ids_fail_cleanly(pkg, cuda):
     rc, out = run(pkg, "17,29", "1", "--size", "256")
     assert rc == 1 and "Summary: 1/2 kernels passed" in out and "not provided by this library" in out
+
+
+@pytest.mark.gpu
+def test_b_pattern_cache_file(pkg, cuda, tmp_path):
+    """--cache-b: first run computes and saves <weights>.bpat, the second loads it; a file written for
+    another shape is recomputed.  The saved bytes equal the oracle's B patterns."""
+    import oracle
+    M, K, N = 128, 256, 384
+    rng = np.random.default_rng(1)
+    B = rng.standard_normal((K, N), dtype=np.float32)
+    B[(np.arange(K) % 8) >= 3] = 0.0
+    path = tmp_path / "w.bin"
+    B.tofile(path)
+    args = ("29", "2", "--load-b", str(path), "--dims", str(M), str(K), str(N), "--cache-b")
+    rc, out = run(pkg, *args)
+    assert rc == 0 and "B patterns: computed and saved to" in out and "PASSED" in out
+    raw = (tmp_path / "w.bin.bpat").read_bytes()
+    assert raw[:8] == b"ESMMBPT1"
+    assert np.array_equal(np.frombuffer(raw[32:], np.uint8).reshape(N // 32, K // 8), oracle.preprocess_b(B))
+    rc, out = run(pkg, *args)
+    assert rc == 0 and "B patterns: loaded from" in out and "PASSED" in out
+    rc, out = run(pkg, "29", "1", "--load-b", str(path), "--dims", str(M), str(K // 2), str(2 * N), "--cache-b")
+    assert "written for another shape, recomputing" in out
