@@ -80,6 +80,8 @@ _SIGNATURES = {
                              C.POINTER(_f)]),
     "esmm_run_kernel_cached_b": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, C.POINTER(_i),
                                       C.POINTER(_f)]),
+    "esmm_run_kernel_pattern": (_i, [_i, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, C.c_char_p,
+                                     C.POINTER(_i), C.POINTER(_f)]),
 }
 
 _lib = None

@@ -660,21 +660,38 @@ int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, f
                     float *h_C, const float *h_C_ref, int runs, int verify, int print_stats, int *passed,
                     float *avg_ms)
 {
-    return esmm_run_kernel_cached_b(kernel_id, rows, cols, inners, d_A, d_B, d_C, h_C, h_C_ref, runs, verify,
-                                    print_stats, nullptr, passed, avg_ms);
+    return esmm_run_kernel_pattern(kernel_id, rows, cols, inners, d_A, d_B, d_C, h_C, h_C_ref, runs, verify,
+                                   print_stats, nullptr, nullptr, passed, avg_ms);
 }
 
 int esmm_run_kernel_cached_b(int kernel_id, int rows, int cols, int inners, float *d_A, float *d_B, float *d_C,
                              float *h_C, const float *h_C_ref, int runs, int verify, int print_stats,
                              const uint8_t *d_b_pat_cached, int *passed, float *avg_ms)
 {
+    return esmm_run_kernel_pattern(kernel_id, rows, cols, inners, d_A, d_B, d_C, h_C, h_C_ref, runs, verify,
+                                   print_stats, d_b_pat_cached, nullptr, passed, avg_ms);
+}
+
+int esmm_run_kernel_pattern(int kernel_id, int rows, int cols, int inners, float *d_A, float *d_B, float *d_C,
+                            float *h_C, const float *h_C_ref, int runs, int verify, int print_stats,
+                            const uint8_t *d_b_pat_cached, const char *pattern, int *passed, float *avg_ms)
+{
     if (passed) *passed = 0;
     if (avg_ms) *avg_ms = 0.f;
     if (!esmm_kernel_id_valid(kernel_id)) return ESMM_ERR_UNSUPPORTED;
     if (!d_A || !d_B || !d_C || (verify && (!h_C || !h_C_ref))) return ESMM_ERR_NULL;
     if (rows <= 0 || cols <= 0 || inners <= 0 || runs <= 0) return ESMM_ERR_SHAPE;
-    const int a_tile = esmm::a_tile_for_kernel(kernel_id);
+    const bool single_operand = kernel_id == 14 || kernel_id == 16 || kernel_id == 17;
+    const int a_tile = single_operand ? 32 : esmm::a_tile_for_kernel(kernel_id);
     if (kernel_id != 15 && a_tile == 0) return ESMM_ERR_UNSUPPORTED;
+    // Id 14 takes its live k from the pattern string, not from the data: the first popcount(pattern)
+    // k of every 8-slice (include/runners.cuh:47-66; the unrolled kernels exist for 1, 2, 4, 6, 8).
+    int prefix = 0;
+    if (kernel_id == 14) {
+        const char *pat = pattern ? pattern : "11111111";
+        if (strlen(pat) != 8) return ESMM_ERR_SHAPE;
+        for (int i = 0; i < 8; ++i) prefix += pat[i] == '1';
+    }
 
     cudaEvent_t start, stop;
     ESMM_CUDA_TRY(cudaEventCreate(&start));
@@ -695,7 +712,7 @@ int esmm_run_kernel_cached_b(int kernel_id, int rows, int cols, int inners, floa
         cudaEventSynchronize(stop);
         cublasDestroy(handle);
     } else {
-        if (print_stats) {
+        if (print_stats && !single_operand) {
             esmm_ab_pattern_metadata meta;
             st = esmm_preprocess_ab(d_A, d_B, rows, cols, inners, a_tile, d_b_pat_cached, &meta);
             if (st == ESMM_OK) {
@@ -720,13 +737,54 @@ int esmm_run_kernel_cached_b(int kernel_id, int rows, int cols, int inners, floa
         // buffer allocated once per runner call (the pattern arrays are allocated per run, as
         // in the reference loop).
         float *d_packed = nullptr;
-        if (a_tile == 32 && st == ESMM_OK) {
+        if (a_tile == 32 && kernel_id != 14 && st == ESMM_OK) {
             cudaError_t e = cudaMalloc(&d_packed, esmm_a_packed_bytes(rows, inners));
             if (e != cudaSuccess) st = esmm::record_cuda_error(e, "cudaMalloc(packed A)");
+        }
+        const size_t a_bytes = esmm_a_pattern_bytes(rows, inners, 32), b_bytes = esmm_b_pattern_bytes(inners, cols);
+        uint8_t *d_fixed_a = nullptr, *d_fixed_b = nullptr;
+        if (kernel_id == 14 && st == ESMM_OK) {
+            // no preprocessing inside the loop: both pattern arrays are constants of the call
+            cudaError_t e = cudaMalloc(&d_fixed_a, a_bytes);
+            if (e == cudaSuccess) e = cudaMalloc(&d_fixed_b, b_bytes);
+            if (e == cudaSuccess) e = cudaMemset(d_fixed_a, (1 << prefix) - 1, a_bytes);
+            if (e == cudaSuccess) e = cudaMemset(d_fixed_b, 0xFF, b_bytes);
+            if (e != cudaSuccess) st = esmm::record_cuda_error(e, "pattern constants for id 14");
         }
         cudaEventRecord(start);
         for (int i = 0; i < runs && st == ESMM_OK; ++i) {
             cudaMemset(d_C, 0, (size_t)rows * cols * sizeof(float));
+            if (kernel_id == 14) {
+                // the reference launches nothing for other counts and leaves C zeroed
+                if (prefix == 1 || prefix == 2 || prefix == 4 || prefix == 6 || prefix == 8)
+                    st = esmm::gemm_ab_launch(rows, cols, inners, d_A, d_B, d_C, d_fixed_a, d_fixed_b, 32, 0);
+                continue;
+            }
+            if (kernel_id == 16 || kernel_id == 17) {
+                // One operand's patterns per run (analyze_sparsity_pattern_gpu / analyze_b_sparsity_warp_
+                // granularity + free, include/runners.cuh:172-178, 236-242); the other operand counts as
+                // all live.  For id 17 the packing pass still leaves out 32-row blocks of A that are all
+                // zero at some k; that drops only terms that are exactly zero.
+                uint8_t *d_ap = nullptr, *d_bp = nullptr;
+                cudaError_t e = cudaMalloc(&d_ap, a_bytes);
+                if (e == cudaSuccess) e = cudaMalloc(&d_bp, b_bytes);
+                if (e != cudaSuccess) st = esmm::record_cuda_error(e, "cudaMalloc(patterns)");
+                if (st == ESMM_OK) {
+                    if (kernel_id == 16) {
+                        e = cudaMemsetAsync(d_bp, 0xFF, b_bytes, 0);
+                        if (e != cudaSuccess) st = esmm::record_cuda_error(e, "cudaMemsetAsync(B patterns)");
+                    } else {
+                        st = esmm_preprocess_b(d_B, inners, cols, d_bp, 0);
+                    }
+                }
+                if (st == ESMM_OK) st = esmm::preprocess_a_pack_launch(d_A, rows, inners, d_ap, d_packed, 0);
+                if (st == ESMM_OK)
+                    st = esmm::gemm_ab_packed_launch(rows, cols, inners, d_packed, d_B, d_C, d_ap, d_bp, 0);
+                cudaDeviceSynchronize();
+                cudaFree(d_ap);
+                cudaFree(d_bp);
+                continue;
+            }
             esmm_ab_pattern_metadata meta;
             st = esmm_preprocess_ab(d_A, d_B, rows, cols, inners, a_tile, d_b_pat_cached, &meta);
             if (st != ESMM_OK) break;
@@ -745,6 +803,8 @@ int esmm_run_kernel_cached_b(int kernel_id, int rows, int cols, int inners, floa
         cudaEventRecord(stop);
         cudaEventSynchronize(stop);
         if (d_packed) cudaFree(d_packed);
+        if (d_fixed_a) cudaFree(d_fixed_a);
+        if (d_fixed_b) cudaFree(d_fixed_b);
     }
 
     float ms = 0.f;

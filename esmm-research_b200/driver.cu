@@ -8,8 +8,8 @@
 //
 // kernels: "29", "29,15", "14-17", "all"; data modes, seeds (12345 / 12346), messages, the cuBLAS
 // verification reference with absolute tolerance 1e-2 and the exit code (0 iff every selected
-// kernel passed) follow the reference.  Differences: the default kernel is 29 (the reference's
-// default, 17, is a B-only kernel outside this library), and ids 14, 16, 17 report FAILED.
+// kernel passed) follow the reference.  Difference: the default kernel is 29 (the reference's
+// default is 17).  The single-operand ids 14, 16, 17 run as degenerate cases of the joint kernel.
 //
 // Additive flags for the inputs the reference CLI cannot express:
 //   --uniform            N(0,1) values, the pattern applied to A's K columns AND B's K rows of every
@@ -437,11 +437,11 @@ int main(int argc, char **argv)
         int ok_flag = 0;
         float avg_ms = 0.f;
         const bool need_c = o.check || o.cpu_check;
-        int st = esmm_run_kernel_cached_b(id, M, N, K, d_A, d_B, d_C, need_c ? h_C : nullptr, o.check ? h_C_ref : nullptr,
-                                          o.runs, o.check && id != 15 ? 1 : 0, o.skip_stats ? 1 : 0, d_b_cached, &ok_flag,
-                                          &avg_ms);
+        int st = esmm_run_kernel_pattern(id, M, N, K, d_A, d_B, d_C, need_c ? h_C : nullptr, o.check ? h_C_ref : nullptr,
+                                         o.runs, o.check && id != 15 ? 1 : 0, o.skip_stats ? 1 : 0, d_b_cached,
+                                         o.pattern.c_str(), &ok_flag, &avg_ms);
         bool res = (st == ESMM_OK) && ok_flag;
-        if (st == ESMM_ERR_UNSUPPORTED) cout << "Kernel " << id << " is not provided by this library (joint-sparse ids and cuBLAS only)" << endl;
+        if (st == ESMM_ERR_UNSUPPORTED) cout << "Kernel " << id << " is not provided by this library" << endl;
         double cpu_rel = -1.0;
         if (o.cpu_check && st == ESMM_OK) {
             if (!o.check) cudaCheckError(cudaMemcpy(h_C, d_C, nC * sizeof(float), cudaMemcpyDeviceToHost));

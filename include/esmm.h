@@ -261,8 +261,10 @@ int esmm_parse_kernel_selection(const char *selection, int *ids, int cap);
  * run_esmm_ab_optimized_v3 / _no_check (runners.cuh:827-897), run_cuBlas
  * (:109-144) and the `switch` of run_single_kernel (driver.cu:40-129).
  * Ids served: 15 (cuBLAS), 29, and the joint-sparse ids 20, 21, 25, 26, 27, 28, 30
- * as aliases of the same kernel at their own A granularity.  Ids 14, 16, 17 return
- * ESMM_ERR_UNSUPPORTED.  *passed gets 1/0; *avg_ms the average time per run.
+ * as aliases of the same kernel at their own A granularity; the single-operand ids
+ * 16 (A patterns only, B all live), 17 (B patterns only) and 14 (see
+ * esmm_run_kernel_pattern) as degenerate cases of it.  *passed gets 1/0; *avg_ms the
+ * average time per run.
  */
 int esmm_run_kernel(int kernel_id, int rows, int cols, int inners, float *d_A, float *d_B,
                     float *d_C, float *h_C, const float *h_C_ref, int runs, int verify,
@@ -278,6 +280,19 @@ int esmm_run_kernel_cached_b(int kernel_id, int rows, int cols, int inners, floa
                              float *d_C, float *h_C, const float *h_C_ref, int runs, int verify,
                              int print_skip_stats, const uint8_t *d_b_pat_cached, int *passed,
                              float *avg_ms);
+
+/*
+ * The general form: d_b_pat_cached as above, and the driver's 8-character pattern string, which only
+ * id 14 reads.  run_esmm_unrolled (include/runners.cuh:30-106) never looks at the data: it multiplies the
+ * first popcount(pattern) k of every 8-slice of K - the unrolled kernels exist for 1, 2, 4, 6 and 8 live
+ * k; for any other count the reference launches nothing and C stays zero, and so does this.  Here that is
+ * the joint kernel with every A pattern byte = (1 << popcount) - 1 and every B byte 0xFF, no
+ * preprocessing in the loop.  pattern == NULL means "11111111".  Other ids ignore the string.
+ */
+int esmm_run_kernel_pattern(int kernel_id, int rows, int cols, int inners, float *d_A, float *d_B,
+                            float *d_C, float *h_C, const float *h_C_ref, int runs, int verify,
+                            int print_skip_stats, const uint8_t *d_b_pat_cached, const char *pattern,
+                            int *passed, float *avg_ms);
 
 #ifdef __cplusplus
 }

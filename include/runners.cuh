@@ -8,6 +8,7 @@
 //   run_esmm_ab_optimized_v3 (+ 9-argument overload, _no_check)   include/runners.cuh:827-897
 //   run_cuBlas, run_cuBlas_no_check                                 include/runners.cuh:109-144
 //   the other joint-sparse runners (ids 20, 21, 25, 26, 27, 28, 30) include/runners.cuh:278-995
+//   the single-operand runners (ids 14, 16, 17)                     include/runners.cuh:30-106, 150-275
 //   preprocess_ab<BK, TILE_M_A, WN>, ABPatternMetadata,
 //   free_ab_pattern_metadata                                        src/preprocessors/ab_preprocessor.cu:7-24, 297-326
 //   parse_kernel_selection, get_kernel_name, verifyResults,
@@ -156,3 +157,40 @@ ESMM_DEFINE_RUNNER(run_esmm_ab_optimized_v2_baseline, 27)
 ESMM_DEFINE_RUNNER(run_esmm_ab_gmem_32, 28)
 ESMM_DEFINE_RUNNER(run_esmm_ab_compressed_k, 30)
 #undef ESMM_DEFINE_RUNNER
+
+// The single-operand ids (include/runners.cuh:30-106, 150-211, 214-275): the reference's argument lists,
+// which have no skip-stats flag; id 14 also takes the driver's pattern string.
+inline bool run_esmm_a_sparse_blockwise(int rows, int cols, int inners, float *d_A, float *d_B, float *d_C,
+                                        float *h_C, float *h_C_ref, int runs, bool verify = true)
+{
+    return esmm_runner_detail::run(16, rows, cols, inners, d_A, d_B, d_C, h_C, h_C_ref, runs, verify, false);
+}
+inline bool run_esmm_a_sparse_blockwise_no_check(int rows, int cols, int inners, float *d_A, float *d_B,
+                                                 float *d_C, int runs)
+{
+    return run_esmm_a_sparse_blockwise(rows, cols, inners, d_A, d_B, d_C, nullptr, nullptr, runs, false);
+}
+inline bool run_esmm_b_sparse_warp(int rows, int cols, int inners, float *d_A, float *d_B, float *d_C,
+                                   float *h_C, float *h_C_ref, int runs, bool verify = true)
+{
+    return esmm_runner_detail::run(17, rows, cols, inners, d_A, d_B, d_C, h_C, h_C_ref, runs, verify, false);
+}
+inline bool run_esmm_b_sparse_warp_no_check(int rows, int cols, int inners, float *d_A, float *d_B,
+                                            float *d_C, int runs)
+{
+    return run_esmm_b_sparse_warp(rows, cols, inners, d_A, d_B, d_C, nullptr, nullptr, runs, false);
+}
+inline bool run_esmm_unrolled(int rows, int cols, int inners, float *d_A, float *d_B, float *d_C, float *h_C,
+                              float *h_C_ref, int runs, std::string_view pattern, bool verify = true)
+{
+    int passed = 0;
+    const std::string pat(pattern);
+    const int st = esmm_run_kernel_pattern(14, rows, cols, inners, d_A, d_B, d_C, h_C, h_C_ref, runs, verify ? 1 : 0,
+                                           0, nullptr, pat.c_str(), &passed, nullptr);
+    return st == ESMM_OK && passed != 0;
+}
+inline bool run_esmm_unrolled_no_check(int rows, int cols, int inners, float *d_A, float *d_B, float *d_C,
+                                       int runs, std::string_view pattern)
+{
+    return run_esmm_unrolled(rows, cols, inners, d_A, d_B, d_C, nullptr, nullptr, runs, pattern, false);
+}

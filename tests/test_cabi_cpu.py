@@ -48,7 +48,8 @@ def test_argument_validation_needs_no_device(pkg):
     assert L.esmm_sgemm_joint(128, 128, 128, ok_ptr, ok_ptr, ok_ptr, ok_ptr, ok_ptr + 16, 0) == pkg.ERR_ALIGN
     assert L.esmm_run_kernel(29, 128, 128, 128, 0, 0, 0, 0, 0, 1, 0, 0, None, None) == pkg.ERR_NULL
     assert L.esmm_run_kernel(33, 128, 128, 128, ok_ptr, ok_ptr, ok_ptr, 0, 0, 1, 0, 0, None, None) == pkg.ERR_UNSUPPORTED
-    assert L.esmm_run_kernel(17, 128, 128, 128, ok_ptr, ok_ptr, ok_ptr, 0, 0, 1, 0, 0, None, None) == pkg.ERR_UNSUPPORTED
+    assert L.esmm_run_kernel_pattern(14, 128, 128, 128, ok_ptr, ok_ptr, ok_ptr, 0, 0, 1, 0, 0, None, b"1111", None,
+                                     None) == pkg.ERR_SHAPE
     assert L.esmm_interleave_shards(ok_ptr, ok_ptr, 8, 12, 2, 0) == pkg.ERR_SHAPE
     for st in range(11):
         assert L.esmm_strerror(st)

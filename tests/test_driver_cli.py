@@ -84,9 +84,14 @@ def test_load_raw_weights(pkg, cuda, tmp_path):
 
 
 @pytest.mark.gpu
-def test_single_operand_ids_fail_cleanly(pkg, cuda):
-    rc, out = run(pkg, "17,29", "1", "--size", "256")
-    assert rc == 1 and "Summary: 1/2 kernels passed" in out and "not provided by this library" in out
+def test_single_operand_ids(pkg, cuda):
+    """Ids 14, 16, 17 run through the joint kernel: default column-pattern data (A's K columns masked by
+    the pattern, which is what id 14 assumes), verified against cuBLAS like the reference driver does."""
+    rc, out = run(pkg, "14-17", "2", "--size", "256", "--pattern", "11110000")
+    assert rc == 0 and "Summary: 4/4 kernels passed" in out, out
+    # id 14 has kernels for 1, 2, 4, 6, 8 live k only: with 3 nothing is launched and C stays zero
+    rc, out = run(pkg, "14", "1", "--size", "256", "--pattern", "11100000")
+    assert rc == 1 and "Verification failed" in out and "Summary: 0/1 kernels passed" in out
 
 
 @pytest.mark.gpu

@@ -341,11 +341,49 @@ def test_run_kernel_ids(cuda, pkg, oracle_mod, capfd):
         assert oracle_mod.rel_inf_err(h_c, h_ref) <= TOL
     out = capfd.readouterr().out
     assert out.count("Kernel time:") == 9 and "=== Skip Stats: K29 ===" in out
+    # single-operand ids: 16 (A patterns, B all live) and 17 (B patterns) give the joint kernel's bits
+    h_29 = h_c.copy()
+    for kid in (16, 17):
+        st = L.esmm_run_kernel(kid, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), h_c.ctypes.data,
+                               h_ref.ctypes.data, 1, 1, 0, C.byref(passed), C.byref(avg))
+        assert st == 0 and passed.value == 1, kid
+        assert np.array_equal(h_c, h_29), kid
+    capfd.readouterr()
     h_bad = h_ref + 1.0
     st = L.esmm_run_kernel(29, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), h_c.ctypes.data,
                            h_bad.ctypes.data, 1, 1, 0, C.byref(passed), C.byref(avg))
     assert st == pkg.ERR_VERIFY and passed.value == 0
     assert "Verification failed" in capfd.readouterr().out
+
+
+def test_run_kernel_prefix_pattern(cuda, pkg, oracle_mod, capfd):
+    """Id 14 multiplies the first popcount(pattern) k of every 8-slice whatever the data holds
+    (include/runners.cuh:47-66): on a dense A the result is the product with A's other columns dropped."""
+    M, N, K = 256, 384, 512
+    rng = np.random.default_rng(77)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    B = rng.standard_normal((K, N), dtype=np.float32)
+    dA, dB = cuda.from_numpy(A).cuda(), cuda.from_numpy(B).cuda()
+    dC = cuda.zeros((M, N), device="cuda")
+    L = pkg.lib()
+    passed, avg = C.c_int(0), C.c_float(0)
+    for pat, live in ((b"11110000", 4), (b"10000001", 2), (b"11111111", 8), (b"00000001", 1), (b"11101110", 6)):
+        st = L.esmm_run_kernel_pattern(14, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), None, None, 1, 0, 0,
+                                       None, pat, C.byref(passed), C.byref(avg))
+        assert st == 0 and passed.value == 1
+        Am = A.copy()
+        Am[:, (np.arange(K) % 8) >= live] = 0.0
+        a_pat = np.full((M // 32, K // 8), (1 << live) - 1, np.uint8)
+        b_pat = np.full((N // 32, K // 8), 0xFF, np.uint8)
+        assert np.array_equal(dC.cpu().numpy(), oracle_mod.gemm_joint(A, B, a_pat, b_pat)), pat
+        assert oracle_mod.rel_inf_err(dC.cpu().numpy(), oracle_mod.sgemm_f64(Am, B)) <= TOL
+    # a count without an unrolled kernel: nothing runs, C stays zero
+    st = L.esmm_run_kernel_pattern(14, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), None, None, 1, 0, 0,
+                                   None, b"11100000", C.byref(passed), C.byref(avg))
+    assert st == 0 and float(dC.abs().max()) == 0.0
+    assert L.esmm_run_kernel_pattern(14, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), None, None, 1, 0, 0,
+                                     None, b"111", C.byref(passed), C.byref(avg)) == pkg.ERR_SHAPE
+    capfd.readouterr()
 
 
 def test_plan_host_buffers(cuda, pkg, oracle_mod):
