@@ -28,9 +28,9 @@
 //     pattern row; a thread holds 8 x 8 outputs, 4 rows in each 32-row block).  Per stage a
 //     warp forms its two 32-bit joint masks with two ballots.  If every row of the stage is
 //     live for both row blocks - always the case for uniform patterns, at any density - it
-//     runs straight-line code (4 sixteen-byte loads and 64 FFMA per k).  Otherwise it walks
-//     the indices of its live rows, two at a time, loading the next pair under the
-//     multiply-adds of the current one.
+//     runs straight-line code (4 sixteen-byte loads and 32 two-wide FMAs per k).  Otherwise it
+//     walks the set bits of its masks, loading the next live row under the multiply-adds of
+//     the current one.
 //
 // Lanes are laid out so that every group of 4 consecutive lanes touches 2 row chunks x 2
 // column chunks: on this GPU a 16-byte shared load costs 2 wavefronts when each such group
@@ -111,7 +111,7 @@ __host__ __device__ inline PackedSmem packed_smem_layout(int stages, int cap)
     L.rmask_stride = (uint32_t)cap;
     o += 2 * L.rmask_stride;
     o = (o + 15u) & ~15u;
-    L.wlist_off = o;  // per consumer warp: indices of its live rows of the current stage
+    L.wlist_off = o;  // per consumer warp: offsets of the live rows of its top and its bottom block
     o += P_CONSUMER_WARPS * 2 * 96;  // two lists of WLIST_BYTES per warp
     L.bar_off = o;    // full[P_MAX_STAGES], empty[P_MAX_STAGES], list_full[2], list_empty[2]
     o += (2 * P_MAX_STAGES + 4) * 8;
@@ -189,24 +189,19 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
     }
 }
 
-// ---- stages that are not all-live: per-warp index lists ------------------------------------------
-// A list holds, ascending, the byte offset in the stage (row * 512, 16 bits) of every row that is
-// live for the warp, padded with 8 zero entries so that look-ahead loads need no bounds checks.
-// When the warp's two 32-row blocks have the same live rows (jt == jb) there is one list and every
-// listed row is multiplied into all 8 x 8 outputs (mode BOTH).  Otherwise the top and the bottom
-// block get a list each and are processed one after the other (modes TOP, BOTTOM): each
+// ---- stages that are not all-live ------------------------------------------------------------------
+// When the warp's two 32-row blocks have the same live rows (jt == jb) every live row goes into all
+// 8 x 8 outputs (mode BOTH): the set bits of the mask, a warp-uniform value, are walked in ascending
+// order with find-first-set, one row loaded ahead under the 32 two-wide FMAs of the row before.
+// Otherwise the top and the bottom block are processed one after the other (modes TOP, BOTTOM): each
 // accumulator still sees its own live k in ascending order, no multiply-add is predicated, and the
-// only price is that B rows live for both blocks are read from shared memory twice.
-constexpr int WLIST_ENTRIES = ROWS_PER_STAGE + 8;
-constexpr int WLIST_BYTES = 96;   // WLIST_ENTRIES * 2, rounded up to a multiple of 16
-static_assert(WLIST_ENTRIES * 2 <= WLIST_BYTES, "per-warp list does not fit");
+// only price is that B rows live for both blocks are read from shared memory twice.  A row then
+// feeds only 16 two-wide FMAs, too few to hide a find-first-set chain and a load behind: the lanes
+// first write the rows' offsets as a list (in parallel, while the stage may still be in flight) and
+// the loop takes two rows per step from it.  (Measured on random 32-granular patterns: one pass over
+// jt | jb with warp-uniform branches per block is 20 % slower than the two passes, bit walking in
+// the half modes 3-5 % slower than lists, lists in mode BOTH 4 % slower than bit walking.)
 enum { MODE_BOTH = 0, MODE_TOP = 1, MODE_BOTTOM = 2 };
-
-__device__ __forceinline__ unsigned entry_of(const uint2 &w, int j)
-{
-    const unsigned word = (j & 2) ? w.y : w.x;
-    return (j & 1) ? (word >> 16) : (word & 0xFFFFu);
-}
 
 template <int MODE>
 __device__ __forceinline__ KFrag load_entry(const char *sA, const char *sB, unsigned off)
@@ -224,6 +219,48 @@ __device__ __forceinline__ void fma_entry(Acc &acc, const KFrag &f)
 {
     if (MODE != MODE_BOTTOM) fma_top(acc, f);
     if (MODE != MODE_TOP) fma_bottom(acc, f);
+}
+
+// byte offset in the stage of the lowest live row of m, which is removed from m
+__device__ __forceinline__ unsigned pop_row(unsigned &m)
+{
+    const unsigned r = (unsigned)__ffs((int)m) - 1u;
+    m &= m - 1u;
+    return r << 9;
+}
+
+__device__ __forceinline__ void masked_rows_both(Acc &acc, const char *sA, const char *sB, unsigned m)
+{
+    if (m == 0u) return;
+    KFrag f0 = load_entry<MODE_BOTH>(sA, sB, pop_row(m)), f1;
+#pragma unroll 1
+    while (true) {
+        if (m == 0u) {
+            fma_entry<MODE_BOTH>(acc, f0);
+            break;
+        }
+        f1 = load_entry<MODE_BOTH>(sA, sB, pop_row(m));
+        fma_entry<MODE_BOTH>(acc, f0);
+        if (m == 0u) {
+            fma_entry<MODE_BOTH>(acc, f1);
+            break;
+        }
+        f0 = load_entry<MODE_BOTH>(sA, sB, pop_row(m));
+        fma_entry<MODE_BOTH>(acc, f1);
+    }
+}
+
+// A list holds, ascending, the byte offset in the stage (row * 512, 16 bits) of every row that is
+// live for one of the warp's blocks, padded with 8 zero entries so that look-ahead loads need no
+// bounds checks.
+constexpr int WLIST_ENTRIES = ROWS_PER_STAGE + 8;
+constexpr int WLIST_BYTES = 96;   // WLIST_ENTRIES * 2, rounded up to a multiple of 16
+static_assert(WLIST_ENTRIES * 2 <= WLIST_BYTES, "per-warp list does not fit");
+
+__device__ __forceinline__ unsigned entry_of(const uint2 &w, int j)
+{
+    const unsigned word = (j & 2) ? w.y : w.x;
+    return (j & 1) ? (word >> 16) : (word & 0xFFFFu);
 }
 
 // Two rows per step, the next pair loaded before the current pair is multiplied.
@@ -583,19 +620,20 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     acc.anti[i][j] = make_float2(0.0f, 0.0f);
                 }
 
+            // joint masks of a stage: bit r = row r is live for (top | bottom) block x my columns.  The
+            // masks of the next stage are formed under the multiply-adds of the current one (the list's
+            // buffer is padded by one stage, so reading one stage past the end is harmless).
+            unsigned rm = rmask[lane];
             for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
-                // joint masks of the stage: bit r = row r is live for (top | bottom) block x my columns
-                const unsigned rm = rmask[r0 + lane];
                 const unsigned colb = (rm >> b_shift) & 1u;
                 const unsigned jt = __ballot_sync(0xFFFFFFFFu, ((rm >> t_shift) & colb) != 0u);
                 const unsigned jb = __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u);
+                rm = rmask[r0 + ROWS_PER_STAGE + lane];
                 const bool dense = (jt & jb) == 0xFFFFFFFFu && !p.force_listed;
                 int cnt_t = 0, cnt_b = 0;
-                if (!dense) {
-                    // my live rows as lists, written by the lanes in parallel while the stage's data
-                    // may still be in flight
+                if (jt != jb) {
                     cnt_t = build_list(wlist_t, jt, lane);
-                    if (jt != jb) cnt_b = build_list(wlist_b, jb, lane);
+                    cnt_b = build_list(wlist_b, jb, lane);
                     __syncwarp();
                 }
                 ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
@@ -606,7 +644,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 if (dense) {
                     dense_rows(acc, sA, sB);
                 } else if (jt == jb) {
-                    listed_rows<MODE_BOTH>(acc, sA, sB, wlist_t, cnt_t);
+                    masked_rows_both(acc, sA, sB, jt);
                 } else {
                     listed_rows<MODE_TOP>(acc, sA, sB, wlist_t, cnt_t);
                     listed_rows<MODE_BOTTOM>(acc, sA, sB, wlist_b, cnt_b);
