@@ -24,6 +24,12 @@
 //     k.  Other stages are fetched K block by K block (8-row boxes) and row by row, every
 //     lane issuing its own row.  A k that is dead for the whole tile costs neither a copy
 //     nor shared memory nor a slot in any loop;
+//   * a tile all of whose K blocks hold the same run of 1, 2, 4 or 8 consecutive live k, live for all
+//     of its row and column blocks (what uniform patterns, and dense inputs, give), needs no row
+//     list at all: its stages are computed arithmetically and are all-live;
+//   * where 128 x 128 tiles would leave most of the GPU idle (small M x N), the same kernel runs
+//     with 64 x 128 tiles: a 64-row tile reads the left or right half of a 128-row panel of A, a
+//     consumer warp owns 32 x 32 outputs;
 //   * 8 consumer warps own 64 rows x 32 columns of the tile each (two A pattern rows, one B
 //     pattern row; a thread holds 8 x 8 outputs, 4 rows in each 32-row block).  Per stage a
 //     warp forms its two 32-bit joint masks with two ballots.  If every row of the stage is
@@ -80,7 +86,8 @@ struct PackedParams {
     int brow_bits;   // K blocks with more live k than this are fetched whole
     int b_runs_ok;   // K % 8 == 0: the 3-D view of B stays inside the matrix
     int force_listed;  // tuning aid: take the index-list path even for all-live stages
-    int vec_patterns;  // nKB % 16 == 0 and 16-byte aligned pattern arrays: 16 K blocks per lane and load
+    int no_run_tiles;  // tuning aid: build the row list even for tiles that need none
+    int vec_patterns;  // K blocks per lane and load in the mask warp: 16, 4 (alignment permitting) or 0 = bytes
     const uint8_t *a_pat;
     const uint8_t *b_pat;
     float *C;
@@ -93,6 +100,8 @@ struct PackedMaps {
     CUtensorMap a_row, a_kb, a_run[4];
     CUtensorMap b_row, b_kb, b_run[4];
 };
+
+constexpr int RUN_TILE = 0x100;
 
 struct PackedSmem {
     uint32_t stage_off, krow_off, krow_stride, rmask_off, rmask_stride, wlist_off, bar_off, misc_off, total;
@@ -115,8 +124,8 @@ __host__ __device__ inline PackedSmem packed_smem_layout(int stages, int cap)
     o += P_CONSUMER_WARPS * 2 * 96;  // two lists of WLIST_BYTES per warp
     L.bar_off = o;    // full[P_MAX_STAGES], empty[P_MAX_STAGES], list_full[2], list_empty[2]
     o += (2 * P_MAX_STAGES + 4) * 8;
-    L.misc_off = o;   // nrows[2], abort
-    o += 16;
+    L.misc_off = o;   // nrows[2], abort, -, runinfo[2]
+    o += 32;
     L.total = o;
     return L;
 }
@@ -127,11 +136,14 @@ struct KFrag {
     float4 at, ab, b0, b1;
 };
 
+// WMB = 32-row blocks per consumer warp: 2 in the 128 x 128 tiling, 1 in the 64 x 128 tiling (where a
+// thread holds 4 x 8 outputs and the "bottom" half of everything below is compiled out).
+template <int WMB>
 __device__ __forceinline__ KFrag load_kfrag(const char *pa, const char *pb)
 {
     KFrag f;
     f.at = *reinterpret_cast<const float4 *>(pa);
-    f.ab = *reinterpret_cast<const float4 *>(pa + 128);
+    if (WMB == 2) f.ab = *reinterpret_cast<const float4 *>(pa + 128);
     f.b0 = *reinterpret_cast<const float4 *>(pb);
     f.b1 = *reinterpret_cast<const float4 *>(pb + 64);
     return f;
@@ -175,16 +187,18 @@ __device__ __forceinline__ void fma_bottom(Acc &c, const KFrag &f)
 // A stage whose 32 rows are all live for both row blocks: 8 rows of straight-line code per
 // loop trip, so that the compiler can issue the loads of a row under the multiply-adds of
 // the row before.
+template <int WMB>
 __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char *sB)
 {
+    constexpr int A_ROW = 256 * WMB;   // bytes of one k of the A tile
     // (A rolling prefetch across the loop's back edge was measured slower than this form.)
 #pragma unroll 1
     for (int r0 = 0; r0 < ROWS_PER_STAGE; r0 += 8) {
 #pragma unroll
         for (int r = 0; r < 8; ++r) {
-            const KFrag f = load_kfrag(sA + (r0 + r) * ROW_BYTES, sB + (r0 + r) * ROW_BYTES);
+            const KFrag f = load_kfrag<WMB>(sA + (r0 + r) * A_ROW, sB + (r0 + r) * ROW_BYTES);
             fma_top(acc, f);
-            fma_bottom(acc, f);
+            if (WMB == 2) fma_bottom(acc, f);
         }
     }
 }
@@ -203,12 +217,13 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
 // the half modes 3-5 % slower than lists, lists in mode BOTH 4 % slower than bit walking.)
 enum { MODE_BOTH = 0, MODE_TOP = 1, MODE_BOTTOM = 2 };
 
-template <int MODE>
+template <int MODE, int WMB>
 __device__ __forceinline__ KFrag load_entry(const char *sA, const char *sB, unsigned off)
 {
     KFrag f;
-    if (MODE != MODE_BOTTOM) f.at = *reinterpret_cast<const float4 *>(sA + off);
-    if (MODE != MODE_TOP) f.ab = *reinterpret_cast<const float4 *>(sA + off + 128);
+    const unsigned a_off = WMB == 2 ? off : off >> 1;   // A rows are 512 or 256 bytes apart
+    if (MODE != MODE_BOTTOM) f.at = *reinterpret_cast<const float4 *>(sA + a_off);
+    if (MODE != MODE_TOP) f.ab = *reinterpret_cast<const float4 *>(sA + a_off + 128);
     f.b0 = *reinterpret_cast<const float4 *>(sB + off);
     f.b1 = *reinterpret_cast<const float4 *>(sB + off + 64);
     return f;
@@ -221,7 +236,7 @@ __device__ __forceinline__ void fma_entry(Acc &acc, const KFrag &f)
     if (MODE != MODE_TOP) fma_bottom(acc, f);
 }
 
-// byte offset in the stage of the lowest live row of m, which is removed from m
+// byte offset in the stage's B rows of the lowest live row of m, which is removed from m
 __device__ __forceinline__ unsigned pop_row(unsigned &m)
 {
     const unsigned r = (unsigned)__ffs((int)m) - 1u;
@@ -229,23 +244,24 @@ __device__ __forceinline__ unsigned pop_row(unsigned &m)
     return r << 9;
 }
 
+// (128-row tiling only: in the 64-row tiling every stage that is not all-live takes the list.)
 __device__ __forceinline__ void masked_rows_both(Acc &acc, const char *sA, const char *sB, unsigned m)
 {
     if (m == 0u) return;
-    KFrag f0 = load_entry<MODE_BOTH>(sA, sB, pop_row(m)), f1;
+    KFrag f0 = load_entry<MODE_BOTH, 2>(sA, sB, pop_row(m)), f1;
 #pragma unroll 1
     while (true) {
         if (m == 0u) {
             fma_entry<MODE_BOTH>(acc, f0);
             break;
         }
-        f1 = load_entry<MODE_BOTH>(sA, sB, pop_row(m));
+        f1 = load_entry<MODE_BOTH, 2>(sA, sB, pop_row(m));
         fma_entry<MODE_BOTH>(acc, f0);
         if (m == 0u) {
             fma_entry<MODE_BOTH>(acc, f1);
             break;
         }
-        f0 = load_entry<MODE_BOTH>(sA, sB, pop_row(m));
+        f0 = load_entry<MODE_BOTH, 2>(sA, sB, pop_row(m));
         fma_entry<MODE_BOTH>(acc, f1);
     }
 }
@@ -264,22 +280,22 @@ __device__ __forceinline__ unsigned entry_of(const uint2 &w, int j)
 }
 
 // Two rows per step, the next pair loaded before the current pair is multiplied.
-template <int MODE>
+template <int MODE, int WMB>
 __device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char *sB, const uint16_t *list, int cnt)
 {
     const int n4 = cnt & ~3;
     uint2 ew = *reinterpret_cast<const uint2 *>(list);   // entries 0..3
-    KFrag f0 = load_entry<MODE>(sA, sB, entry_of(ew, 0));
-    KFrag f1 = load_entry<MODE>(sA, sB, entry_of(ew, 1));
+    KFrag f0 = load_entry<MODE, WMB>(sA, sB, entry_of(ew, 0));
+    KFrag f1 = load_entry<MODE, WMB>(sA, sB, entry_of(ew, 1));
 #pragma unroll 1
     for (int i = 0; i < n4; i += 4) {
-        const KFrag g0 = load_entry<MODE>(sA, sB, entry_of(ew, 2));
-        const KFrag g1 = load_entry<MODE>(sA, sB, entry_of(ew, 3));
+        const KFrag g0 = load_entry<MODE, WMB>(sA, sB, entry_of(ew, 2));
+        const KFrag g1 = load_entry<MODE, WMB>(sA, sB, entry_of(ew, 3));
         fma_entry<MODE>(acc, f0);
         fma_entry<MODE>(acc, f1);
         ew = *reinterpret_cast<const uint2 *>(list + i + 4);   // padded: always readable
-        f0 = load_entry<MODE>(sA, sB, entry_of(ew, 0));
-        f1 = load_entry<MODE>(sA, sB, entry_of(ew, 1));
+        f0 = load_entry<MODE, WMB>(sA, sB, entry_of(ew, 0));
+        f1 = load_entry<MODE, WMB>(sA, sB, entry_of(ew, 1));
         fma_entry<MODE>(acc, g0);
         fma_entry<MODE>(acc, g1);
     }
@@ -287,7 +303,7 @@ __device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char
     const int rem = cnt - n4;
     if (rem >= 1) fma_entry<MODE>(acc, f0);
     if (rem >= 2) fma_entry<MODE>(acc, f1);
-    if (rem == 3) fma_entry<MODE>(acc, load_entry<MODE>(sA, sB, entry_of(ew, 2)));
+    if (rem == 3) fma_entry<MODE>(acc, load_entry<MODE, WMB>(sA, sB, entry_of(ew, 2)));
 }
 
 // Lanes write the list of the rows whose bit is set in `m`; returns the count.
@@ -300,31 +316,48 @@ __device__ __forceinline__ int build_list(uint16_t *list, unsigned m, int lane)
 }
 
 // ---- mask warp helpers ---------------------------------------------------------------------------
-// Pattern bytes of 16 consecutive K blocks (kb0 .. kb0 + 15, all inside the matrix) for the tile's four
-// 32-row blocks and four 32-column blocks: one 16-byte load per pattern row.  aw[j] / bw[j] get the
-// four bytes of K block kb0 + j (byte i = block i).
-__device__ __forceinline__ void load_patterns16(const PackedParams &p, int tm, int tn, int kb0, bool valid,
-                                                unsigned (&aw)[16], unsigned (&bw)[16])
+// Pattern bytes of KPL (16 or 4) consecutive K blocks kb0 .. kb0 + KPL - 1, all inside the matrix, for the
+// tile's RB 32-row blocks and four 32-column blocks: one 16-byte or 4-byte load per pattern row.  aw[j] /
+// bw[j] get the four bytes of K block kb0 + j (byte i = block i).  Long K takes 16 per lane; shorter K
+// takes 4, so that all lanes have work.
+template <int RB, int KPL>
+__device__ __forceinline__ void load_patterns(const PackedParams &p, int tm, int tn, int kb0, bool valid,
+                                              unsigned (&aw)[KPL], unsigned (&bw)[KPL])
 {
-    uint4 ra[4], rb[4];
+    constexpr int W = KPL / 4;   // 32-bit words per pattern row
+    unsigned ra[4][W], rb[4][W];
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const int mb = tm * 4 + i, nb = tn * 4 + i;
-        ra[i] = make_uint4(0u, 0u, 0u, 0u);
-        rb[i] = make_uint4(0u, 0u, 0u, 0u);
-        if (valid && mb < p.a_rows) ra[i] = *reinterpret_cast<const uint4 *>(p.a_pat + (size_t)mb * p.nKB + kb0);
-        if (valid && nb < p.b_rows) rb[i] = *reinterpret_cast<const uint4 *>(p.b_pat + (size_t)nb * p.nKB + kb0);
+        const int mb = tm * RB + i, nb = tn * 4 + i;
+#pragma unroll
+        for (int w = 0; w < W; ++w) ra[i][w] = rb[i][w] = 0u;
+        if (valid && i < RB && mb < p.a_rows) {
+            const uint8_t *src = p.a_pat + (size_t)mb * p.nKB + kb0;
+            if (KPL == 16) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                ra[i][0] = v.x, ra[i][W > 1 ? 1 : 0] = v.y, ra[i][W > 2 ? 2 : 0] = v.z, ra[i][W > 3 ? 3 : 0] = v.w;
+            } else {
+                ra[i][0] = *reinterpret_cast<const unsigned *>(src);
+            }
+        }
+        if (valid && nb < p.b_rows) {
+            const uint8_t *src = p.b_pat + (size_t)nb * p.nKB + kb0;
+            if (KPL == 16) {
+                const uint4 v = *reinterpret_cast<const uint4 *>(src);
+                rb[i][0] = v.x, rb[i][W > 1 ? 1 : 0] = v.y, rb[i][W > 2 ? 2 : 0] = v.z, rb[i][W > 3 ? 3 : 0] = v.w;
+            } else {
+                rb[i][0] = *reinterpret_cast<const unsigned *>(src);
+            }
+        }
     }
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
+    for (int j = 0; j < KPL; ++j) {
         const int sh = 8 * (j & 3);
         unsigned a = 0, b = 0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const unsigned wa = (j >> 2) == 0 ? ra[i].x : (j >> 2) == 1 ? ra[i].y : (j >> 2) == 2 ? ra[i].z : ra[i].w;
-            const unsigned wb = (j >> 2) == 0 ? rb[i].x : (j >> 2) == 1 ? rb[i].y : (j >> 2) == 2 ? rb[i].z : rb[i].w;
-            a |= ((wa >> sh) & 0xFFu) << (8 * i);
-            b |= ((wb >> sh) & 0xFFu) << (8 * i);
+            a |= ((ra[i][j >> 2] >> sh) & 0xFFu) << (8 * i);
+            b |= ((rb[i][j >> 2] >> sh) & 0xFFu) << (8 * i);
         }
         aw[j] = a;
         bw[j] = b;
@@ -367,9 +400,76 @@ __device__ __forceinline__ int warp_inclusive_scan(int v, int lane)
     return v;
 }
 
+// First pass of the mask warp over a tile's pattern bytes: the live byte of its first K block, whether all
+// K blocks share it, and the number of live k.
+// whether the live k of a K block are live for each of the tile's RB row blocks and 4 column blocks
+template <int RB>
+__device__ __forceinline__ bool blocks_cover(unsigned aw, unsigned bw, unsigned live)
+{
+    const unsigned l4 = live * 0x01010101u, am = RB == 4 ? 0xFFFFFFFFu : 0x0000FFFFu;
+    return ((aw & l4 & am) == (l4 & am)) && ((bw & l4) == l4);
+}
+
+template <int RB, int KPL>
+__device__ __forceinline__ void tile_scan(const PackedParams &p, int tm, int tn, int lane, unsigned &live_first,
+                                          bool &uniform, bool &full, int &live_total)
+{
+    for (int c0 = 0; c0 < p.nKB; c0 += 32 * KPL) {
+        const int kb0 = c0 + KPL * lane;
+        unsigned aw[KPL], bw[KPL];
+        load_patterns<RB, KPL>(p, tm, tn, kb0, kb0 < p.nKB, aw, bw);
+        if (c0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, tile_live(aw[0], bw[0]), 0);
+        bool same = true, cover = true;
+        int cnt = 0;
+#pragma unroll
+        for (int j = 0; j < KPL; ++j) {
+            const unsigned live = tile_live(aw[j], bw[j]);
+            same = same && live == live_first;
+            cover = cover && blocks_cover<RB>(aw[j], bw[j], live);
+            cnt += __popc(live);
+        }
+        uniform = uniform && __all_sync(0xFFFFFFFFu, kb0 >= p.nKB || same);
+        full = full && __all_sync(0xFFFFFFFFu, kb0 >= p.nKB || cover);
+        live_total += __reduce_add_sync(0xFFFFFFFFu, cnt);
+    }
+}
+
+// Second pass: the row list.  Lane l owns K blocks c0 + KPL l .. c0 + KPL l + KPL - 1 (consecutive lanes,
+// consecutive K); K blocks with more than whole_above live k are listed whole.  Returns the row count.
+template <int RB, int KPL>
+__device__ __forceinline__ int tile_list(const PackedParams &p, int tm, int tn, int lane, int whole_above,
+                                         uint16_t *krow, uint8_t *rmask)
+{
+    int pos = 0;
+    for (int c0 = 0; c0 < p.nKB; c0 += 32 * KPL) {
+        const int kb0 = c0 + KPL * lane;
+        unsigned aw[KPL], bw[KPL];
+        load_patterns<RB, KPL>(p, tm, tn, kb0, kb0 < p.nKB, aw, bw);
+        unsigned rows[KPL];
+        int c = 0;
+#pragma unroll
+        for (int j = 0; j < KPL; ++j) {
+            const unsigned live = tile_live(aw[j], bw[j]);
+            rows[j] = live == 0u ? 0u : (__popc(live) > whole_above ? 0xFFu : live);
+            c += __popc(rows[j]);
+        }
+        const int incl = warp_inclusive_scan(c, lane);
+        int q = pos + incl - c;
+#pragma unroll
+        for (int j = 0; j < KPL; ++j) q = append_rows(krow, rmask, q, kb0 + j, rows[j], aw[j], bw[j]);
+        pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
+    }
+    return pos;
+}
+
+template <int WMB>
 __global__ void __launch_bounds__(P_THREADS, 1)
 esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const PackedParams p)
 {
+    constexpr int TM_ROWS = 64 * WMB;                  // rows of a tile of C: 128 or 64
+    constexpr int RB = 2 * WMB;                        // 32-row blocks per tile
+    constexpr int A_ROW = TM_ROWS * 4;                 // bytes of one k of the A tile in shared memory
+    constexpr uint32_t STAGE_ROW_BYTES = A_ROW + ROW_BYTES;
     extern __shared__ __align__(1024) char smem[];
     const PackedSmem L = packed_smem_layout(p.stages, p.cap);
     const int warp = threadIdx.x >> 5;
@@ -382,6 +482,10 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
     const uint32_t lempty0 = smem_u32(bars + 2 * P_MAX_STAGES + 2);
     volatile int *nrows = reinterpret_cast<volatile int *>(smem + L.misc_off);
     volatile int *abort_flag = nrows + 2;
+    // per list buffer: 0, or RUN_TILE | log2(c) | kk0 << 4 for a tile whose every K block has the same c = 1, 2,
+    // 4 or 8 consecutive live k (kk0 .. kk0 + c - 1), live for all of the tile's row and column blocks.  Such
+    // a tile needs no row list: stage s is the 3-D box of K blocks 32 s / c .. and every stage is all-live.
+    volatile int *runinfo = nrows + 4;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
@@ -414,25 +518,12 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             uint8_t *rmask = reinterpret_cast<uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
             // A first pass over the tile's pattern bytes decides the listing policy.
             unsigned live_first = 0;
-            bool uniform = true;
+            bool uniform = true, full = true;
             int live_total = 0;
-            if (p.vec_patterns) {
-                for (int c0 = 0; c0 < p.nKB; c0 += 512) {
-                    const int kb0 = c0 + 16 * lane;
-                    unsigned aw[16], bw[16];
-                    load_patterns16(p, tm, tn, kb0, kb0 < p.nKB, aw, bw);
-                    if (c0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, tile_live(aw[0], bw[0]), 0);
-                    bool same = true;
-                    int cnt = 0;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const unsigned live = tile_live(aw[j], bw[j]);
-                        same = same && live == live_first;
-                        cnt += __popc(live);
-                    }
-                    uniform = uniform && __all_sync(0xFFFFFFFFu, kb0 >= p.nKB || same);
-                    live_total += __reduce_add_sync(0xFFFFFFFFu, cnt);
-                }
+            if (p.vec_patterns == 16) {
+                tile_scan<RB, 16>(p, tm, tn, lane, live_first, uniform, full, live_total);
+            } else if (p.vec_patterns == 4) {
+                tile_scan<RB, 4>(p, tm, tn, lane, live_first, uniform, full, live_total);
             } else {
                 for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
                     const int kb = kb0 + lane;
@@ -440,14 +531,15 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     if (kb < p.nKB) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int mb = tm * 4 + i, nb = tn * 4 + i;
-                            if (mb < p.a_rows) au |= p.a_pat[(size_t)mb * p.nKB + kb];
+                            const int mb = tm * RB + i, nb = tn * 4 + i;
+                            if (i < RB && mb < p.a_rows) au |= p.a_pat[(size_t)mb * p.nKB + kb];
                             if (nb < p.b_rows) bu |= p.b_pat[(size_t)nb * p.nKB + kb];
                         }
                     }
                     const unsigned live = au & bu;
                     if (kb0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, live, 0);
                     uniform = uniform && __all_sync(0xFFFFFFFFu, kb >= p.nKB || live == live_first);
+                    full = false;   // the byte-wise path keeps the general listing
                     live_total += __reduce_add_sync(0xFFFFFFFFu, __popc(live));
                 }
             }
@@ -455,27 +547,23 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             // only on sparse tiles (on average at most 2 live k per K block); denser tiles list
             // every live K block whole.
             const int whole_above = uniform ? BK : (live_total <= 2 * p.nKB ? p.brow_bits : 0);
+            // a run tile?  c = 1, 2, 4 or 8 consecutive live k, whole stages only, 3-D view of B valid
+            int run_code = 0;
+            {
+                const int c = __popc(live_first);
+                const int kk0 = __ffs((int)live_first) - 1;
+                if (uniform && full && live_first != 0u && (c & (c - 1)) == 0 &&
+                    (live_first >> kk0) == (1u << c) - 1u && (p.nKB * c) % ROWS_PER_STAGE == 0 && p.b_runs_ok &&
+                    !p.force_listed && !p.no_run_tiles)
+                    run_code = RUN_TILE | (31 - __clz(c)) | (kk0 << 4);
+            }
             int pos = 0;
-            if (p.vec_patterns) {
-                // lane l owns K blocks c0 + 16 l .. c0 + 16 l + 15: consecutive lanes, consecutive K
-                for (int c0 = 0; c0 < p.nKB; c0 += 512) {
-                    const int kb0 = c0 + 16 * lane;
-                    unsigned aw[16], bw[16];
-                    load_patterns16(p, tm, tn, kb0, kb0 < p.nKB, aw, bw);
-                    unsigned rows[16];
-                    int c = 0;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        const unsigned live = tile_live(aw[j], bw[j]);
-                        rows[j] = live == 0u ? 0u : (__popc(live) > whole_above ? 0xFFu : live);
-                        c += __popc(rows[j]);
-                    }
-                    const int incl = warp_inclusive_scan(c, lane);
-                    int q = pos + incl - c;
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) q = append_rows(krow, rmask, q, kb0 + j, rows[j], aw[j], bw[j]);
-                    pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
-                }
+            if (run_code) {
+                pos = p.nKB * __popc(live_first);
+            } else if (p.vec_patterns == 16) {
+                pos = tile_list<RB, 16>(p, tm, tn, lane, whole_above, krow, rmask);
+            } else if (p.vec_patterns == 4) {
+                pos = tile_list<RB, 4>(p, tm, tn, lane, whole_above, krow, rmask);
             } else {
                 for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
                     const int kb = kb0 + lane;
@@ -483,8 +571,8 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     if (kb < p.nKB) {
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
-                            const int mb = tm * 4 + i, nb = tn * 4 + i;
-                            if (mb < p.a_rows) aw |= (unsigned)p.a_pat[(size_t)mb * p.nKB + kb] << (8 * i);
+                            const int mb = tm * RB + i, nb = tn * 4 + i;
+                            if (i < RB && mb < p.a_rows) aw |= (unsigned)p.a_pat[(size_t)mb * p.nKB + kb] << (8 * i);
                             if (nb < p.b_rows) bw |= (unsigned)p.b_pat[(size_t)nb * p.nKB + kb] << (8 * i);
                         }
                     }
@@ -497,14 +585,17 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 }
             }
             // rows past the end of the last stage read as dead
-            {
+            if (!run_code) {
                 const int q = pos + lane;
                 if (q < ((pos + 31) & ~31)) {
                     krow[q] = 0;
                     rmask[q] = 0;
                 }
             }
-            if (lane == 0) nrows[buf] = pos;
+            if (lane == 0) {
+                nrows[buf] = pos;
+                runinfo[buf] = run_code;
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
             if (it == 0) ESMM_STAMP(1);
@@ -524,8 +615,35 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             const uint16_t *krow = reinterpret_cast<const uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
             const int n = nrows[buf];
-            const int a_row0 = tm * p.kp, b_col0 = tn * TILE_N;
-            for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
+            const int run_code = runinfo[buf];
+            // packed A is stored in panels of 128 rows: a 64-row tile is the left or right half of one
+            const int panel = WMB == 2 ? tm : tm >> 1;
+            const int a_x = WMB == 2 ? 0 : (tm & 1) * TM_ROWS;
+            const int a_row0 = panel * p.kp, b_col0 = tn * TILE_N;
+            if (run_code) {
+                // a run tile: whole stages, each one box per operand, no row list
+                const int lc = run_code & 15, kk0 = (run_code >> 4) & 7;
+                for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
+                    ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
+                    if (!ok) break;
+                    const uint32_t full = full0 + 8 * slot;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(full, (uint32_t)ROWS_PER_STAGE * STAGE_ROW_BYTES);
+                        const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
+                        const int kb0 = r0 >> lc;
+                        tma_load_3d(s0, &maps.a_run[lc], a_x, kk0, panel * p.nKB + kb0, full);
+                        tma_load_3d(s0 + STAGE_HALF_BYTES, &maps.b_run[lc], b_col0, kk0, kb0, full);
+                    }
+                    issued_bits |= 1u << slot;
+                    parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
+                    if (it == 0) ESMM_STAMP(400 + r0 / ROWS_PER_STAGE);
+                    if (++slot == p.stages) {
+                        slot = 0;
+                        phase ^= 1;
+                    }
+                }
+            }
+            for (int r0 = 0; r0 < n && !run_code; r0 += ROWS_PER_STAGE) {
                 const int cnt = min(ROWS_PER_STAGE, n - r0);
                 const bool valid = lane < cnt;
                 const int k = valid ? (int)krow[r0 + lane] : -1;
@@ -552,20 +670,21 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 const uint32_t full = full0 + 8 * slot;
-                if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * 2u * ROW_BYTES);
+                if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * STAGE_ROW_BYTES);
                 __syncwarp();
-                const uint32_t sa = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES + lane * ROW_BYTES;
-                const uint32_t sb = sa + STAGE_HALF_BYTES;
+                const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
+                const uint32_t sa = s0 + lane * A_ROW;
+                const uint32_t sb = s0 + STAGE_HALF_BYTES + lane * ROW_BYTES;
                 if (run >= 0) {
                     if (lane == 0) {
-                        tma_load_3d(sa, &maps.a_run[run], 0, kk0, tm * p.nKB + kb0, full);
+                        tma_load_3d(sa, &maps.a_run[run], a_x, kk0, panel * p.nKB + kb0, full);
                         tma_load_3d(sb, &maps.b_run[run], b_col0, kk0, kb0, full);
                     }
                 } else if (lead8) {
-                    tma_load_2d(sa, &maps.a_kb, 0, a_row0 + k, full);
+                    tma_load_2d(sa, &maps.a_kb, a_x, a_row0 + k, full);
                     tma_load_2d(sb, &maps.b_kb, b_col0, k, full);
                 } else if (valid && !((cover >> lane) & 1u)) {
-                    tma_load_2d(sa, &maps.a_row, 0, a_row0 + k, full);
+                    tma_load_2d(sa, &maps.a_row, a_x, a_row0 + k, full);
                     tma_load_2d(sb, &maps.b_row, b_col0, k, full);
                 }
                 issued_bits |= 1u << slot;
@@ -590,13 +709,13 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             }
         }
     } else {
-        // ---------------- consumer warps: 64 rows x 32 columns of the tile each ----------------
+        // ---------------- consumer warps: 32 WMB rows x 32 columns of the tile each ----------------
         const int wm = warp >> 2, wn = warp & 3;              // 2 x 4 warps
         const int lm = (lane >> 1) & 7;                       // group of 4 rows within a 32-row block
         const int ln = (lane & 1) | ((lane >> 4) << 1);       // 16-byte column chunk
-        const uint32_t a_thr = (uint32_t)(wm * 64 + lm * 4) * 4;                      // within a row of A
+        const uint32_t a_thr = (uint32_t)(wm * 32 * WMB + lm * 4) * 4;                // within a row of A
         const uint32_t b_thr = STAGE_HALF_BYTES + (uint32_t)(wn * 32 + ln * 4) * 4;  // within a row of B
-        const int t_shift = 2 * wm, b_shift = 4 + wn;
+        const int t_shift = WMB * wm, b_shift = 4 + wn;
         uint16_t *wlist_t = reinterpret_cast<uint16_t *>(smem + L.wlist_off + warp * 2 * WLIST_BYTES);
         uint16_t *wlist_b = wlist_t + WLIST_BYTES / 2;
         int slot = 0;
@@ -610,6 +729,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             const uint8_t *rmask = reinterpret_cast<const uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
             const int n = nrows[buf];
+            const bool run_tile = runinfo[buf] != 0;
 
             Acc acc;
 #pragma unroll
@@ -623,17 +743,18 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             // joint masks of a stage: bit r = row r is live for (top | bottom) block x my columns.  The
             // masks of the next stage are formed under the multiply-adds of the current one (the list's
             // buffer is padded by one stage, so reading one stage past the end is harmless).
-            unsigned rm = rmask[lane];
+            unsigned rm = run_tile ? 0xFFu : rmask[lane];
             for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
                 const unsigned colb = (rm >> b_shift) & 1u;
                 const unsigned jt = __ballot_sync(0xFFFFFFFFu, ((rm >> t_shift) & colb) != 0u);
-                const unsigned jb = __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u);
-                rm = rmask[r0 + ROWS_PER_STAGE + lane];
+                const unsigned jb = WMB == 2 ? __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u) : jt;
+                if (!run_tile) rm = rmask[r0 + ROWS_PER_STAGE + lane];
                 const bool dense = (jt & jb) == 0xFFFFFFFFu && !p.force_listed;
+                // in the 64-row tiling a row feeds 16 two-wide FMAs, as in the half modes: lists there too
                 int cnt_t = 0, cnt_b = 0;
-                if (jt != jb) {
+                if (WMB == 1 ? !dense : jt != jb) {
                     cnt_t = build_list(wlist_t, jt, lane);
-                    cnt_b = build_list(wlist_b, jb, lane);
+                    if (WMB == 2) cnt_b = build_list(wlist_b, jb, lane);
                     __syncwarp();
                 }
                 ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
@@ -642,12 +763,14 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 const char *sB = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + b_thr;
                 if (warp == 0 && it == 0) ESMM_STAMP(10 + r0 / ROWS_PER_STAGE);
                 if (dense) {
-                    dense_rows(acc, sA, sB);
+                    dense_rows<WMB>(acc, sA, sB);
+                } else if (WMB == 1) {
+                    listed_rows<MODE_TOP, 1>(acc, sA, sB, wlist_t, cnt_t);
                 } else if (jt == jb) {
                     masked_rows_both(acc, sA, sB, jt);
                 } else {
-                    listed_rows<MODE_TOP>(acc, sA, sB, wlist_t, cnt_t);
-                    listed_rows<MODE_BOTTOM>(acc, sA, sB, wlist_b, cnt_b);
+                    listed_rows<MODE_TOP, 2>(acc, sA, sB, wlist_t, cnt_t);
+                    listed_rows<MODE_BOTTOM, 2>(acc, sA, sB, wlist_b, cnt_b);
                 }
                 if (warp == 0 && it == 0) ESMM_STAMP(200 + r0 / ROWS_PER_STAGE);
                 __syncwarp();
@@ -662,10 +785,10 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
 
             // epilogue: C is overwritten (beta = 0); un-scramble the 2 x 2 blocks into rows
-            const int row0 = tm * TILE_M + wm * 64 + lm * 4;
+            const int row0 = tm * TM_ROWS + wm * 32 * WMB + lm * 4;
             const int col0 = tn * TILE_N + wn * 32 + ln * 4;
 #pragma unroll
-            for (int pr = 0; pr < 4; ++pr) {
+            for (int pr = 0; pr < 2 * WMB; ++pr) {
 #pragma unroll
                 for (int e = 0; e < 2; ++e) {
                     const int i = 2 * pr + e;                        // row of the thread tile
@@ -715,15 +838,34 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     p.cap = ((p.kp + 31) & ~31) + 32;
     p.a_rows = ceil_div(M, 32);
     p.b_rows = ceil_div(N, PAT_N);
-    p.tiles_m = ceil_div(M, TILE_M);
+    int dev = 0, sms = 0;
+    ESMM_CUDA_TRY(cudaGetDevice(&dev));
+    ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // Tile height: 128 rows, or 64 where that fills the GPU better.  Rounds of tiles per SM, a 64-row
+    // tile counted as 0.55 of a 128-row one (it does half the multiply-adds at a worse ratio of
+    // shared-memory loads).  ESMM_TILE_M = 64 | 128 overrides.
     p.tiles_n = ceil_div(N, TILE_N);
+    const int panels = ceil_div(M, TILE_M);
+    const long t128 = (long)panels * p.tiles_n, t64 = (long)ceil_div(M, 64) * p.tiles_n;
+    const double cost128 = (double)((t128 + sms - 1) / sms), cost64 = 0.55 * (double)((t64 + sms - 1) / sms);
+    int tile_rows = cost64 < cost128 ? 64 : TILE_M;
+    const int forced_rows = env_int("ESMM_TILE_M", 0);
+    if (forced_rows == 64 || forced_rows == TILE_M) tile_rows = forced_rows;
+    p.tiles_m = ceil_div(M, tile_rows);
     p.num_tiles = p.tiles_m * p.tiles_n;
     p.brow_bits = env_int("ESMM_BROW_BITS", 3);
     if (p.brow_bits < 0) p.brow_bits = 0;
     if (p.brow_bits > 8) p.brow_bits = 8;
     p.force_listed = env_int("ESMM_FORCE_LISTED", 0);
-    p.vec_patterns = (p.nKB % 16 == 0) && (((uintptr_t)d_a_pat | (uintptr_t)d_b_pat) & 15) == 0 &&
-                     env_int("ESMM_VEC_PATTERNS", 1);
+    p.no_run_tiles = env_int("ESMM_NO_RUN_TILES", 0);
+    const uintptr_t pat_bits = (uintptr_t)d_a_pat | (uintptr_t)d_b_pat;
+    p.vec_patterns = 0;
+    if (p.nKB % 4 == 0 && (pat_bits & 3) == 0) p.vec_patterns = 4;
+    if (p.nKB % 16 == 0 && (pat_bits & 15) == 0 && p.nKB >= 512) p.vec_patterns = 16;
+    const int forced_vec = env_int("ESMM_VEC_PATTERNS", -1);   // 0, 4, 16: tuning and tests
+    if (forced_vec == 0 || (forced_vec == 4 && p.vec_patterns >= 4) ||
+        (forced_vec == 16 && p.nKB % 16 == 0 && (pat_bits & 15) == 0))
+        p.vec_patterns = forced_vec;
     p.a_pat = d_a_pat;
     p.b_pat = d_b_pat;
     p.C = d_C;
@@ -736,22 +878,20 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     if (L.total > SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
     p.stages = stages;
 
-    int dev = 0, sms = 0;
-    ESMM_CUDA_TRY(cudaGetDevice(&dev));
-    ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
     p.status = device_status_ptr();
     if (!p.status) return ESMM_ERR_CUDA;
 
-    // Packed A is a matrix of 128 columns and tiles_m * kp rows; B is K rows of N columns.  Rows
+    // Packed A is a matrix of 128 columns and panels * kp rows, of which a tile reads all 128 columns
+    // or the 64 of its half; B is K rows of N columns.  Rows
     // (or columns of B) outside the matrices are zero-filled by the copy engine and still counted
     // in the stage's byte total.  The 3-D views split the row index into (k % 8, k / 8); for B
     // that is only valid when K is a multiple of 8 (otherwise the view would reach past row K).
     p.b_runs_ok = (K % BK) == 0;
     PackedMaps maps;
-    const uint64_t a_rows_total = (uint64_t)p.tiles_m * p.kp;
-    int st = make_map_2d(&maps.a_row, d_a_packed, TILE_M, a_rows_total, TILE_M, 1, CU_TENSOR_MAP_SWIZZLE_NONE,
+    const uint64_t a_rows_total = (uint64_t)panels * p.kp;
+    int st = make_map_2d(&maps.a_row, d_a_packed, TILE_M, a_rows_total, tile_rows, 1, CU_TENSOR_MAP_SWIZZLE_NONE,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-    if (!st) st = make_map_2d(&maps.a_kb, d_a_packed, TILE_M, a_rows_total, TILE_M, BK, CU_TENSOR_MAP_SWIZZLE_NONE,
+    if (!st) st = make_map_2d(&maps.a_kb, d_a_packed, TILE_M, a_rows_total, tile_rows, BK, CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     if (!st) st = make_map_2d(&maps.b_row, d_B, (uint64_t)N, (uint64_t)K, TILE_N, 1, CU_TENSOR_MAP_SWIZZLE_NONE,
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
@@ -759,8 +899,8 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
     for (int i = 0; i < 4 && !st; ++i) {
         const uint32_t c = 1u << i;
-        st = make_map_3d(&maps.a_run[i], d_a_packed, TILE_M, BK, (uint64_t)p.tiles_m * p.nKB, (uint64_t)TILE_M * 4,
-                         (uint64_t)TILE_M * 4 * BK, TILE_M, c, ROWS_PER_STAGE / c);
+        st = make_map_3d(&maps.a_run[i], d_a_packed, TILE_M, BK, (uint64_t)panels * p.nKB, (uint64_t)TILE_M * 4,
+                         (uint64_t)TILE_M * 4 * BK, tile_rows, c, ROWS_PER_STAGE / c);
         if (!st) {
             if (p.b_runs_ok)
                 st = make_map_3d(&maps.b_run[i], d_B, (uint64_t)N, BK, (uint64_t)p.nKB, (uint64_t)N * 4,
@@ -771,12 +911,18 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     }
     if (st) return st;
 
-    ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)L.total));
     int grid = env_int("ESMM_GRID", sms);
     if (grid > p.num_tiles) grid = p.num_tiles;
     if (grid < 1) grid = 1;
-    esmm_joint_sgemm_packed_kernel<<<grid, P_THREADS, L.total, stream>>>(maps, p);
+    if (tile_rows == 64) {
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<1>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total));
+        esmm_joint_sgemm_packed_kernel<1><<<grid, P_THREADS, L.total, stream>>>(maps, p);
+    } else {
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<2>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total));
+        esmm_joint_sgemm_packed_kernel<2><<<grid, P_THREADS, L.total, stream>>>(maps, p);
+    }
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;
 }

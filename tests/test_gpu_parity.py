@@ -158,8 +158,17 @@ def test_preprocess_ab_metadata(cuda, pkg, oracle_mod):
 
 # ---- joint-sparse GEMM: both kernels against the oracle ----------------------------------------------
 @pytest.mark.parametrize("pat", [0xFF, 0x0F, 0x03, 0x01, 0xA5, 0x80, 0x3C])
-def test_gemm_uniform_patterns(cuda, pkg, oracle_mod, pat):
+def test_gemm_uniform_patterns(cuda, pkg, oracle_mod, monkeypatch, pat):
+    """Tiles whose K blocks all hold the same run of 1, 2, 4 or 8 consecutive live k need no row list (0xFF,
+    0x0F, 0x03, 0x01, 0x80, 0x3C here); the same inputs with that shortcut switched off, and patterns that
+    are no such run (0xA5), take the general listing."""
     A, B = workloads.uniform_pattern(256, 256, 512, pat, seed=pat)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    monkeypatch.setenv("ESMM_NO_RUN_TILES", "1")
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    monkeypatch.delenv("ESMM_NO_RUN_TILES")
+    # K blocks not a multiple of the stage depth (last stage partial) and a ragged edge tile
+    A, B = workloads.uniform_pattern(200, 160, 8 * 21, pat, seed=pat + 1)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
@@ -220,6 +229,29 @@ def test_gemm_row_fetch_policies(cuda, pkg, oracle_mod, monkeypatch, brow):
     A, B = workloads.tile_random(256, 256, 512, 0.3, 0.4, seed=12, gran_a=32, gran_b=32)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
     A, B = workloads.uniform_pattern(128, 128, 256, 0x03, seed=1)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
+@pytest.mark.parametrize("rows", [64, 128])
+def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, monkeypatch, rows):
+    """The packed kernel tiles C in 128 x 128 or, where that fills the GPU better, 64 x 128 (a 64-row tile is
+    one half of a 128-row panel of packed A).  Both tilings, forced, on uniform, random, ragged and small-M
+    inputs: same bits as the oracle."""
+    monkeypatch.setenv("ESMM_TILE_M", str(rows))
+    for pat in (0xFF, 0x0F, 0x01, 0x24):
+        A, B = workloads.uniform_pattern(384, 256, 512, pat, seed=pat)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.tile_random(320, 384, 1024, 0.4, 0.5, seed=21, gran_a=32, gran_b=32)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.tile_random(200, 132, 250 * 4, 0.5, 0.5, seed=22, gran_a=32, gran_b=32)   # ragged M, N
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.all_byte_values(seed=23)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    for M in (16, 48, 96):
+        A, B = workloads.llm_mlp(M, 512, 1024, seed=M)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    monkeypatch.setenv("ESMM_FORCE_LISTED", "1")
+    A, B = workloads.uniform_pattern(192, 256, 256, 0x0F, seed=2)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
@@ -466,10 +498,12 @@ def test_bounded_wait_reports_timeout_and_context_survives(cuda, pkg, oracle_mod
 
 
 def test_gemm_mask_builder_paths_agree(cuda, pkg, oracle_mod, monkeypatch):
-    """The tile's row list is built from 16-byte pattern loads when the pattern rows allow it and
-    byte by byte otherwise; both must give the same C."""
+    """The tile's row list is built from 16-byte pattern loads (long K), 4-byte loads (shorter K) or byte
+    by byte (pattern rows that are not a multiple of 4 bytes); all must give the same C."""
     A, B = workloads.tile_random(256, 384, 8192 + 128, 0.3, 0.5, seed=17, gran_a=32, gran_b=32)  # 1040 K blocks
-    monkeypatch.setenv("ESMM_VEC_PATTERNS", "0")
-    check_all_paths(cuda, pkg, oracle_mod, A, B)
-    monkeypatch.setenv("ESMM_VEC_PATTERNS", "1")
+    for mode in ("0", "4", "16"):
+        monkeypatch.setenv("ESMM_VEC_PATTERNS", mode)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    monkeypatch.delenv("ESMM_VEC_PATTERNS")
+    A, B = workloads.tile_random(256, 256, 8 * 37, 0.5, 0.5, seed=18, gran_a=32, gran_b=32)      # 37 K blocks: bytes
     check_all_paths(cuda, pkg, oracle_mod, A, B)
