@@ -66,6 +66,8 @@ _SIGNATURES = {
     "esmm_selftest_bounded_wait": (_i, [C.c_uint, _vp]),
     "esmm_plan_create": (_i, [_i, _i, _i, _vp, _i, C.POINTER(_vp)]),
     "esmm_plan_run": (_i, [_vp, _vp, _vp]),
+    "esmm_plan_submit": (_i, [_vp, _vp, _vp]),
+    "esmm_plan_wait": (_i, [_vp]),
     "esmm_plan_destroy": (_i, [_vp]),
     "esmm_cublas_sgemm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp]),
     "esmm_ffma_peak_tflops": (_i, [C.POINTER(C.c_double), C.POINTER(_i)]),

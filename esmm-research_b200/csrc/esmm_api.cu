@@ -333,8 +333,8 @@ struct esmm_plan {
     int M, N, K, chunks;
     float *d_A, *d_B, *d_C, *d_a_packed;
     uint8_t *d_a_pat, *d_b_pat;
-    cudaStream_t streams[3];
-    cudaEvent_t up[64], done[64];
+    cudaStream_t streams[4];   // copies in, kernels of even chunks, kernels of odd chunks, copies out
+    cudaEvent_t up[64], done[64], down[64];
 };
 
 int esmm_plan_destroy(esmm_plan *pl)
@@ -346,11 +346,12 @@ int esmm_plan_destroy(esmm_plan *pl)
     cudaFree(pl->d_a_pat);
     cudaFree(pl->d_a_packed);
     cudaFree(pl->d_b_pat);
-    for (int i = 0; i < 3; ++i)
+    for (int i = 0; i < 4; ++i)
         if (pl->streams[i]) cudaStreamDestroy(pl->streams[i]);
     for (int i = 0; i < pl->chunks; ++i) {
         if (pl->up[i]) cudaEventDestroy(pl->up[i]);
         if (pl->done[i]) cudaEventDestroy(pl->done[i]);
+        if (pl->down[i]) cudaEventDestroy(pl->down[i]);
     }
     delete pl;
     return ESMM_OK;
@@ -387,10 +388,11 @@ int esmm_plan_create(int M, int N, int K, const float *h_B, int chunks, esmm_pla
     PLAN_TRY(cudaMalloc(&pl->d_a_pat, esmm_a_pattern_bytes(M, K, 32)));
     PLAN_TRY(cudaMalloc(&pl->d_a_packed, esmm_a_packed_bytes(M, K)));
     PLAN_TRY(cudaMalloc(&pl->d_b_pat, esmm_b_pattern_bytes(K, N)));
-    for (int i = 0; i < 3; ++i) PLAN_TRY(cudaStreamCreateWithFlags(&pl->streams[i], cudaStreamNonBlocking));
+    for (int i = 0; i < 4; ++i) PLAN_TRY(cudaStreamCreateWithFlags(&pl->streams[i], cudaStreamNonBlocking));
     for (int i = 0; i < chunks; ++i) {
         PLAN_TRY(cudaEventCreateWithFlags(&pl->up[i], cudaEventDisableTiming));
         PLAN_TRY(cudaEventCreateWithFlags(&pl->done[i], cudaEventDisableTiming));
+        PLAN_TRY(cudaEventCreateWithFlags(&pl->down[i], cudaEventDisableTiming));
     }
     PLAN_TRY(cudaMemcpy(pl->d_B, h_B, (size_t)K * N * 4, cudaMemcpyHostToDevice));
 #undef PLAN_TRY
@@ -406,11 +408,24 @@ int esmm_plan_create(int M, int N, int K, const float *h_B, int chunks, esmm_pla
 
 int esmm_plan_run(esmm_plan *pl, const float *h_A, float *h_C)
 {
+    const int st = esmm_plan_submit(pl, h_A, h_C);
+    return st != ESMM_OK ? st : esmm_plan_wait(pl);
+}
+
+int esmm_plan_wait(esmm_plan *pl)
+{
+    if (!pl) return ESMM_ERR_NULL;
+    ESMM_CUDA_TRY(cudaStreamSynchronize(pl->streams[3]));   // every copy out follows its chunk's kernels
+    return esmm_device_status(pl->streams[3]);
+}
+
+int esmm_plan_submit(esmm_plan *pl, const float *h_A, float *h_C)
+{
     if (!pl || !h_A || !h_C) return ESMM_ERR_NULL;
     const int M = pl->M, N = pl->N, K = pl->K;
     const int tiles = esmm::ceil_div(M, 128);
     const int nKB = esmm::ceil_div(K, esmm::BK);
-    cudaStream_t s_up = pl->streams[0], s_run = pl->streams[1], s_down = pl->streams[2];
+    cudaStream_t s_up = pl->streams[0], s_down = pl->streams[3];
     int tile0 = 0;
     for (int c = 0; c < pl->chunks; ++c) {
         const int tile1 = (int)((long)tiles * (c + 1) / pl->chunks);
@@ -418,10 +433,18 @@ int esmm_plan_run(esmm_plan *pl, const float *h_A, float *h_C)
         tile0 = tile1;
         if (r1 <= r0) continue;
         const size_t a_off = (size_t)r0 * K, c_off = (size_t)r0 * N;
+        // Chunks alternate between two kernel streams, so that the first CTAs of a chunk's GEMM fill the
+        // SMs that the last, partial wave of the chunk before leaves idle.
+        cudaStream_t s_run = pl->streams[1 + (c & 1)];
+        // The device buffers are reused by the next submission: its copy of A's chunk waits for this
+        // one's kernels, its kernels wait for this one's copy of C's chunk (events never recorded yet
+        // count as complete).
+        ESMM_CUDA_TRY(cudaStreamWaitEvent(s_up, pl->done[c], 0));
         ESMM_CUDA_TRY(cudaMemcpyAsync(pl->d_A + a_off, h_A + a_off, (size_t)(r1 - r0) * K * 4,
                                       cudaMemcpyHostToDevice, s_up));
         ESMM_CUDA_TRY(cudaEventRecord(pl->up[c], s_up));
         ESMM_CUDA_TRY(cudaStreamWaitEvent(s_run, pl->up[c], 0));
+        ESMM_CUDA_TRY(cudaStreamWaitEvent(s_run, pl->down[c], 0));
         uint8_t *apat = pl->d_a_pat + (size_t)(r0 / 32) * nKB;
         float *apacked = pl->d_a_packed + (size_t)r0 * nKB * esmm::BK;  // r0 is a multiple of 128
         int st = esmm::preprocess_a_pack_launch(pl->d_A + a_off, r1 - r0, K, apat, apacked, s_run);
@@ -433,9 +456,9 @@ int esmm_plan_run(esmm_plan *pl, const float *h_A, float *h_C)
         ESMM_CUDA_TRY(cudaStreamWaitEvent(s_down, pl->done[c], 0));
         ESMM_CUDA_TRY(cudaMemcpyAsync(h_C + c_off, pl->d_C + c_off, (size_t)(r1 - r0) * N * 4,
                                       cudaMemcpyDeviceToHost, s_down));
+        ESMM_CUDA_TRY(cudaEventRecord(pl->down[c], s_down));
     }
-    ESMM_CUDA_TRY(cudaStreamSynchronize(s_down));
-    return esmm_device_status(s_run);
+    return ESMM_OK;
 }
 
 // ---- baselines / helpers -----------------------------------------------------

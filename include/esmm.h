@@ -205,6 +205,16 @@ int esmm_selftest_bounded_wait(unsigned budget_us, void *stream);
 typedef struct esmm_plan esmm_plan;
 int esmm_plan_create(int M, int N, int K, const float *h_B, int chunks, esmm_plan **plan);
 int esmm_plan_run(esmm_plan *plan, const float *h_A, float *h_C);
+/*
+ * The two halves of esmm_plan_run.  esmm_plan_submit only enqueues (copies, kernels, copies back) and
+ * returns; esmm_plan_wait returns when everything submitted to the plan has landed in its h_C, with
+ * the device status.  Several submissions to one plan, or to several plans, may be in flight: the copies
+ * of one overlap the kernels of another (a plan's device buffers are handed from one submission to the
+ * next chunk by chunk).  h_A and h_C must be pinned host memory for the copies to be asynchronous, and
+ * must stay valid and untouched until the wait returns.
+ */
+int esmm_plan_submit(esmm_plan *plan, const float *h_A, float *h_C);
+int esmm_plan_wait(esmm_plan *plan);
 int esmm_plan_destroy(esmm_plan *plan);
 
 /* ---- comparison baselines, measurement helpers ---------------------------- */

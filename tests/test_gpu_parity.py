@@ -433,6 +433,26 @@ def test_plan_host_buffers(cuda, pkg, oracle_mod):
         pkg.check(pkg.lib().esmm_plan_run(plan, hA.data_ptr(), hC.data_ptr()), "plan_run twice")
         assert np.array_equal(hC.numpy(), Cref), chunks
         pkg.lib().esmm_plan_destroy(plan)
+    # several submissions in flight on one plan (different inputs, own result buffers) and on a second plan
+    L = pkg.lib()
+    A2 = A[::-1].copy()
+    Cref2 = oracle_mod.gemm_joint(A2, B)
+    hA2, hC2, hC3 = cuda.from_numpy(A2).pin_memory(), cuda.empty((M, N)).pin_memory(), cuda.empty((M, N)).pin_memory()
+    p1, p2 = C.c_void_p(), C.c_void_p()
+    pkg.check(L.esmm_plan_create(M, N, K, B.ctypes.data, 3, C.byref(p1)), "plan_create")
+    pkg.check(L.esmm_plan_create(M, N, K, B.ctypes.data, 2, C.byref(p2)), "plan_create")
+    for rep in range(3):
+        for h in (hC, hC2, hC3):
+            h.fill_(float("nan"))
+        pkg.check(L.esmm_plan_submit(p1, hA.data_ptr(), hC.data_ptr()), "submit")
+        pkg.check(L.esmm_plan_submit(p1, hA2.data_ptr(), hC2.data_ptr()), "submit")
+        pkg.check(L.esmm_plan_submit(p2, hA2.data_ptr(), hC3.data_ptr()), "submit")
+        pkg.check(L.esmm_plan_wait(p1), "wait")
+        pkg.check(L.esmm_plan_wait(p2), "wait")
+        assert np.array_equal(hC.numpy(), Cref) and np.array_equal(hC2.numpy(), Cref2) and np.array_equal(hC3.numpy(), Cref2)
+    L.esmm_plan_destroy(p1)
+    L.esmm_plan_destroy(p2)
+    assert L.esmm_plan_submit(None, hA.data_ptr(), hC.data_ptr()) == pkg.ERR_NULL and L.esmm_plan_wait(None) == pkg.ERR_NULL
 
 
 def test_cublas_and_generators(cuda, pkg, oracle_mod):
