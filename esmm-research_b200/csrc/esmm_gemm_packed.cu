@@ -15,15 +15,16 @@
 //     for which row blocks and which column blocks the row is live.  On a tile whose K
 //     blocks do not all share one live byte, K blocks with more than `brow_bits` live k are
 //     appended whole (8 rows), so that they can be fetched as one box;
-//   * a TMA warp cuts the row list into stages of 32 rows and fetches each stage's rows into
+//   * three producer warps cut the row list into stages of 32 rows and fetch each stage's rows into
 //     a ring slot ([32][512 B] of A, [32][512 B] of B), guarded by full / empty mbarriers.
 //     Both operands are also described to the copy engine as 3-D tensors (column, k % 8,
 //     k / 8), so a stage whose rows are "the same c consecutive k offsets of 32 / c
 //     consecutive K blocks" (c = 1, 2, 4, 8: what uniform patterns such as 10000000,
 //     11000000, 11110000 and 11111111 produce) is ONE box per operand, landing in ascending
 //     k.  Other stages are fetched K block by K block (8-row boxes) and row by row, every
-//     lane issuing its own row.  A k that is dead for the whole tile costs neither a copy
-//     nor shared memory nor a slot in any loop;
+//     lane issuing its own row, the rows of a stage shared out among the producer warps (a
+//     copy costs its warp about 70 cycles of issue, and warps issue in parallel).  A k that is
+//     dead for the whole tile costs neither a copy nor shared memory nor a slot in any loop;
 //   * a tile all of whose K blocks hold the same run of 1, 2, 4 or 8 consecutive live k, live for all
 //     of its row and column blocks (what uniform patterns, and dense inputs, give), needs no row
 //     list at all: its stages are computed arithmetically and are all-live;
@@ -55,9 +56,19 @@ constexpr int ROWS_PER_STAGE = 32;
 constexpr int STAGE_HALF_BYTES = ROWS_PER_STAGE * ROW_BYTES;   // 16384: A rows, then B rows
 constexpr int PSTAGE_BYTES = 2 * STAGE_HALF_BYTES;             // 32768
 constexpr int P_CONSUMER_WARPS = 8;
-constexpr int P_TMA_WARP = P_CONSUMER_WARPS;
-constexpr int P_MASK_WARP = P_CONSUMER_WARPS + 1;
-constexpr int P_THREADS = (P_CONSUMER_WARPS + 2) * 32;         // 320
+// Issuing a tensor copy costs the issuing warp about 70 cycles per active lane, whatever the box size,
+// and different warps issue in parallel (measured: 32, 64 and 128 single-row copies from 1, 2 and 4
+// warps all land within the same 2200 cycles).  A stage fetched row by row is 64 copies, so the rows
+// of a stage are spread over several producer warps.
+// Three of them: with the 8 consumer warps and the mask warp that is 12 warps, 3 per SM sub-partition,
+// which leaves each thread up to 168 registers (a 13th warp would cap them at 128).
+#ifndef ESMM_TMA_WARPS
+#define ESMM_TMA_WARPS 3
+#endif
+constexpr int P_TMA_WARPS = ESMM_TMA_WARPS;                    // 1 .. 3
+constexpr int P_TMA_WARP = P_CONSUMER_WARPS;                   // first producer warp
+constexpr int P_MASK_WARP = P_CONSUMER_WARPS + P_TMA_WARPS;
+constexpr int P_THREADS = (P_CONSUMER_WARPS + P_TMA_WARPS + 1) * 32;
 constexpr int P_MAX_STAGES = 6;
 
 // Optional timeline for tuning (build with -DESMM_TRACE): CTA 0 stamps %globaltimer at a few points
@@ -84,6 +95,8 @@ struct PackedParams {
     int tiles_m, tiles_n, num_tiles;
     int stages;
     int brow_bits;   // K blocks with more live k than this are fetched whole
+    int row_density; // ... on tiles with at most this many live k per K block on average; denser tiles
+                     // fetch every live K block whole
     int b_runs_ok;   // K % 8 == 0: the 3-D view of B stays inside the matrix
     int force_listed;  // tuning aid: take the index-list path even for all-live stages
     int no_run_tiles;  // tuning aid: build the row list even for tiles that need none
@@ -494,7 +507,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(lfull0 + 8 * b, 1);
-            mbar_init(lempty0 + 8 * b, P_CONSUMER_WARPS + 1);
+            mbar_init(lempty0 + 8 * b, P_CONSUMER_WARPS + P_TMA_WARPS);
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -546,7 +559,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             // uniform tile: list live k only.  Otherwise single rows cost a copy each, which pays
             // only on sparse tiles (on average at most 2 live k per K block); denser tiles list
             // every live K block whole.
-            const int whole_above = uniform ? BK : (live_total <= 2 * p.nKB ? p.brow_bits : 0);
+            const int whole_above = uniform ? BK : (live_total <= p.row_density * p.nKB ? p.brow_bits : 0);
             // a run tile?  c = 1, 2, 4 or 8 consecutive live k, whole stages only, 3-D view of B valid
             int run_code = 0;
             {
@@ -600,9 +613,15 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
             if (it == 0) ESMM_STAMP(1);
         }
-    } else if (warp == P_TMA_WARP) {
-        // ---------------- TMA warp: one lane per row of the stage ----------------
-        if (lane < 12) tma_prefetch_descriptor(&maps.a_row + lane);
+    } else if (warp >= P_TMA_WARP) {
+        // ---------------- producer warps: one lane per row of the stage ----------------
+        // All of them walk the row list and take the same decisions; producer q issues the copies of
+        // rows 32 q / P .. of each stage, producer 0 also the stage's byte count and whole-stage boxes.
+        // (A copy may complete before producer 0 has posted the byte count: the barrier's transaction
+        // count then goes negative for a moment, which it is allowed to, and the phase cannot complete
+        // before producer 0's arrival.)
+        const int q = warp - P_TMA_WARP;
+        if (q == 0 && lane < 12) tma_prefetch_descriptor(&maps.a_row + lane);
         int slot = 0;
         uint32_t phase = 0;
         uint32_t issued_bits = 0, parity_bits = 0;  // per slot: ever issued / parity of last issue
@@ -624,19 +643,24 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 // a run tile: whole stages, each one box per operand, no row list
                 const int lc = run_code & 15, kk0 = (run_code >> 4) & 7;
                 for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
+                    // (every producer waits for every stage's slot, also where it has nothing to copy: a
+                    // parity wait only tells "this phase" from "the one before", so no producer may get
+                    // more than one lap of the ring ahead of the consumers)
                     ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
                     if (!ok) break;
                     const uint32_t full = full0 + 8 * slot;
-                    if (lane == 0) {
+                    if (q == 0 && lane == 0) {
                         mbar_arrive_expect_tx(full, (uint32_t)ROWS_PER_STAGE * STAGE_ROW_BYTES);
                         const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
                         const int kb0 = r0 >> lc;
                         tma_load_3d(s0, &maps.a_run[lc], a_x, kk0, panel * p.nKB + kb0, full);
                         tma_load_3d(s0 + STAGE_HALF_BYTES, &maps.b_run[lc], b_col0, kk0, kb0, full);
                     }
-                    issued_bits |= 1u << slot;
-                    parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
-                    if (it == 0) ESMM_STAMP(400 + r0 / ROWS_PER_STAGE);
+                    if (q == 0) {
+                        issued_bits |= 1u << slot;
+                        parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
+                    }
+                    if (it == 0 && q == 0) ESMM_STAMP(400 + r0 / ROWS_PER_STAGE);
                     if (++slot == p.stages) {
                         slot = 0;
                         phase ^= 1;
@@ -666,30 +690,36 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 unsigned cover = lead_mask | (lead_mask << 1);
                 cover |= cover << 2;
                 cover |= cover << 4;                                  // rows fetched by some 8-row box
+                // my share of the stage: the rows (or leading rows of 8-row boxes) in my lane group
+                const bool mine = ((lane * P_TMA_WARPS) >> 5) == q;
+                const bool box8 = run < 0 && lead8 && mine;
+                const bool row1 = run < 0 && !lead8 && valid && !((cover >> lane) & 1u) && mine;
                 ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
-                const uint32_t full = full0 + 8 * slot;
-                if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * STAGE_ROW_BYTES);
-                __syncwarp();
-                const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
-                const uint32_t sa = s0 + lane * A_ROW;
-                const uint32_t sb = s0 + STAGE_HALF_BYTES + lane * ROW_BYTES;
-                if (run >= 0) {
-                    if (lane == 0) {
-                        tma_load_3d(sa, &maps.a_run[run], a_x, kk0, panel * p.nKB + kb0, full);
-                        tma_load_3d(sb, &maps.b_run[run], b_col0, kk0, kb0, full);
+                if (q == 0 || __any_sync(0xFFFFFFFFu, box8 || row1)) {
+                    const uint32_t full = full0 + 8 * slot;
+                    if (q == 0 && lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * STAGE_ROW_BYTES);
+                    __syncwarp();
+                    const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
+                    const uint32_t sa = s0 + lane * A_ROW;
+                    const uint32_t sb = s0 + STAGE_HALF_BYTES + lane * ROW_BYTES;
+                    if (run >= 0) {
+                        if (q == 0 && lane == 0) {
+                            tma_load_3d(sa, &maps.a_run[run], a_x, kk0, panel * p.nKB + kb0, full);
+                            tma_load_3d(sb, &maps.b_run[run], b_col0, kk0, kb0, full);
+                        }
+                    } else if (box8) {
+                        tma_load_2d(sa, &maps.a_kb, a_x, a_row0 + k, full);
+                        tma_load_2d(sb, &maps.b_kb, b_col0, k, full);
+                    } else if (row1) {
+                        tma_load_2d(sa, &maps.a_row, a_x, a_row0 + k, full);
+                        tma_load_2d(sb, &maps.b_row, b_col0, k, full);
                     }
-                } else if (lead8) {
-                    tma_load_2d(sa, &maps.a_kb, a_x, a_row0 + k, full);
-                    tma_load_2d(sb, &maps.b_kb, b_col0, k, full);
-                } else if (valid && !((cover >> lane) & 1u)) {
-                    tma_load_2d(sa, &maps.a_row, a_x, a_row0 + k, full);
-                    tma_load_2d(sb, &maps.b_row, b_col0, k, full);
+                    issued_bits |= 1u << slot;
+                    parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
                 }
-                issued_bits |= 1u << slot;
-                parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
-                if (it == 0) ESMM_STAMP(400 + r0 / ROWS_PER_STAGE);
+                if (it == 0 && q == 0) ESMM_STAMP(400 + r0 / ROWS_PER_STAGE);
                 if (++slot == p.stages) {
                     slot = 0;
                     phase ^= 1;
@@ -730,6 +760,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             const uint8_t *rmask = reinterpret_cast<const uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
             const int n = nrows[buf];
             const bool run_tile = runinfo[buf] != 0;
+            if (warp == 0) ESMM_STAMP(600 + 4 * it);
 
             Acc acc;
 #pragma unroll
@@ -783,6 +814,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             if (!ok) break;
             __syncwarp();
             if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+            if (warp == 0) ESMM_STAMP(601 + 4 * it);
 
             // epilogue: C is overwritten (beta = 0); un-scramble the 2 x 2 blocks into rows
             const int row0 = tm * TM_ROWS + wm * 32 * WMB + lm * 4;
@@ -806,6 +838,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     }
                 }
             }
+            if (warp == 0) ESMM_STAMP(602 + 4 * it);
         }
     }
 
@@ -853,9 +886,10 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     if (forced_rows == 64 || forced_rows == TILE_M) tile_rows = forced_rows;
     p.tiles_m = ceil_div(M, tile_rows);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.brow_bits = env_int("ESMM_BROW_BITS", 3);
+    p.brow_bits = env_int("ESMM_BROW_BITS", 6);
     if (p.brow_bits < 0) p.brow_bits = 0;
     if (p.brow_bits > 8) p.brow_bits = 8;
+    p.row_density = env_int("ESMM_ROW_DENSITY", 6);
     p.force_listed = env_int("ESMM_FORCE_LISTED", 0);
     p.no_run_tiles = env_int("ESMM_NO_RUN_TILES", 0);
     const uintptr_t pat_bits = (uintptr_t)d_a_pat | (uintptr_t)d_b_pat;
