@@ -64,6 +64,8 @@ _SIGNATURES = {
     "esmm_sgemm_joint_static": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "esmm_device_status": (_i, [_vp]),
     "esmm_selftest_bounded_wait": (_i, [C.c_uint, _vp]),
+    "esmm_cusparse_spmm": (_i, [_i, _i, _i, _vp, _vp, _vp, _i, C.POINTER(_f), C.POINTER(_f),
+                                C.POINTER(C.c_longlong)]),
     "esmm_plan_create": (_i, [_i, _i, _i, _vp, _i, C.POINTER(_vp)]),
     "esmm_plan_run": (_i, [_vp, _vp, _vp]),
     "esmm_plan_submit": (_i, [_vp, _vp, _vp]),

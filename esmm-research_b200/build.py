@@ -1,4 +1,4 @@
-"""Builds libesmm_b200.so (the C-ABI library) and exec_b200 (the driver CLI) in-tree with
+"""Builds libesmm_b200.so (the C-ABI library), exec_b200 (the driver CLI) and cusparse_bench in-tree with
 nvcc for sm_100a.  Usage: `python build.py [--force] [--verbose]`."""
 from __future__ import annotations
 
@@ -11,11 +11,14 @@ ROOT = os.path.dirname(HERE)
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 LIB = os.path.join(HERE, "libesmm_b200.so")
 EXE = os.path.join(HERE, "exec_b200")
+SPARSE_EXE = os.path.join(HERE, "cusparse_bench")
+SPARSE_SRC = os.path.join(HERE, "cusparse_bench.cu")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo"] + ARCH
 
 LIB_SRCS = [os.path.join(HERE, "csrc", f) for f in
-            ("esmm_gemm.cu", "esmm_gemm_packed.cu", "esmm_preprocess.cu", "esmm_api.cu", "esmm_noalloc.cu")]
+            ("esmm_gemm.cu", "esmm_gemm_packed.cu", "esmm_preprocess.cu", "esmm_api.cu", "esmm_noalloc.cu",
+             "esmm_cusparse.cu")]
 LIB_DEPS = LIB_SRCS + [os.path.join(HERE, "csrc", "esmm_common.cuh"), os.path.join(HERE, "csrc", "esmm_gemm_shared.cuh"), os.path.join(ROOT, "include", "esmm.h")]
 EXE_SRCS = [os.path.join(HERE, "driver.cu")]
 EXE_DEPS = EXE_SRCS + [os.path.join(ROOT, "include", "runners.cuh"), os.path.join(ROOT, "include", "esmm.h")]
@@ -32,12 +35,17 @@ def build(force: bool = False, verbose: bool = False) -> str:
     srcs = [s for s in LIB_SRCS if os.path.exists(s)]
     if force or _stale(LIB, LIB_DEPS):
         cmd = [NVCC] + COMMON + (["-Xptxas", "-v"] if verbose else []) + \
-              ["-Xcompiler", "-fPIC", "-shared", "-o", LIB] + srcs + ["-lcublas"]
+              ["-Xcompiler", "-fPIC", "-shared", "-o", LIB] + srcs + ["-lcublas", "-lcusparse"]
         print("+", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)
     if os.path.exists(EXE_SRCS[0]) and (force or _stale(EXE, EXE_DEPS + [LIB])):
         cmd = [NVCC] + COMMON + ["-I" + ROOT, "-o", EXE] + EXE_SRCS + \
               ["-L" + HERE, "-lesmm_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
+        print("+", " ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
+    if os.path.exists(SPARSE_SRC) and (force or _stale(SPARSE_EXE, [SPARSE_SRC, os.path.join(ROOT, "include", "esmm.h"), LIB])):
+        cmd = [NVCC] + COMMON + ["-I" + ROOT, "-o", SPARSE_EXE, SPARSE_SRC,
+                                 "-L" + HERE, "-lesmm_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN"]
         print("+", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)
     return LIB

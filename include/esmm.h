@@ -227,6 +227,14 @@ int esmm_cublas_sgemm(int M, int N, int K, const float *d_A, const float *d_B, f
  * chains on every SM, timed with CUDA events); *sm_count gets the SM count. */
 int esmm_ffma_peak_tflops(double *tflops, int *sm_count);
 
+/* cuSPARSE SpMM baseline (src/benchmarks/cusparse_benchmark.cu:56-247): A (M x K, row-major, dense
+ * storage) is converted to CSR and multiplied with dense B into C.  *spmm_ms: average of `runs` SpMM
+ * calls with A already in CSR; *total_ms: average of `runs` (conversion + SpMM) calls; *nnz: stored
+ * nonzeros of A (the work is 2 * nnz * N flops).  Library calls only, allocates and frees its own
+ * buffers, synchronises the device.  Any output pointer may be NULL. */
+int esmm_cusparse_spmm(int M, int N, int K, const float *d_A, const float *d_B, float *d_C, int runs,
+                       float *spmm_ms, float *total_ms, long long *nnz);
+
 /* Counter-based N(mean, std) generator with block-structured zeros, on the device.
  * Element (r, c) of a rows x cols row-major matrix; k = c when k_axis == 0 (matrix A),
  * k = r when k_axis == 1 (matrix B); the other index is the "outer" index.
