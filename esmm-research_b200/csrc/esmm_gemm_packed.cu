@@ -853,12 +853,19 @@ extern "C" int esmm_trace_read(unsigned long long *host, int n)
 }
 #endif
 
+// esmm_gemm_skinny.cu: the kernel for M <= 32
+bool gemm_ab_skinny_applies(int M, int N, int K);
+int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                          const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream);
+
 int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                           const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream)
 {
     if (!d_a_packed || !d_B || !d_C || !d_a_pat || !d_b_pat) return ESMM_ERR_NULL;
     if (M <= 0 || N <= 0 || K <= 0 || (K & 3) || (N & 3)) return ESMM_ERR_SHAPE;
     if (((uintptr_t)d_a_packed | (uintptr_t)d_B | (uintptr_t)d_C) & 15) return ESMM_ERR_ALIGN;
+    if (gemm_ab_skinny_applies(M, N, K))
+        return gemm_ab_skinny_launch(M, N, K, d_a_packed, d_B, d_C, d_a_pat, d_b_pat, stream);
 
     PackedParams p;
     memset(&p, 0, sizeof p);

@@ -255,6 +255,26 @@ def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, monkeypatch, rows):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
+@pytest.mark.parametrize("skinny", [1, 0])
+def test_gemm_few_rows(cuda, pkg, oracle_mod, monkeypatch, skinny):
+    """M <= 32 (one pattern block of A) and N >= 128 runs the strip kernel (one CTA per 32 columns); the same
+    inputs with that kernel switched off go through the tiled kernel.  Same bits as the oracle either way."""
+    if not skinny:
+        monkeypatch.setenv("ESMM_NO_SKINNY", "1")
+    for M, N, K, pa, pb in [(16, 256, 256, 0.5, 0.5), (32, 1408, 1024, 0.4, 0.6), (1, 128, 64, 1.0, 1.0),
+                            (31, 132, 8 * 37, 0.7, 0.3), (8, 512, 4096, 0.2, 0.9), (32, 160, 76, 0.8, 0.8),
+                            (24, 256, 2048, 0.0, 0.5)]:
+        A, B = workloads.tile_random(M, N, K, pa, pb, seed=M + N + K, gran_a=32, gran_b=32)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    for pat in (0xFF, 0x0F, 0x81):
+        A, B = workloads.uniform_pattern(32, 384, 512, pat, seed=pat)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.llm_mlp(16, 1408, 2048, seed=5)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.all_byte_values(M=32, N=256, seed=6)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
 def test_gemm_coarser_and_finer_a_patterns(cuda, pkg, oracle_mod):
     """A pattern granularities of the other joint-sparse kernel ids (64 rows: ids 20/25, 8 rows: id 21)
     give the same C as 32 rows: the extra terms they admit or drop are exact zeros."""
