@@ -371,6 +371,40 @@ def run_ours(args) -> None:
         cpu_baseline = {"value": 2.0 * rows * N * K / dt / 1e12, "unit": "TFLOP/s", "cores": cpu.threads,
                         "kind": cpu.kind, "sample": sample, "seconds": dt}
 
+    # ---- the multi-GPU workload on this one GPU: the base the --gpus N > 1 lines (workload c5) compare with ----
+    scaling_base = None
+    if world == 1 and workload == "c2" and not args.no_scaling_base:
+        S5 = 16384
+        A5 = torch.empty((S5, S5), device=dev)
+        B5 = torch.empty((S5, S5), device=dev)
+        C5 = torch.empty((S5, S5), device=dev)
+        pkg.fill_normal(A5.data_ptr(), S5, S5, 0, 1, mode=1, pattern=0x03)
+        pkg.fill_normal(B5.data_ptr(), S5, S5, 1, 1000, mode=1, pattern=0x03)
+        bp5 = torch.empty(L.esmm_b_pattern_bytes(S5, S5), dtype=torch.uint8, device=dev)
+        pkg.preprocess_b(B5.data_ptr(), S5, S5, bp5.data_ptr())
+        ws5 = torch.empty(pkg.sgemm_joint_workspace_bytes(S5, S5), dtype=torch.uint8, device=dev)
+
+        def step5():
+            pkg.sgemm_joint(S5, S5, S5, A5.data_ptr(), B5.data_ptr(), C5.data_ptr(), bp5.data_ptr(), ws5.data_ptr())
+
+        for _ in range(3):
+            step5()
+        torch.cuda.synchronize()
+        n5 = 5
+        a5, b5 = ev(), ev()
+        a5.record()
+        for _ in range(n5):
+            step5()
+        b5.record()
+        torch.cuda.synchronize()
+        pkg.device_status()
+        ms5 = a5.elapsed_time(b5) / n5
+        scaling_base = {"workload": "c5: M=N=K=16384 FP32, pattern 11000000, on this one GPU", "ms_per_step": ms5,
+                        "value": 2.0 * S5 ** 3 / (ms5 * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": n5,
+                        "note": "bench.py --gpus N > 1 runs this workload column-sharded; its value / this value is the "
+                                "speed-up over one GPU (the N = 1 headline above is workload c2, a different problem)"}
+        del A5, B5, C5, bp5, ws5
+
     if rank == 0:
         line = {
             "metric": "dense-equivalent TFLOP/s at 4096^3 FP32 vs block density, incl. A-pattern preprocess"
@@ -392,7 +426,7 @@ def run_ours(args) -> None:
             "sweep": sweep, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(args.steps * len(cases) * 2), "clocks": clocks,
             "ffma_peak_tflops_measured": ffma_peak, "hbm_peak_gbs": hbm_peak, "hbm_peak_source": hbm_src,
-            "sm_count": sms, "gather_c": gather,
+            "sm_count": sms, "gather_c": gather, "scaling_base": scaling_base,
         }
         print(json.dumps(line), flush=True)
     if dist is not None:
@@ -415,6 +449,7 @@ def main() -> None:
     ap.add_argument("--size", type=int, default=None, help="override M = N = K (experiments only)")
     ap.add_argument("--chunks", type=int, default=8, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-scaling-base", action="store_true", help="skip the single-GPU run of the multi-GPU workload")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
