@@ -377,7 +377,7 @@ def run_ours(args) -> None:
 
     # ---- the multi-GPU workload on this one GPU: the base the --gpus N > 1 lines (workload c5) compare with ----
     scaling_base = None
-    if world == 1 and workload == "c2" and not args.no_scaling_base:
+    if rank == 0 and not args.no_scaling_base and (workload == "c2" or world > 1) and not args.size:
         S5 = 16384
         A5 = torch.empty((S5, S5), device=dev)
         B5 = torch.empty((S5, S5), device=dev)
@@ -406,8 +406,10 @@ def run_ours(args) -> None:
         scaling_base = {"workload": "c5: M=N=K=16384 FP32, pattern 11000000, on this one GPU", "ms_per_step": ms5,
                         "value": 2.0 * S5 ** 3 / (ms5 * 1e-3) / 1e12, "unit": "TFLOP/s", "steps": n5,
                         "note": "bench.py --gpus N > 1 runs this workload column-sharded; its value / this value is the "
-                                "speed-up over one GPU (the N = 1 headline above is workload c2, a different problem)"}
+                                "speed-up over one GPU (the N = 1 headline is workload c2, a different problem)"}
         del A5, B5, C5, bp5, ws5
+    if dist is not None:
+        barrier()   # the other ranks wait for rank 0's single-GPU run
 
     if rank == 0:
         line = {
