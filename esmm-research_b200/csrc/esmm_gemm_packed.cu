@@ -230,7 +230,8 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
 // first write the rows' offsets as a list (in parallel, while the stage may still be in flight) and
 // the loop takes two rows per step from it.  (Measured on random 32-granular patterns: one pass over
 // jt | jb with warp-uniform branches per block is 20 % slower than the two passes, bit walking in
-// the half modes 3-5 % slower than lists, lists in mode BOTH 4 % slower than bit walking.)
+// the half modes 3-5 % slower than lists, lists in mode BOTH 4 % slower than bit walking, a switch
+// per nibble of the mask into straight-line code 38 % slower.)
 enum { MODE_BOTH = 0, MODE_TOP = 1, MODE_BOTTOM = 2 };
 
 template <int MODE, int WMB>
