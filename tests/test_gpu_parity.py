@@ -275,6 +275,22 @@ def test_gemm_few_rows(cuda, pkg, oracle_mod, monkeypatch, skinny):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
+def test_gemm_random_shapes(cuda, pkg, oracle_mod):
+    """Seeded random shapes and densities (ragged M, N % 4 == 0, K % 4 == 0, all three kernels and both tilings get
+    their share through the launch heuristics): same bits as the oracle everywhere."""
+    rng = np.random.default_rng(2024)
+    for case in range(40):
+        M = int(rng.integers(1, 320))
+        N = 4 * int(rng.integers(1, 130))
+        K = 4 * int(rng.integers(1, 160))
+        pa, pb = float(rng.choice([0.1, 0.3, 0.6, 1.0])), float(rng.choice([0.1, 0.4, 0.8, 1.0]))
+        A, B = workloads.tile_random(M, N, K, pa, pb, seed=1000 + case, gran_a=32, gran_b=32)
+        if case % 5 == 0:       # a few exact zeros and negative zeros inside live blocks
+            A[rng.integers(0, M), :] = 0.0
+            B[:, rng.integers(0, N)] = -0.0
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
 def test_gemm_coarser_and_finer_a_patterns(cuda, pkg, oracle_mod):
     """A pattern granularities of the other joint-sparse kernel ids (64 rows: ids 20/25, 8 rows: id 21)
     give the same C as 32 rows: the extra terms they admit or drop are exact zeros."""
