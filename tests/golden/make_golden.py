@@ -2,7 +2,7 @@
 (oracle/_ref/libesmm_ref.so, built by oracle/Makefile from the reference tree).
 
   python tests/golden/make_golden.py cpu   # needs no GPU: reference host functions
-  python tests/golden/make_golden.py gpu   # needs a GPU: reference pattern kernels + kernel id 29
+  python tests/golden/make_golden.py gpu [output directory]   # needs a GPU: reference pattern kernels + kernel id 29
 
 cpu -> ref_cpu.npz : inputs drawn by the reference's own rand()-based generators
                      (randomize_matrix_A_blocklevel<8,32>, randomize_matrix_B_blocklevel_fixed<8,32>,
@@ -10,8 +10,8 @@ cpu -> ref_cpu.npz : inputs drawn by the reference's own rand()-based generators
                      them, and the reference's kernel-selection parser / kernel names.
 gpu -> ref_gpu.npz : for seeded inputs (recreated by seed in the tests, not stored), the pattern
                      bytes of preprocess_ab<8,32,32> and the C of esmm_ab_optimized_v3 as run on a B200.
-The gpu mode writes into gpurun_out/ when that directory exists (it is what comes back from the GPU
-box); copy the file into tests/golden/ afterwards.
+The gpu mode writes ref_gpu.npz into the output directory given (default: tests/golden/ itself), for the case
+that the GPU machine is not the one that holds the repository.
 """
 from __future__ import annotations
 
@@ -105,7 +105,7 @@ def gpu() -> None:
             assert e == 0, e
             out[name + ".C"] = dC.cpu().numpy()
         out[name + ".shape"] = np.array([M, N, K])
-    dst = os.path.join(ROOT, "gpurun_out") if os.path.isdir(os.path.join(ROOT, "gpurun_out")) else HERE
+    dst = sys.argv[2] if len(sys.argv) > 2 else HERE
     np.savez_compressed(os.path.join(dst, "ref_gpu.npz"), **out)
     print("wrote", os.path.join(dst, "ref_gpu.npz"))
 
