@@ -311,7 +311,64 @@ def run_ours(args) -> None:
 
     # ---- end to end through the host-buffer entry point (pinned host A and C, copies inside) ----
     e2e = None
-    if rank == 0 or dist is not None:
+    if dist is not None:
+        # Multi-GPU: A lives in host memory once.  Every rank brings in 1 / world of its rows over its own PCIe
+        # link, an all-gather over NVLink completes the replicas, then the rank's shard is computed and its
+        # columns of C go back to host memory.
+        c = cases[0]
+        n_chunks = max(1, args.chunks)
+        while n_chunks > 1 and M % (n_chunks * 128 * world):
+            n_chunks -= 1
+        rows_c = M // n_chunks                      # rows per chunk: whole tiles, equal slices per rank
+        rows_s = rows_c // world
+        dA = torch.empty((M, K), device=dev)
+        hC = torch.empty((M, Nl), pin_memory=True)
+        hA = []                                     # this rank's slice of every chunk, pinned
+        for i in range(n_chunks):
+            h = torch.empty((rows_s, K), pin_memory=True)
+            h.copy_(c["A"][i * rows_c + rank * rows_s:i * rows_c + (rank + 1) * rows_s])
+            hA.append(h)
+        ws_c = [torch.empty(pkg.sgemm_joint_workspace_bytes(rows_c, K), dtype=torch.uint8, device=dev)
+                for _ in range(n_chunks)]
+        s_up, s_run, s_down = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+        ev_up = [torch.cuda.Event() for _ in range(n_chunks)]
+        ev_run = [torch.cuda.Event() for _ in range(n_chunks)]
+
+        def e2e_step():
+            # chunks of rows: slice in + all-gather on one stream, packing + GEMM on a second, C out on a third
+            for i in range(n_chunks):
+                rows = slice(i * rows_c, (i + 1) * rows_c)
+                with torch.cuda.stream(s_up):
+                    sharding.upload_rows_replicated(hA[i], dA[rows], rank, world, dist)
+                    ev_up[i].record(s_up)
+                s_run.wait_event(ev_up[i])
+                pkg.sgemm_joint(rows_c, Nl, K, dA[rows].data_ptr(), c["B"].data_ptr(), Cd[rows].data_ptr(),
+                                c["bp"].data_ptr(), ws_c[i].data_ptr(), stream=s_run.cuda_stream)
+                ev_run[i].record(s_run)
+                s_down.wait_event(ev_run[i])
+                with torch.cuda.stream(s_down):
+                    hC[rows].copy_(Cd[rows], non_blocking=True)
+            torch.cuda.synchronize()
+
+        for _ in range(2):
+            e2e_step()
+        assert torch.equal(dA, c["A"])       # the replica assembled from the ranks' slices is A
+        barrier()
+        e2e_steps = max(1, min(args.steps, 10))
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        barrier()
+        dt = sharding.max_over_ranks(time.perf_counter() - t0, dist, dev)
+        pkg.device_status()
+        e2e = {"value": flops_dense * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(4 * M * K), "d2h_bytes_per_step": int(4 * M * N),
+               "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps, "chunks": n_chunks,
+               "note": "whole job per step, in row chunks on three streams: every rank copies 1 / world of the chunk's "
+                       "rows of A from pinned host memory, all-gather over NVLink, packing + GEMM on the rank's column "
+                       "shard, the chunk of C back to pinned host memory; B and its patterns resident"}
+        del dA, hA, hC, ws_c
+    elif rank == 0:
         import ctypes as C
         plans = []
         for c in cases:

@@ -2,8 +2,11 @@
 
 The reference has no multi-GPU code.  The joint-sparse SGEMM partitions without any exchange:
 rank g owns columns [n0, n1) of B, of the B patterns and of C; A and its patterns are replicated,
-and every rank runs the A preprocessor on its own replica.  A collective appears only when the
-caller wants all of C on one rank (`gather_columns`).
+and every rank runs the A preprocessor on its own replica.  A collective appears only at the two
+ends: when A arrives from host memory (`upload_rows_replicated`: every rank copies 1 / world of the
+rows over its own PCIe link and the replicas are completed by an all-gather over NVLink, instead of
+`world` full copies competing for host memory bandwidth) and when the caller wants all of C on one
+rank (`gather_columns`).
 
 Nothing here computes: the compute calls are the C-ABI entry points, made by the caller on its
 shard.  torch.distributed (NCCL on GPUs, gloo in the CPU tests) is the only dependency.
@@ -56,6 +59,33 @@ def max_over_ranks(value: float, dist, device=None) -> float:
     t = torch.tensor([value], dtype=torch.float64, device=device)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     return float(t.item())
+
+
+def row_slice(M: int, world: int, rank: int) -> tuple[int, int]:
+    """Rows [r0, r1) of A that rank `rank` brings in from host memory: equal slices (the all-gather is
+    a plain one), which needs M % world == 0."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"bad rank {rank} of {world}")
+    if M % world:
+        raise ValueError(f"M = {M} does not split into {world} equal row slices")
+    rows = M // world
+    return rank * rows, (rank + 1) * rows
+
+
+def upload_rows_replicated(h_rows, d_full, rank: int, world: int, dist) -> None:
+    """Makes d_full ([M, K], this rank's device replica of A) complete on every rank from host slices.
+
+    h_rows: this rank's rows [r0, r1) of A in (pinned) host memory, r0, r1 = row_slice(M, world, rank).
+    The slice is copied into its place in d_full and the other ranks' slices arrive by an in-place
+    all-gather.  Work on the current stream of d_full's device; with world == 1 it is a plain copy."""
+    M = d_full.shape[0]
+    r0, r1 = row_slice(M, world, rank)
+    if tuple(h_rows.shape) != (r1 - r0, d_full.shape[1]):
+        raise ValueError(f"host slice has shape {tuple(h_rows.shape)}, expected {(r1 - r0, d_full.shape[1])}")
+    mine = d_full[r0:r1]
+    mine.copy_(h_rows, non_blocking=True)
+    if world > 1:
+        dist.all_gather_into_tensor(d_full.view(-1), mine.view(-1))
 
 
 def gather_columns(c_shard, shard: ColumnShard, dist, interleave=None):

@@ -32,6 +32,12 @@ def _worker(rank, world, port, fail_rank, results):
         if not ready:
             results[rank] = "aborted"
             return
+        # A arrives from "host memory" in row slices, one per rank, and every rank ends with the whole of it
+        r0, r1 = sharding.row_slice(M, world, rank)
+        replica = torch.full((M, K), float("nan"))
+        sharding.upload_rows_replicated(torch.from_numpy(A[r0:r1].copy()), replica, rank, world, dist)
+        assert np.array_equal(replica.numpy(), A)
+        A = replica.numpy()
         Bs = np.ascontiguousarray(B[:, sh.n0:sh.n1])                 # contiguous K x N/G shard
         bp = oracle.preprocess_b(Bs)                                  # per-shard cached B patterns
         assert np.array_equal(bp, oracle.preprocess_b(B)[sh.n0 // 32:sh.n1 // 32])
@@ -75,3 +81,12 @@ def test_shard_columns_validation():
         sharding.shard_columns(4096, 8, 8)
     with pytest.raises(ValueError):
         sharding.shard_columns(4096, 4, 0, align=48)
+    assert [sharding.row_slice(4096, 4, r) for r in range(4)] == [(0, 1024), (1024, 2048), (2048, 3072), (3072, 4096)]
+    with pytest.raises(ValueError):
+        sharding.row_slice(4097, 4, 0)
+    import torch
+    full = torch.zeros((8, 4))
+    sharding.upload_rows_replicated(torch.ones((8, 4)), full, 0, 1, None)      # one rank: a plain copy
+    assert bool((full == 1).all())
+    with pytest.raises(ValueError):
+        sharding.upload_rows_replicated(torch.ones((4, 4)), full, 0, 1, None)
