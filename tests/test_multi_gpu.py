@@ -1,5 +1,5 @@
-"""Two ranks on two GPUs (NCCL): N-column shards computed through the C ABI, gathered and interleaved,
-must equal the single-GPU result bit for bit.  Skipped on a box with fewer than two GPUs; the host
+"""Two ranks on two GPUs (NCCL): A assembled on every rank from per-rank row uploads, N-column shards computed
+through the C ABI, gathered and interleaved, must equal the single-GPU result bit for bit.  Skipped on a box with fewer than two GPUs; the host
 logic is also covered without GPUs by tests/test_sharding_cpu.py."""
 import os
 import sys
@@ -40,6 +40,12 @@ def _worker(rank, world, port, results):
             return c
 
         ok = sharding.preflight(True, dist, torch.device("cuda", rank))
+        # A from host memory: each rank uploads its rows, the all-gather completes every replica
+        r0, r1 = sharding.row_slice(M, world, rank)
+        replica = torch.full((M, K), float("nan"), device="cuda")
+        sharding.upload_rows_replicated(torch.from_numpy(A[r0:r1].copy()).pin_memory(), replica, rank, world, dist)
+        torch.cuda.synchronize()
+        ok = ok and torch.equal(replica.cpu(), torch.from_numpy(A))
         c_shard = joint(B[:, sh.n0:sh.n1])
 
         def interleave(staging, out, m, n, w):
