@@ -231,7 +231,10 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
 // the loop takes two rows per step from it.  (Measured on random 32-granular patterns: one pass over
 // jt | jb with warp-uniform branches per block is 20 % slower than the two passes, bit walking in
 // the half modes 3-5 % slower than lists, lists in mode BOTH 4 % slower than bit walking, a switch
-// per nibble of the mask into straight-line code 38 % slower.)
+// per nibble of the mask into straight-line code 38 % slower.  For masks made of bytes 0x00 / 0xFF
+// (block-pruned operands) a walk in groups of 8 rows with one three-way choice per group gained nothing
+// on a pruned-MLP shape - there the spread of live rows between the 8 warps of a stage is what costs -
+// and made the other paths 1-5 % slower.)
 enum { MODE_BOTH = 0, MODE_TOP = 1, MODE_BOTTOM = 2 };
 
 template <int MODE, int WMB>

@@ -275,6 +275,24 @@ def test_gemm_few_rows(cuda, pkg, oracle_mod, monkeypatch, skinny):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
+@pytest.mark.parametrize("rows", [128, 64])
+def test_gemm_block_structured(cuda, pkg, oracle_mod, monkeypatch, rows):
+    """Whole 8-deep blocks live or dead (pattern bytes 0x00 / 0xFF), what pruning at the pattern granularity gives:
+    the producers fetch whole K blocks, the consumers' masks come in bytes.  Both tilings, same bits as the oracle."""
+    monkeypatch.setenv("ESMM_TILE_M", str(rows))
+    for M, N, K, pa, pb in [(256, 384, 1024, 0.4, 0.5), (384, 256, 8 * 37, 0.7, 0.3), (200, 132, 512, 0.5, 0.9),
+                            (128, 128, 2048, 0.15, 0.15), (256, 256, 512, 1.0, 0.5), (256, 256, 512, 0.5, 1.0)]:
+        A, B = workloads.block_random(M, N, K, pa, pb, seed=M + N + K)
+        ap = oracle_mod.preprocess_a(A)
+        assert set(np.unique(ap)) <= {0, 255}
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    # blocks whose bytes are 0x00 / 0xFF only in some stages: mixed with single live k elsewhere
+    A, B = workloads.block_random(256, 256, 1024, 0.5, 0.5, seed=9)
+    A[:, 100] = 0.0
+    B[300, :] = 0.0
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
 def test_gemm_random_shapes(cuda, pkg, oracle_mod):
     """Seeded random shapes and densities (ragged M, N % 4 == 0, K % 4 == 0, all three kernels and both tilings get
     their share through the launch heuristics): same bits as the oracle everywhere."""

@@ -71,6 +71,20 @@ def llm_mlp(M, N, K, seed: int = 0, a_zero_frac: float = 0.6, b_keep_frac: float
     return np.ascontiguousarray(A[:, idx], np.float32), np.ascontiguousarray(B[idx, :], np.float32)
 
 
+def block_random(M, N, K, pa, pb, seed=0):
+    """Whole 32 x 8 blocks of A and 8 x 32 blocks of B live with probability pa / pb (every pattern byte
+    0x00 or 0xFF): what pruning at the pattern granularity produces."""
+    rng = np.random.default_rng(seed)
+    A = rng.standard_normal((M, K), dtype=np.float32)
+    B = rng.standard_normal((K, N), dtype=np.float32)
+    mb, nb, kb = -(-M // 32), -(-N // 32), -(-K // 8)
+    la = (rng.random((mb, kb)) < pa).astype(np.float32)
+    lb = (rng.random((nb, kb)) < pb).astype(np.float32)
+    A *= np.repeat(np.repeat(la, 32, axis=0), 8, axis=1)[:M, :K]
+    B *= np.repeat(np.repeat(lb, 32, axis=0), 8, axis=1)[:N, :K].T
+    return A, B
+
+
 def all_byte_values(M=256, N=256, seed=0):
     """A and B whose pattern arrays contain every byte value 0..255 (K = 256 * 8)."""
     K = 256 * 8
