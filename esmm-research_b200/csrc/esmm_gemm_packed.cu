@@ -234,7 +234,8 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
 // per nibble of the mask into straight-line code 38 % slower.  For masks made of bytes 0x00 / 0xFF
 // (block-pruned operands) a walk in groups of 8 rows with one three-way choice per group gained nothing
 // on a pruned-MLP shape - there the spread of live rows between the 8 warps of a stage is what costs -
-// and made the other paths 1-5 % slower.)
+// and made the other paths 1-5 % slower; preparing masks and lists one stage ahead (two list buffers)
+// was 2-5 % slower on every workload.)
 enum { MODE_BOTH = 0, MODE_TOP = 1, MODE_BOTTOM = 2 };
 
 template <int MODE, int WMB>
