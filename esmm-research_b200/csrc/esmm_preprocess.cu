@@ -15,6 +15,13 @@ namespace esmm {
 constexpr int PRE_THREADS = 128;
 
 // `v != 0.0f` as an integer test: -0.0f is zero, NaN and denormals are nonzero.
+// environment knob for tuning (read at every launch)
+static int env_int_pre(const char *name, int dflt)
+{
+    const char *v = getenv(name);
+    return v && *v ? atoi(v) : dflt;
+}
+
 __device__ __forceinline__ unsigned nz(float v) { return (__float_as_uint(v) << 1) != 0u; }
 
 __device__ __forceinline__ unsigned nz4(const float4 &v)
@@ -122,6 +129,70 @@ esmm_preprocess_a_pack_kernel(const float *__restrict__ A, int M, int K, int nMB
             const int k = kc * 128 + c;  // global k = kb * 8 + kk
             if (((liveq[c & 3] >> (c >> 2)) & 1u) && k < nKB * BK)
                 dst[(size_t)k * 128] = tile[c * 32 + ((lane + (c >> 2)) & 31)];
+        }
+        __syncwarp();
+    }
+}
+
+// The same with half the task (the default; ESMM_PACK=128 selects the kernel above): 32 rows x 64 columns per warp (8 KB in flight and 8 KB of shared
+// memory per warp instead of 16, half the registers), so that more warps are resident and the tail of
+// the grid is shorter.  Lane = (row parity h, column group cl): lane loads rows 2 i + h, columns
+// 4 cl .. 4 cl + 3.  Element (r, c) of the tile lives at c * 32 + ((r + 2 (c >> 2)) & 31): both the
+// stores (lanes differ in 2 cl + h) and the k-major loads (lanes differ in r) are conflict-free.
+constexpr int PACK64_SMEM_PER_WARP = 64 * 32 * 4;  // 8 KB
+
+__global__ void __launch_bounds__(PACK_WARPS * 32)
+esmm_preprocess_a_pack64_kernel(const float *__restrict__ A, int M, int K, int nMB, int nKB, int k_chunks,
+                                uint8_t *__restrict__ out, float *__restrict__ packed)
+{
+    extern __shared__ __align__(16) float pack_smem[];
+    float *tile = pack_smem + (threadIdx.x >> 5) * (PACK64_SMEM_PER_WARP / 4);
+    const int lane = threadIdx.x & 31;
+    const int h = lane >> 4, cl = lane & 15;
+    const long warps_total = (long)gridDim.x * PACK_WARPS;
+    const long tasks = (long)nMB * k_chunks;
+    for (long task = (long)blockIdx.x * PACK_WARPS + (threadIdx.x >> 5); task < tasks; task += warps_total) {
+        const int mb = (int)(task / k_chunks);
+        const int kc = (int)(task - (long)mb * k_chunks);
+        const int col = kc * 64 + cl * 4;
+        const bool col_ok = col < K;
+        const int row0 = mb * 32;
+        const float *src = A + (size_t)row0 * K + col;
+        float4 v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int r = 2 * i + h;
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (col_ok && row0 + r < M) v[i] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K));
+        }
+        unsigned nib = 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) nib |= nz4(v[i]);
+        nib |= __shfl_xor_sync(0xFFFFFFFFu, nib, 16);           // both row parities
+        // live columns of the chunk: bit cl of liveq[q] says column 4 cl + q has a nonzero
+        unsigned liveq[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) liveq[q] = __ballot_sync(0xFFFFFFFFu, (nib >> q) & 1u);
+        // only live columns go through the tile (and every store depends on all the loads, which keeps
+        // them in flight together)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const int pos = (2 * i + h + 2 * cl) & 31;
+            if (nib & 1u) tile[(cl * 4 + 0) * 32 + pos] = v[i].x;
+            if (nib & 2u) tile[(cl * 4 + 1) * 32 + pos] = v[i].y;
+            if (nib & 4u) tile[(cl * 4 + 2) * 32 + pos] = v[i].z;
+            if (nib & 8u) tile[(cl * 4 + 3) * 32 + pos] = v[i].w;
+        }
+        const unsigned other = __shfl_xor_sync(0xFFFFFFFFu, nib, 1);
+        const int kb_lane = kc * 8 + (cl >> 1);
+        if (h == 0 && !(cl & 1) && kb_lane < nKB) out[(size_t)mb * nKB + kb_lane] = (uint8_t)(nib | (other << 4));
+        __syncwarp();
+        float *dst = packed + (size_t)(mb >> 2) * nKB * BK * 128 + (mb & 3) * 32 + lane;
+#pragma unroll 8
+        for (int c = 0; c < 64; ++c) {
+            const int k = kc * 64 + c;  // global k = kb * 8 + kk
+            if (((liveq[c & 3] >> (c >> 2)) & 1u) && k < nKB * BK)
+                dst[(size_t)k * 128] = tile[c * 32 + ((lane + 2 * (c >> 2)) & 31)];
         }
         __syncwarp();
     }
@@ -248,10 +319,31 @@ int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, flo
     if (!d_A || !d_out || !d_packed) return ESMM_ERR_NULL;
     if (M <= 0 || K <= 0 || (K & 3)) return ESMM_ERR_SHAPE;
     if (((uintptr_t)d_A | (uintptr_t)d_packed) & 15) return ESMM_ERR_ALIGN;
-    const int nMB = ceil_div(M, 32), nKB = ceil_div(K, BK), k_chunks = ceil_div(K, 128);
-    const long tasks = (long)nMB * k_chunks;
+    const int nMB = ceil_div(M, 32), nKB = ceil_div(K, BK);
     const int sms = sm_count();
     if (sms <= 0) return record_cuda_error_text("no CUDA device");
+    if (env_int_pre("ESMM_PACK", 64) == 64) {
+        const int k_chunks = ceil_div(K, 64);
+        const long tasks = (long)nMB * k_chunks;
+        static bool attr64_set[64] = {false};
+        int dev = 0;
+        ESMM_CUDA_TRY(cudaGetDevice(&dev));
+        const int smem = PACK_WARPS * PACK64_SMEM_PER_WARP;
+        if (dev >= 0 && dev < 64 && !attr64_set[dev]) {
+            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_preprocess_a_pack64_kernel,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+            attr64_set[dev] = true;
+        }
+        long blocks = (tasks + PACK_WARPS - 1) / PACK_WARPS;
+        const long cap = (long)sms * 6 * 8;
+        if (blocks > cap) blocks = cap;
+        esmm_preprocess_a_pack64_kernel<<<(unsigned)blocks, PACK_WARPS * 32, smem, stream>>>(
+            d_A, M, K, nMB, nKB, k_chunks, d_out, d_packed);
+        ESMM_CUDA_TRY(cudaGetLastError());
+        return ESMM_OK;
+    }
+    const int k_chunks = ceil_div(K, 128);
+    const long tasks = (long)nMB * k_chunks;
     static bool attr_set[64] = {false};
     int dev = 0;
     ESMM_CUDA_TRY(cudaGetDevice(&dev));

@@ -293,6 +293,20 @@ def test_gemm_block_structured(cuda, pkg, oracle_mod, monkeypatch, rows):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
+def test_packing_kernel_variants(cuda, pkg, oracle_mod, monkeypatch):
+    """The packing preprocessor has a 32 x 64 task per warp (default) and a 32 x 128 one; both must give the
+    oracle's pattern bytes and a packed copy the GEMM turns into the oracle's C (workspace poisoned with NaN
+    bit patterns: a dead entry that were read would show)."""
+    for variant in ("128", "64"):
+        monkeypatch.setenv("ESMM_PACK", variant)
+        for M, N, K, pa, pb in [(256, 256, 512, 0.5, 0.5), (100, 132, 8 * 37, 0.3, 0.7), (384, 128, 4 * 75, 0.8, 0.4),
+                                (16, 256, 256, 0.5, 0.5), (200, 64, 64, 1.0, 1.0)]:
+            A, B = workloads.tile_random(M, N, K, pa, pb, seed=M + K, gran_a=32, gran_b=32)
+            check_all_paths(cuda, pkg, oracle_mod, A, B)
+        A, B = workloads.all_byte_values(seed=31)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
 def test_gemm_random_shapes(cuda, pkg, oracle_mod):
     """Seeded random shapes and densities (ragged M, N % 4 == 0, K % 4 == 0, all three kernels and both tilings get
     their share through the launch heuristics): same bits as the oracle everywhere."""
