@@ -64,6 +64,11 @@ _SIGNATURES = {
     "esmm_sgemm_joint_static": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "esmm_device_status": (_i, [_vp]),
     "esmm_selftest_bounded_wait": (_i, [C.c_uint, _vp]),
+    "esmm_tf32x3_b_create": (_i, [_vp, _i, _i, _i, C.POINTER(_vp)]),
+    "esmm_tf32x3_b_destroy": (None, [_vp]),
+    "esmm_tf32x3_b_live_k": (_i, [_vp]),
+    "esmm_tf32x3_workspace_bytes": (C.c_size_t, [_i, _i]),
+    "esmm_sgemm_joint_tf32x3": (_i, [_i, _vp, _vp, _vp, _vp, _vp]),
     "esmm_cusparse_spmm": (_i, [_i, _i, _i, _vp, _vp, _vp, _i, C.POINTER(_f), C.POINTER(_f),
                                 C.POINTER(C.c_longlong)]),
     "esmm_plan_create": (_i, [_i, _i, _i, _vp, _i, C.POINTER(_vp)]),
@@ -149,6 +154,42 @@ def preprocess_a_packed(d_A: int, M: int, K: int, d_out: int, d_packed: int, str
 def gemm_ab_packed(M, N, K, d_a_packed, d_B, d_C, d_a_pat, d_b_pat, stream: int = 0) -> None:
     check(lib().esmm_gemm_ab_packed(M, N, K, d_a_packed, d_B, d_C, d_a_pat, d_b_pat, stream),
           "esmm_gemm_ab_packed")
+
+
+class Tf32x3B:
+    """The "B offline" state of the optional 3xTF32 tensor-core path (B patterns, kept k, B transposed and
+    split), owned by the library; `compact` drops k whose row of B is all zero from both operands."""
+
+    def __init__(self, d_B: int, K: int, N: int, compact: bool = True):
+        self.handle = C.c_void_p()
+        self.K, self.N = K, N
+        check(lib().esmm_tf32x3_b_create(d_B, K, N, 1 if compact else 0, C.byref(self.handle)),
+              "esmm_tf32x3_b_create")
+
+    @property
+    def live_k(self) -> int:
+        return int(lib().esmm_tf32x3_b_live_k(self.handle))
+
+    def close(self) -> None:
+        if self.handle:
+            lib().esmm_tf32x3_b_destroy(self.handle)
+            self.handle = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def tf32x3_workspace_bytes(M: int, K: int) -> int:
+    return int(lib().esmm_tf32x3_workspace_bytes(M, K))
+
+
+def sgemm_joint_tf32x3(M: int, d_A: int, b: Tf32x3B, d_C: int, d_workspace: int, stream: int = 0) -> None:
+    """Optional tensor-core variant (3xTF32; within a few 1e-6 of the FP32 path, not bit-identical): split of
+    A + A patterns + product.  d_workspace holds tf32x3_workspace_bytes(M, b.K)."""
+    check(lib().esmm_sgemm_joint_tf32x3(M, d_A, b.handle, d_C, d_workspace, stream), "esmm_sgemm_joint_tf32x3")
 
 
 def device_status(stream: int = 0) -> None:

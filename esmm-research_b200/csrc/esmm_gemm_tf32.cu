@@ -1,0 +1,567 @@
+// Optional tensor-core variant of the joint-sparse SGEMM: 3xTF32 on tcgen05 (sm_100a), accumulators in TMEM.
+//
+// Every FP32 operand is split into two TF32 parts, x = hi + lo (hi = x rounded to TF32, lo = (x - hi) rounded
+// to TF32), and a product is taken as  a_hi b_hi + a_hi b_lo + a_lo b_hi  with FP32 accumulation: three
+// tensor-core MMAs per K step instead of 64 FP32 multiply-adds per thread.  The dropped a_lo b_lo term and the
+// rounding of lo are of relative size 2^-22, far inside the 1e-4 relative tolerance the results are held to;
+// the result is NOT bit-identical to the FP32 FMA kernels, which is why this is a separate entry point.
+//
+// Skipping happens at K-block (8 k) granularity, the K extent of one kind::tf32 MMA: a K block of a 128 x 128
+// tile is fetched and multiplied only if some k in it is live for the tile (OR of the tile's four A pattern
+// bytes AND OR of its four B pattern bytes).  Everything skipped multiplies exact zeros, so the sum is the one
+// the reference's masked FMA chain forms (src/kernels/esmm_ab_optimized_v3.cu:157, 183-203) up to rounding.
+//
+// Layouts: both operands K-major.  A_hi, A_lo: M x K row-major, written per call by the split kernel.
+// Bt_hi, Bt_lo: N x K row-major (B transposed), written once per B ("B offline").  One K block of a tile is a
+// TMA box of 8 floats x 128 rows with the 32-byte swizzle, which is exactly the canonical K-major shared-memory
+// layout of a 128 x 8 TF32 operand, so a live K block costs four boxes and three MMAs wherever it sits in K.
+//
+// One persistent CTA per SM: a mask warp lists the live K blocks of the next tile, a producer warp fetches stages
+// of four K blocks into a three-deep ring (64 KB per stage), one thread issues the MMAs and commits them to the
+// ring's and the accumulator's mbarriers, four epilogue warps drain one of two TMEM accumulators (128 lanes x 128
+// columns each) while the other is being filled.  Every wait is bounded, as in the other kernels.
+#include <algorithm>
+#include <cstring>
+#include <vector>
+
+#include "esmm_gemm_shared.cuh"
+
+namespace esmm {
+
+constexpr int T_GROUP_KB = 4;                // K blocks per fetch group: 32 floats = one 128-byte swizzle row
+constexpr int T_PART_BYTES = 128 * 128;      // one operand part of a group: 128 rows x 32 floats
+constexpr int T_STAGE_BYTES = 4 * T_PART_BYTES;   // A_hi, A_lo, B_hi, B_lo: 65536
+constexpr int T_STAGES = 3;
+constexpr int T_CHUNK = 8;                   // groups (256 k) accumulated in tensor memory before the epilogue adds them up
+constexpr int T_THREADS = 256;               // warps: 0 and 3 producers, 1 MMA, 2 mask, 4-7 epilogue
+constexpr int T_TMEM_COLS = 256;             // two accumulators of 128 columns
+
+struct Tf32Params {
+    int M, N, K, nKB, cap;
+    int a_rows, b_rows, tiles_m, tiles_n, num_tiles;
+    const uint8_t *a_pat;
+    const uint8_t *b_pat;
+    float *C;
+    int *status;
+};
+
+struct Tf32Maps {
+    CUtensorMap a_hi, a_lo, b_hi, b_lo;      // boxes of 32 floats x 128 rows, 128-byte swizzle
+};
+
+// shared-memory matrix descriptor of a K-major TF32 operand inside a 128-byte-swizzled tile of 128 rows x 32
+// floats: rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout
+// type 2.  The K block j of the tile starts 32 j bytes into the row; the swizzle is a function of the address.
+__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr)
+{
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// instruction descriptor: D = F32, A = B = TF32, both K-major, N = 128, M = 128
+constexpr uint32_t UMMA_IDESC_TF32_128x128 = (1u << 4) | (2u << 7) | (2u << 10) | (16u << 17) | (8u << 24);
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate)
+{
+    const uint32_t zero = 0u;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_d),
+        "l"(da), "l"(db), "r"(UMMA_IDESC_TF32_128x128), "r"(accumulate), "r"(zero)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// x = hi + lo with both parts representable in TF32 (low 13 mantissa bits clear)
+__device__ __forceinline__ void split_tf32(float x, float &hi, float &lo)
+{
+    uint32_t h, l;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+    hi = __uint_as_float(h);
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(l) : "f"(x - hi));
+    lo = __uint_as_float(l);
+}
+
+// A (M x K, row-major) -> A_hi, A_lo (M x Kc, row-major).  klist == nullptr: Kc == K, the same columns.
+// Otherwise column j of the output is column klist[j] of A (ascending; -1: a zero column of padding).
+__global__ void esmm_tf32_split_kernel(const float *__restrict__ A, int M, int K, const int *__restrict__ klist,
+                                       int Kc, float *__restrict__ hi, float *__restrict__ lo)
+{
+    const int q = Kc >> 2;                                     // float4 groups per output row
+    const size_t n4 = (size_t)M * q;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 v;
+        if (klist == nullptr) {
+            v = __ldg(reinterpret_cast<const float4 *>(A) + i);
+        } else {
+            const size_t row = i / q;
+            const int4 k = __ldg(reinterpret_cast<const int4 *>(klist) + (i - row * q));
+            const float *a = A + row * K;
+            v.x = k.x >= 0 ? __ldg(a + k.x) : 0.0f;
+            v.y = k.y >= 0 ? __ldg(a + k.y) : 0.0f;
+            v.z = k.z >= 0 ? __ldg(a + k.z) : 0.0f;
+            v.w = k.w >= 0 ? __ldg(a + k.w) : 0.0f;
+        }
+        float4 h, l;
+        split_tf32(v.x, h.x, l.x);
+        split_tf32(v.y, h.y, l.y);
+        split_tf32(v.z, h.z, l.z);
+        split_tf32(v.w, h.w, l.w);
+        reinterpret_cast<float4 *>(hi)[i] = h;
+        reinterpret_cast<float4 *>(lo)[i] = l;
+    }
+}
+
+// B (K x N, row-major) -> Bt_hi, Bt_lo (N x Kc, row-major): 32 x 32 tiles through shared memory; row j of the tile
+// column is row klist[j] of B (or j itself without a list)
+__global__ void esmm_tf32_split_transpose_kernel(const float *__restrict__ B, int K, int N, const int *__restrict__ klist,
+                                                 int Kc, float *__restrict__ bt_hi, float *__restrict__ bt_lo)
+{
+    __shared__ float tile[32][33];
+    const int j0 = blockIdx.y * 32, n0 = blockIdx.x * 32;
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int j = j0 + r, n = n0 + threadIdx.x;
+        const int k = j < Kc ? (klist ? klist[j] : j) : -1;
+        tile[r][threadIdx.x] = (k >= 0 && k < K && n < N) ? B[(size_t)k * N + n] : 0.0f;
+    }
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += blockDim.y) {
+        const int n = n0 + r, j = j0 + threadIdx.x;
+        if (n < N && j < Kc) {
+            float h, l;
+            split_tf32(tile[threadIdx.x][r], h, l);
+            bt_hi[(size_t)n * Kc + j] = h;
+            bt_lo[(size_t)n * Kc + j] = l;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(T_THREADS, 1)
+esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32Params p)
+{
+    extern __shared__ __align__(1024) char smem[];
+    // layout: ring (T_STAGES x 64 KB) | group lists (2 x cap u16) | barriers | misc
+    const int list_stride = ((p.cap * 2 + 15) & ~15) / 2;
+    uint16_t *lists = reinterpret_cast<uint16_t *>(smem + T_STAGES * T_STAGE_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + T_STAGES * T_STAGE_BYTES + 4 * list_stride);
+    // full[3], empty[3], acc_full[2], acc_empty[2], lfull[2], lempty[2]
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 3), accf0 = smem_u32(bars + 6),
+                   acce0 = smem_u32(bars + 8), lfull0 = smem_u32(bars + 10), lempty0 = smem_u32(bars + 12);
+    volatile int *nlive = reinterpret_cast<volatile int *>(bars + 14);   // [2]: live groups of the listed tile
+    volatile int *abort_flag = nlive + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(const_cast<int *>(nlive + 3));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < T_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);        // one tcgen05.commit per stage
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);         // tcgen05.commit after the chunk's last MMA
+            mbar_init(acce0 + 8 * b, 4);         // the four epilogue warps
+            mbar_init(lfull0 + 8 * b, 1);
+            mbar_init(lempty0 + 8 * b, 6);       // producer warp, MMA thread, four epilogue warps
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(T_TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int nGroups = (p.nKB + T_GROUP_KB - 1) / T_GROUP_KB;
+    bool ok = true;
+
+    if (warp == 2) {
+        // ---------------- mask warp: live groups of the tile (index | live K blocks << 12), one tile ahead ----------------
+        int it = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(lempty0 + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            uint16_t *list = lists + buf * list_stride;
+            int pos = 0;
+            for (int g0 = 0; g0 < nGroups; g0 += 32) {
+                const int g = g0 + lane;
+                unsigned live = 0;
+                if (g < nGroups) {
+                    // four pattern bytes per row block: one 32-bit load when the row of bytes allows it
+                    unsigned au[T_GROUP_KB] = {0, 0, 0, 0}, bu[T_GROUP_KB] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const int mb = tm * 4 + i, nb = tn * 4 + i;
+#pragma unroll
+                        for (int j = 0; j < T_GROUP_KB; ++j) {
+                            const int kb = g * T_GROUP_KB + j;
+                            if (kb < p.nKB) {
+                                if (mb < p.a_rows) au[j] |= p.a_pat[(size_t)mb * p.nKB + kb];
+                                if (nb < p.b_rows) bu[j] |= p.b_pat[(size_t)nb * p.nKB + kb];
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < T_GROUP_KB; ++j) live |= ((au[j] & bu[j]) != 0u ? 1u : 0u) << j;
+                }
+                const unsigned m = __ballot_sync(0xFFFFFFFFu, live != 0u);
+                if (live) list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
+                pos += __popc(m);
+            }
+            if (lane == 0) nlive[buf] = pos;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
+        }
+    } else if (warp == 0) {
+        // ---------------- producer: one stage per live group, lanes 0-3 fetch A_hi, A_lo, B_hi, B_lo ----------------
+        if (lane < 4) tma_prefetch_descriptor(&maps.a_hi + lane);
+        int slot = 0, it = 0;
+        uint32_t phase = 0, issued_bits = 0, parity_bits = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const uint16_t *list = lists + buf * list_stride;
+            const int n = nlive[buf];
+            const int row0 = (lane & 2) ? tn * TILE_N : tm * TILE_M;
+            for (int q = 0; q < n; ++q) {
+                ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                const uint32_t full = full0 + 8 * slot;
+                if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)T_STAGE_BYTES);
+                __syncwarp();
+                if (lane < 4) {
+                    const int k = (int)(list[q] & 0xFFFu) * (T_GROUP_KB * BK);
+                    tma_load_2d(smem_u32(smem) + (uint32_t)slot * T_STAGE_BYTES + (uint32_t)lane * T_PART_BYTES,
+                                &maps.a_hi + lane, k, row0, full);
+                }
+                issued_bits |= 1u << slot;
+                parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
+                if (++slot == T_STAGES) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+        }
+        if (!ok && lane == 0) {
+            // leave only after the copies already issued have landed (bounded)
+            for (int s = 0; s < T_STAGES; ++s) {
+                if (!(issued_bits & (1u << s))) continue;
+                const uint32_t par = (parity_bits >> s) & 1u;
+                for (int tries = 0; tries < (1 << 16); ++tries)
+                    if (mbar_try_wait(full0 + 8 * s, par)) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue: one thread; a chunk of T_CHUNK groups per accumulator ----------------
+        if (lane == 0) {
+            int slot = 0, it = 0;
+            uint32_t phase = 0, chunk = 0;
+            for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+                const int buf = it & 1;
+                ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+                if (!ok) break;
+                const uint16_t *list = lists + buf * list_stride;
+                const int n = nlive[buf];
+                for (int c0 = 0; c0 < n && ok; c0 += T_CHUNK, ++chunk) {
+                    // this chunk's accumulator: free once the epilogue has drained the chunk two before it
+                    const uint32_t ab = chunk & 1u;
+                    ok = mbar_wait(acce0 + 8 * ab, ((chunk >> 1) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d = tmem + ab * 128u;
+                    uint32_t accumulate = 0;
+                    const int c1 = min(n, c0 + T_CHUNK);
+                    for (int q = c0; q < c1; ++q) {
+                        ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t s0 = smem_u32(smem) + (uint32_t)slot * T_STAGE_BYTES;
+                        unsigned live = (unsigned)list[q] >> 12;
+                        while (live) {
+                            const uint32_t off = (uint32_t)(__ffs(live) - 1) * 32u;
+                            live &= live - 1;
+                            const uint64_t ah = umma_desc_k128(s0 + off);
+                            const uint64_t al = umma_desc_k128(s0 + T_PART_BYTES + off);
+                            const uint64_t bh = umma_desc_k128(s0 + 2 * T_PART_BYTES + off);
+                            const uint64_t bl = umma_desc_k128(s0 + 3 * T_PART_BYTES + off);
+                            umma_tf32(d, al, bh, accumulate);   // small terms first
+                            umma_tf32(d, ah, bl, 1u);
+                            umma_tf32(d, ah, bh, 1u);
+                            accumulate = 1u;
+                        }
+                        umma_commit(empty0 + 8 * slot);          // the slot is free when these MMAs have read it
+                        if (++slot == T_STAGES) {
+                            slot = 0;
+                            phase ^= 1;
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit(accf0 + 8 * ab);                 // the chunk is complete when all its MMAs are
+                }
+                if (!ok) break;
+                mbar_arrive(lempty0 + 8 * buf);
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue: warp w owns TMEM lanes 32 (w - 4) .., one C row per thread; chunk sums are added
+        // in registers with round-to-nearest, which keeps the tensor core's own accumulation runs short ----------------
+        const int q = warp - 4;
+        int it = 0;
+        uint32_t chunk = 0;
+        for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+            const int buf = it & 1;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            if (!ok) break;
+            const int n = nlive[buf];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+            float acc[TILE_N];
+#pragma unroll
+            for (int j = 0; j < TILE_N; ++j) acc[j] = 0.0f;
+            for (int c0 = 0; c0 < n && ok; c0 += T_CHUNK, ++chunk) {
+                const uint32_t ab = chunk & 1u;
+                ok = mbar_wait(accf0 + 8 * ab, (chunk >> 1) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < TILE_N; cc += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32(tmem + ((uint32_t)(q * 32) << 16) + ab * 128u + (uint32_t)cc, r);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[cc + j] += __uint_as_float(r[j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acce0 + 8 * ab);
+            }
+            if (!ok) break;
+            const int row = tm * TILE_M + q * 32 + lane;
+            if (row < p.M) {
+                float *dst = p.C + (size_t)row * p.N + tn * TILE_N;
+#pragma unroll
+                for (int j = 0; j < TILE_N; j += 4)
+                    if (tn * TILE_N + j < p.N)
+                        *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            }
+        }
+    }
+
+    if (!ok && lane == 0) atomicExch(p.status, (int)ESMM_ERR_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(T_TMEM_COLS));
+}
+
+}  // namespace esmm
+
+// "B offline" state of the 3xTF32 path (opaque to callers)
+struct esmm_tf32x3_b {
+    int K, N, Kc;            // Kc: columns kept (a multiple of 8; == K without compaction)
+    int device;
+    int *d_klist;            // Kc entries, or nullptr when every k is kept
+    float *d_bt;             // Bt_hi (N x Kc) then Bt_lo (N x Kc)
+    uint8_t *d_b_pat;        // patterns of the kept rows of B: ceil(N / 32) x Kc / 8
+};
+
+extern "C" {
+
+void esmm_tf32x3_b_destroy(esmm_tf32x3_b *b)
+{
+    if (!b) return;
+    cudaFree(b->d_klist);
+    cudaFree(b->d_bt);
+    cudaFree(b->d_b_pat);
+    delete b;
+}
+
+int esmm_tf32x3_b_create(const float *d_B, int K, int N, int compact, esmm_tf32x3_b **out)
+{
+    using namespace esmm;
+    if (!d_B || !out) return ESMM_ERR_NULL;
+    *out = nullptr;
+    if (K <= 0 || N <= 0 || (K & 7) || (N & 3)) return ESMM_ERR_SHAPE;
+    if (((uintptr_t)d_B) & 15) return ESMM_ERR_ALIGN;
+    const int nKB = K / BK, nNB = ceil_div(N, PAT_N);
+    esmm_tf32x3_b *b = new esmm_tf32x3_b();
+    b->K = K;
+    b->N = N;
+    b->Kc = K;
+    int st = ESMM_OK;
+    auto fail = [&](int code) {
+        esmm_tf32x3_b_destroy(b);
+        return code;
+    };
+    if (cudaGetDevice(&b->device) != cudaSuccess) return fail(record_cuda_error_text("cudaGetDevice failed"));
+
+    // patterns of the whole of B, on the host too: they say which rows of B hold anything at all
+    std::vector<uint8_t> pat((size_t)nNB * nKB);
+    uint8_t *d_pat = nullptr;
+    if (cudaMalloc(&d_pat, pat.size()) != cudaSuccess) return fail(record_cuda_error_text("cudaMalloc failed (B patterns)"));
+    st = esmm_preprocess_b(d_B, K, N, d_pat, nullptr);
+    if (st == ESMM_OK && cudaMemcpy(pat.data(), d_pat, pat.size(), cudaMemcpyDeviceToHost) != cudaSuccess)
+        st = record_cuda_error_text("cudaMemcpy failed (B patterns)");
+    if (st != ESMM_OK) {
+        cudaFree(d_pat);
+        return fail(st);
+    }
+
+    std::vector<int> klist;
+    if (compact) {
+        std::vector<uint8_t> any(nKB, 0);
+        for (int nb = 0; nb < nNB; ++nb)
+            for (int kb = 0; kb < nKB; ++kb) any[kb] |= pat[(size_t)nb * nKB + kb];
+        for (int k = 0; k < K; ++k)
+            if ((any[k >> 3] >> (k & 7)) & 1) klist.push_back(k);
+        if (klist.empty()) klist.push_back(-1);              // B is all zero: one group of zero columns
+        while (klist.size() % (T_GROUP_KB * BK)) klist.push_back(-1);   // whole fetch groups
+        if ((int)klist.size() >= K)
+            klist.clear();                                   // nothing to gain: keep the direct path
+        else
+            b->Kc = (int)klist.size();
+    }
+    const int Kc = b->Kc, nKBc = Kc / BK;
+    if (!klist.empty()) {
+        // patterns of the kept rows: bit i of block jb comes from row klist[8 jb + i]
+        std::vector<uint8_t> pc((size_t)nNB * nKBc, 0);
+        for (int nb = 0; nb < nNB; ++nb)
+            for (int j = 0; j < Kc; ++j) {
+                const int k = klist[j];
+                if (k >= 0 && ((pat[(size_t)nb * nKB + (k >> 3)] >> (k & 7)) & 1)) pc[(size_t)nb * nKBc + (j >> 3)] |= 1u << (j & 7);
+            }
+        cudaFree(d_pat);
+        d_pat = nullptr;
+        if (cudaMalloc(&b->d_b_pat, pc.size()) != cudaSuccess ||
+            cudaMemcpy(b->d_b_pat, pc.data(), pc.size(), cudaMemcpyHostToDevice) != cudaSuccess ||
+            cudaMalloc(&b->d_klist, (size_t)Kc * sizeof(int)) != cudaSuccess ||
+            cudaMemcpy(b->d_klist, klist.data(), (size_t)Kc * sizeof(int), cudaMemcpyHostToDevice) != cudaSuccess)
+            return fail(record_cuda_error_text("cudaMalloc / cudaMemcpy failed (compacted B patterns)"));
+    } else {
+        b->d_b_pat = d_pat;
+    }
+
+    if (cudaMalloc(&b->d_bt, (size_t)2 * N * Kc * sizeof(float)) != cudaSuccess)
+        return fail(record_cuda_error_text("cudaMalloc failed (split B)"));
+    dim3 grid((unsigned)ceil_div(N, 32), (unsigned)ceil_div(Kc, 32)), block(32, 8);
+    esmm_tf32_split_transpose_kernel<<<grid, block>>>(d_B, K, N, b->d_klist, Kc, b->d_bt, b->d_bt + (size_t)N * Kc);
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaDeviceSynchronize();
+    if (e != cudaSuccess) return fail(record_cuda_error_text(cudaGetErrorString(e)));
+    *out = b;
+    return ESMM_OK;
+}
+
+int esmm_tf32x3_b_live_k(const esmm_tf32x3_b *b) { return b ? b->Kc : 0; }
+
+size_t esmm_tf32x3_workspace_bytes(int M, int K)
+{
+    if (M <= 0 || K <= 0) return 0;
+    const size_t pat = (esmm_a_pattern_bytes(M, K, 32) + 255) & ~(size_t)255;
+    return pat + (size_t)2 * M * K * sizeof(float);
+}
+
+int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, float *d_C, void *d_workspace,
+                            void *stream_)
+{
+    using namespace esmm;
+    cudaStream_t stream = (cudaStream_t)stream_;
+    if (!d_A || !b || !d_C || !d_workspace) return ESMM_ERR_NULL;
+    const int N = b->N, K = b->K, Kc = b->Kc;
+    if (M <= 0) return ESMM_ERR_SHAPE;
+    if (((uintptr_t)d_A | (uintptr_t)d_C) & 15) return ESMM_ERR_ALIGN;
+    if (((uintptr_t)d_workspace) & 255) return ESMM_ERR_ALIGN;
+    const int nKB = Kc / BK;
+    if (ceil_div(nKB, T_GROUP_KB) > 4095) return ESMM_ERR_TOO_LARGE;   // 12-bit group index in the list entries
+
+    // workspace (sized for the uncompacted K): A patterns | A_hi | A_lo, all of the kept columns only
+    uint8_t *a_pat = static_cast<uint8_t *>(d_workspace);
+    float *a_hi = reinterpret_cast<float *>(a_pat + ((esmm_a_pattern_bytes(M, K, 32) + 255) & ~(size_t)255));
+    float *a_lo = a_hi + (size_t)M * Kc;
+    {
+        const size_t n4 = (size_t)M * (Kc / 4);
+        const int blocks = (int)std::max<size_t>(1, std::min<size_t>((n4 + 255) / 256, 148 * 16));
+        esmm_tf32_split_kernel<<<blocks, 256, 0, stream>>>(d_A, M, K, b->d_klist, Kc, a_hi, a_lo);
+        ESMM_CUDA_TRY(cudaGetLastError());
+    }
+    // a value whose TF32 parts are both zero contributes nothing, so the patterns are those of the hi part
+    int st = esmm_preprocess_a(a_hi, M, Kc, 32, a_pat, stream);
+    if (st != ESMM_OK) return st;
+
+    Tf32Params p;
+    memset(&p, 0, sizeof p);
+    p.M = M;
+    p.N = N;
+    p.K = Kc;
+    p.nKB = nKB;
+    p.cap = ceil_div(nKB, T_GROUP_KB) + 32;
+    p.a_rows = ceil_div(M, 32);
+    p.b_rows = ceil_div(N, PAT_N);
+    p.tiles_m = ceil_div(M, TILE_M);
+    p.tiles_n = ceil_div(N, TILE_N);
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.a_pat = a_pat;
+    p.b_pat = b->d_b_pat;
+    p.C = d_C;
+    p.status = device_status_ptr();
+    if (!p.status) return ESMM_ERR_CUDA;
+
+    Tf32Maps maps;
+    const float *bt_hi = b->d_bt, *bt_lo = b->d_bt + (size_t)N * Kc;
+    const CUtensorMapL2promotion l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+    const uint32_t box_k = T_GROUP_KB * BK;
+    st = make_map_2d(&maps.a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, l2);
+    if (!st) st = make_map_2d(&maps.a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, l2);
+    if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, CU_TENSOR_MAP_SWIZZLE_128B, l2);
+    if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, CU_TENSOR_MAP_SWIZZLE_128B, l2);
+    if (st) return st;
+
+    const size_t smem = (size_t)T_STAGES * T_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 14 * 8 + 16;
+    if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
+    int dev = 0, sms = 0;
+    ESMM_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev != b->device) return record_cuda_error_text("esmm_sgemm_joint_tf32x3: B was prepared on another device");
+    ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)smem));
+    const int grid = std::min(sms, p.num_tiles);
+    esmm_joint_sgemm_tf32x3_kernel<<<grid, T_THREADS, smem, stream>>>(maps, p);
+    ESMM_CUDA_TRY(cudaGetLastError());
+    return ESMM_OK;
+}
+
+}  // extern "C"

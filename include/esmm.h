@@ -227,6 +227,30 @@ int esmm_cublas_sgemm(int M, int N, int K, const float *d_A, const float *d_B, f
  * chains on every SM, timed with CUDA events); *sm_count gets the SM count. */
 int esmm_ffma_peak_tflops(double *tflops, int *sm_count);
 
+/* Optional tensor-core variant: the joint-sparse product as 3xTF32 on the 5th-generation tensor cores
+ * (tcgen05.mma kind::tf32, accumulators in tensor memory).  No counterpart in the reference, whose kernels
+ * are FP32 FMA only.  Every operand is split as x = hi + lo (both TF32) and a product is formed as
+ * a_hi b_hi + a_hi b_lo + a_lo b_hi; the tensor core accumulates runs of 256 k in FP32, the runs are added in
+ * registers.  C agrees with esmm_gemm_ab to a few 1e-6 of max |C| (inside the 1e-4 bound the FP32 path is
+ * held to) but is NOT bit-identical to it.  Requires K % 8 == 0, N % 4 == 0, finite inputs.
+ * Work is skipped at two levels: k with an all-zero row of B are dropped from both operands when B is prepared
+ * (compact != 0), and of what is left a 128 x 128 tile multiplies only the 8-wide K blocks in which its A and
+ * B patterns share a live k.
+ *
+ * esmm_tf32x3_b_create: the "B offline" step (beside esmm_preprocess_b): B patterns, the list of kept k, B
+ *   transposed and split.  Allocates device memory, synchronises; the handle belongs to the current device.
+ * esmm_tf32x3_b_live_k: k kept (K without compaction; else a multiple of 32, padding included).
+ * esmm_sgemm_joint_tf32x3: split (and gather) of A + A patterns + product, three launches on `stream`, no
+ *   allocation.  d_A: M x K row-major; d_C: M x N; d_workspace: esmm_tf32x3_workspace_bytes(M, K) bytes,
+ *   256-byte aligned. */
+typedef struct esmm_tf32x3_b esmm_tf32x3_b;
+int esmm_tf32x3_b_create(const float *d_B, int K, int N, int compact, esmm_tf32x3_b **out);
+void esmm_tf32x3_b_destroy(esmm_tf32x3_b *b);
+int esmm_tf32x3_b_live_k(const esmm_tf32x3_b *b);
+size_t esmm_tf32x3_workspace_bytes(int M, int K);
+int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, float *d_C, void *d_workspace,
+                            void *stream);
+
 /* cuSPARSE SpMM baseline (src/benchmarks/cusparse_benchmark.cu:56-247): A (M x K, row-major, dense
  * storage) is converted to CSR and multiplied with dense B into C.  *spmm_ms: average of `runs` SpMM
  * calls with A already in CSR; *total_ms: average of `runs` (conversion + SpMM) calls; *nnz: stored
