@@ -278,6 +278,18 @@ def run_ours(args) -> None:
                                                        c["bp"].data_ptr(), ws.data_ptr()), reps)
         cub_ms, _ = time_each(lambda: pkg.cublas_sgemm(M, Nl, K, c["A"].data_ptr(), c["B"].data_ptr(),
                                                        Cd.data_ptr()), reps)
+        # optional tensor-core variant (3xTF32, inside the 1e-4 tolerance but not bit-identical): reported beside
+        # the FP32 path, never part of `value`
+        tb = pkg.Tf32x3B(c["B"].data_ptr(), K, Nl, True)
+        ws_t = torch.empty(pkg.tf32x3_workspace_bytes(M, K), dtype=torch.uint8, device=dev)
+        Ct = torch.empty((M, Nl), device=dev)
+        tf_ms, _ = time_each(lambda: pkg.sgemm_joint_tf32x3(M, c["A"].data_ptr(), tb, Ct.data_ptr(), ws_t.data_ptr()),
+                             reps)
+        pkg.sgemm_joint(M, Nl, K, c["A"].data_ptr(), c["B"].data_ptr(), Cd.data_ptr(), c["bp"].data_ptr(), ws.data_ptr())
+        tf_err = float(((Ct - Cd).abs().max() / Cd.abs().max().clamp_min(1e-30)).item())
+        tf_live_k = tb.live_k
+        tb.close()
+        del ws_t, Ct
         density = bin(c["pat"]).count("1") / 8.0
         exec_flops = flops_dense_local * density           # uniform pattern: joint density = pattern density
         pre_bytes = 4.0 * M * K + ap_bytes + 4.0 * M * K * density   # read A, write patterns, write live packed rows
@@ -293,6 +305,10 @@ def run_ours(args) -> None:
             "frac_of_nominal_fp32_peak": exec_flops / (gemm_ms * 1e-3) / 1e12 / NOMINAL_FP32_TFLOPS,
             "preprocess_gbs": pre_bytes / (pre_ms * 1e-3) / 1e9,
             "preprocess_frac_of_hbm": pre_bytes / (pre_ms * 1e-3) / 1e9 / hbm_peak,
+            "tf32x3": {"ms_total": tf_ms, "speedup_vs_cublas_incl_pre": cub_ms / tf_ms,
+                       "speedup_vs_fp32_path": both_ms / tf_ms, "live_k": tf_live_k,
+                       "rel_inf_vs_fp32_path": tf_err,
+                       "dense_equiv_tflops_incl_pre": flops_dense_local / (tf_ms * 1e-3) / 1e12},
         }
         gemm_ms_sum += gemm_ms
         pre_ms_sum += pre_ms

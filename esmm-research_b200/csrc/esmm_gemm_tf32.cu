@@ -6,20 +6,36 @@
 // rounding of lo are of relative size 2^-22, far inside the 1e-4 relative tolerance the results are held to;
 // the result is NOT bit-identical to the FP32 FMA kernels, which is why this is a separate entry point.
 //
-// Skipping happens at K-block (8 k) granularity, the K extent of one kind::tf32 MMA: a K block of a 128 x 128
-// tile is fetched and multiplied only if some k in it is live for the tile (OR of the tile's four A pattern
-// bytes AND OR of its four B pattern bytes).  Everything skipped multiplies exact zeros, so the sum is the one
-// the reference's masked FMA chain forms (src/kernels/esmm_ab_optimized_v3.cu:157, 183-203) up to rounding.
+// Skipping happens at two levels.  (1) When B is prepared, every k whose row of B is all zero is dropped from both
+// operands (the split of A gathers the kept columns), so patterns that repeat in every K block, the reference's
+// benchmark patterns, shrink K itself.  (2) Of what is left, a K block (8 k, the K extent of one kind::tf32 MMA)
+// of a 128 x 128 tile is multiplied only if some k in it is live for the tile (OR of the tile's four A pattern
+// bytes AND OR of its four B pattern bytes), and a group of four K blocks is fetched only if one of them is.
+// Everything skipped multiplies exact zeros, so the sum is the one the reference's masked FMA chain forms
+// (src/kernels/esmm_ab_optimized_v3.cu:157, 183-203) up to rounding.
 //
-// Layouts: both operands K-major.  A_hi, A_lo: M x K row-major, written per call by the split kernel.
-// Bt_hi, Bt_lo: N x K row-major (B transposed), written once per B ("B offline").  One K block of a tile is a
-// TMA box of 8 floats x 128 rows with the 32-byte swizzle, which is exactly the canonical K-major shared-memory
-// layout of a 128 x 8 TF32 operand, so a live K block costs four boxes and three MMAs wherever it sits in K.
+// Rounding: the tensor core's own FP32 accumulation loses accuracy linearly in the number of MMAs (3e-5 of
+// max |C| at K = 4096 when a whole tile is accumulated in one run), so a run is limited to T_CHUNK groups
+// (256 k) and the epilogue warps add the runs in registers with round-to-nearest: 2e-6 at K = 4096 and 16384.
 //
-// One persistent CTA per SM: a mask warp lists the live K blocks of the next tile, a producer warp fetches stages
-// of four K blocks into a three-deep ring (64 KB per stage), one thread issues the MMAs and commits them to the
-// ring's and the accumulator's mbarriers, four epilogue warps drain one of two TMEM accumulators (128 lanes x 128
-// columns each) while the other is being filled.  Every wait is bounded, as in the other kernels.
+// Layouts: both operands K-major.  A_hi, A_lo: M x Kc row-major, written per call by the split kernel.
+// Bt_hi, Bt_lo: N x Kc row-major (B transposed), written once per B ("B offline").  A group of four K blocks of
+// one operand part is one TMA box of 32 floats x 128 rows with the 128-byte swizzle (16 KB), the canonical
+// K-major shared-memory layout; the MMA of K block j of the group reads it through a descriptor that starts
+// 32 j bytes into the swizzled row.  (Boxes of one K block with the 32-byte swizzle were measured first: 1.6 x
+// slower, the copy engine handles about one box row per cycle whatever its width.)
+//
+// One persistent CTA per SM, 8 warps: a mask warp lists the live groups of the next tile, a producer warp fetches
+// one group per stage into a three-deep ring (64 KB per stage), one thread issues the MMAs and commits them to
+// the ring's and the accumulator's mbarriers, four epilogue warps drain one of two TMEM accumulators (128 lanes x
+// 128 columns each) while the other is being filled.  Every wait is bounded, as in the other kernels, and the
+// tensor memory is freed on every path out.
+//
+// Measured on one B200 at 4096^3 (whole call: split + A patterns + product): 0.67 ms dense against 2.36 ms for
+// the FP32 kernel; the tensor pipe is busy 58 % of the time and the rest is operand delivery (16 KB per K block
+// per SM, about 64 B per clock per SM: one MMA instead of three per K block is only 24 % faster, pulling groups
+// into L2 ahead of the ring changes nothing).  Halving the bytes per MMA needs a CTA pair sharing B halves
+// (cta_group::2), which is not built.
 #include <algorithm>
 #include <cstring>
 #include <vector>
@@ -33,7 +49,7 @@ constexpr int T_PART_BYTES = 128 * 128;      // one operand part of a group: 128
 constexpr int T_STAGE_BYTES = 4 * T_PART_BYTES;   // A_hi, A_lo, B_hi, B_lo: 65536
 constexpr int T_STAGES = 3;
 constexpr int T_CHUNK = 8;                   // groups (256 k) accumulated in tensor memory before the epilogue adds them up
-constexpr int T_THREADS = 256;               // warps: 0 and 3 producers, 1 MMA, 2 mask, 4-7 epilogue
+constexpr int T_THREADS = 256;               // warps: 0 producer, 1 MMA, 2 mask, 3 idle, 4-7 epilogue
 constexpr int T_TMEM_COLS = 256;             // two accumulators of 128 columns
 
 struct Tf32Params {
