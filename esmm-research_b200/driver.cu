@@ -44,6 +44,7 @@ const char *kUsageKernels[][2] = {
     {"28", "A+B GMem-32 (K25 with 32-row, global mem patterns)"},
     {"29", "A+B Optimized V3 (K26 + templated smem + float2 A-loads)"},
     {"30", "A+B Compressed-K (K29 + compressed K-list + set-bit dotIdx)"},
+    {"129", "A+B 3xTF32 on tensor cores (additive: not in the reference, not part of 'all')"},
 };
 
 void print_usage(const char *prog)
@@ -51,7 +52,7 @@ void print_usage(const char *prog)
     using std::cout;
     using std::endl;
     cout << "Usage: " << prog << " [kernel_choice] [runs] [options]" << endl;
-    cout << "\nAvailable kernels: 14, 15, 16, 17, 20, 21, 25, 26, 27, 28, 29, 30" << endl;
+    cout << "\nAvailable kernels: 14, 15, 16, 17, 20, 21, 25, 26, 27, 28, 29, 30 (and 129)" << endl;
     for (auto &k : kUsageKernels) cout << "  " << k[0] << ": " << k[1] << endl;
     cout << "\nKernel selection formats:" << endl;
     cout << "  Single:   29          (run K29)" << endl;
@@ -289,7 +290,7 @@ int main(int argc, char **argv)
     for (int k : o.kernels)
         if (!esmm_kernel_id_valid(k)) {
             cout << "Error: Kernel " << k
-                 << " is not a valid kernel. Valid kernels are: 14, 15, 16, 17, 20, 21, 25, 26, 27, 28, 29, 30." << endl;
+                 << " is not a valid kernel. Valid kernels are: 14, 15, 16, 17, 20, 21, 25, 26, 27, 28, 29, 30, 129." << endl;
             cout << "Run '" << argv[0] << " --help' to see available kernels." << endl;
             return 1;
         }

@@ -89,6 +89,9 @@ def test_kernel_selection_and_names_match_reference(pkg):
         assert L.esmm_kernel_name(int(i)).decode() == str(name)
     valid = [i for i in range(40) if L.esmm_kernel_id_valid(i)]
     assert valid == [14, 15, 16, 17, 20, 21, 25, 26, 27, 28, 29, 30]
+    # additive id outside the reference's 1-100 range: the optional tensor-core variant; 'all' does not select it
+    assert L.esmm_kernel_id_valid(129) and b"3xTF32" in L.esmm_kernel_name(129)
+    assert pkg.parse_kernel_selection("129") == [129] and 129 not in pkg.parse_kernel_selection("all")
 
 
 def test_skip_stats_match_oracle(pkg, oracle_mod):

@@ -165,3 +165,32 @@ def test_argument_checks(cuda, pkg):
     assert L.esmm_sgemm_joint_tf32x3(32, A.data_ptr(), b.handle, c.data_ptr(), ws.data_ptr() + 16, None) == 3
     L.esmm_tf32x3_b_destroy(None)                                              # a no-op
     b.close()
+
+
+def test_runner_id_129_and_cli(cuda, pkg, oracle_mod, capfd):
+    """The reference's timed runner loop (verification against the cuBLAS result included) with the tensor-core
+    variant as additive kernel id 129, through the C ABI and through the exec_b200 command line."""
+    import ctypes as C
+    import subprocess
+    M = N = K = 512
+    A, B = workloads.tile_random(M, N, K, 0.5, 0.5, seed=31, gran_a=64, gran_b=32)
+    dA, dB = cuda.from_numpy(A).cuda(), cuda.from_numpy(B).cuda()
+    dC = cuda.zeros((M, N), device="cuda")
+    h_ref, h_c = np.zeros((M, N), np.float32), np.zeros((M, N), np.float32)
+    L = pkg.lib()
+    passed, avg = C.c_int(0), C.c_float(0)
+    assert L.esmm_run_kernel(15, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), h_ref.ctypes.data, None, 1, 0,
+                             0, C.byref(passed), C.byref(avg)) == 0
+    st = L.esmm_run_kernel(129, M, N, K, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), h_c.ctypes.data,
+                           h_ref.ctypes.data, 3, 1, 1, C.byref(passed), C.byref(avg))
+    assert st == 0 and passed.value == 1 and avg.value > 0
+    assert rel_inf(h_c, oracle_mod.gemm_joint(A, B)) <= TIGHT
+    out = capfd.readouterr().out
+    assert "=== Skip Stats: K129 ===" in out
+    # K not a multiple of 8 is outside what the tensor-core path takes: a status, no launch
+    st = L.esmm_run_kernel(129, 64, 64, 60, dA.data_ptr(), dB.data_ptr(), dC.data_ptr(), h_c.ctypes.data,
+                           h_ref.ctypes.data, 1, 0, 0, C.byref(passed), C.byref(avg))
+    assert st == 2
+    p = subprocess.run([pkg.EXE_PATH, "129", "2", "--size", "512", "--pattern", "11110000"], capture_output=True,
+                       text=True, timeout=600)
+    assert p.returncode == 0 and "PASSED" in p.stdout.upper(), p.stdout + p.stderr
