@@ -65,25 +65,91 @@ struct Tf32Maps {
     CUtensorMap a_hi, a_lo, b_hi, b_lo;      // boxes of 32 floats x 128 rows, 128-byte swizzle
 };
 
-// shared-memory matrix descriptor of a K-major TF32 operand inside a 128-byte-swizzled tile of 128 rows x 32
-// floats: rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), descriptor version 1, layout
-// type 2.  The K block j of the tile starts 32 j bytes into the row; the swizzle is a function of the address.
-__device__ __forceinline__ uint64_t umma_desc_k128(uint32_t saddr)
+// Shared-memory matrix descriptor of a K-major TF32 operand inside a 128-byte-swizzled tile of rows x 32 floats:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset 64 at bit 32), descriptor version 1
+// (bit 46), layout type 2 (bits 61-63), leading byte offset 1 (bit 16), start address >> 4 in the low 14 bits.
+// K block j of the tile starts 32 j bytes into the row; the swizzle is a function of the address.
+// The descriptor as two words: only the low one (start address, leading byte offset) changes from MMA to MMA; the
+// K block j of a tile adds 2 j to it (32 j bytes >> 4).  The issuing thread's own instructions are on the critical
+// path (one MMA of K = 8 keeps the tensor pipe busy for only about 65 cycles), so the 64-bit descriptor is put
+// together inside the asm block from one precomputed word and a constant.
+constexpr uint32_t UMMA_DESC_HI_K128 = 64u | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+
+// instruction descriptors: D = F32, A = B = TF32, both K-major; N = 128; M = 128 (one CTA) or 256 (CTA pair)
+constexpr uint32_t UMMA_IDESC_TF32_128x128 = (1u << 4) | (2u << 7) | (2u << 10) | (16u << 17) | (8u << 24);
+constexpr uint32_t UMMA_IDESC_TF32_256x128 = (1u << 4) | (2u << 7) | (2u << 10) | (16u << 17) | (16u << 24);
+
+template <bool PAIR>
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate)
 {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+    if constexpr (PAIR) {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %3, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t}\n" ::"r"(tmem_d),
+            "r"(a_lo), "r"(b_lo), "r"(UMMA_IDESC_TF32_256x128), "r"(accumulate), "r"(UMMA_DESC_HI_K128), "r"(0u)
+            : "memory");
+    } else {
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+            "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\tsetp.ne.b32 p, %4, 0;\n\t"
+            "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}\n" ::"r"(tmem_d),
+            "r"(a_lo), "r"(b_lo), "r"(UMMA_IDESC_TF32_128x128), "r"(accumulate), "r"(UMMA_DESC_HI_K128), "r"(0u)
+            : "memory");
+    }
 }
 
-// instruction descriptor: D = F32, A = B = TF32, both K-major, N = 128, M = 128
-constexpr uint32_t UMMA_IDESC_TF32_128x128 = (1u << 4) | (2u << 7) | (2u << 10) | (16u << 17) | (8u << 24);
-
-__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate)
+// the three products of K block j of a group: small terms first
+template <bool PAIR>
+__device__ __forceinline__ void umma_kblock(uint32_t d, uint32_t ah, uint32_t al, uint32_t bh, uint32_t bl, uint32_t j,
+                                            uint32_t accumulate)
 {
-    const uint32_t zero = 0u;
+    umma_tf32<PAIR>(d, al + 2u * j, bh + 2u * j, accumulate);
+    umma_tf32<PAIR>(d, ah + 2u * j, bl + 2u * j, 1u);
+    umma_tf32<PAIR>(d, ah + 2u * j, bh + 2u * j, 1u);
+}
+
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t done;
     asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}\n" ::"r"(tmem_d),
-        "l"(da), "l"(db), "r"(UMMA_IDESC_TF32_128x128), "r"(accumulate), "r"(zero)
+        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(done)
+        : "r"(bar), "r"(parity)
         : "memory");
+    return done != 0;
+}
+
+// All live K blocks of a group (live: 4-bit mask, not 0); the dense case is unrolled with constant offsets.
+// A wait on a data barrier costs the issuing thread about 170 cycles even when the data is there, more than
+// two MMAs take, and the tensor pipe runs dry meanwhile.  So the next group's barrier is polled (one
+// non-blocking test) right after this group's first K block is issued, while the pipe has work queued; the
+// caller skips its wait when the poll said "landed".
+template <bool PAIR>
+__device__ __forceinline__ bool umma_group(uint32_t d, uint32_t ah, uint32_t al, uint32_t bh, uint32_t bl, unsigned live,
+                                           uint32_t &accumulate, uint32_t next_bar, uint32_t next_parity)
+{
+    bool next_ready;
+    if (live == 0xFu) {
+        umma_kblock<PAIR>(d, ah, al, bh, bl, 0u, accumulate);
+        next_ready = mbar_test_wait(next_bar, next_parity);
+        umma_kblock<PAIR>(d, ah, al, bh, bl, 1u, 1u);
+        umma_kblock<PAIR>(d, ah, al, bh, bl, 2u, 1u);
+        umma_kblock<PAIR>(d, ah, al, bh, bl, 3u, 1u);
+    } else {
+        uint32_t j = (uint32_t)(__ffs(live) - 1);
+        live &= live - 1;
+        umma_kblock<PAIR>(d, ah, al, bh, bl, j, accumulate);
+        next_ready = mbar_test_wait(next_bar, next_parity);
+        while (live) {
+            j = (uint32_t)(__ffs(live) - 1);
+            live &= live - 1;
+            umma_kblock<PAIR>(d, ah, al, bh, bl, j, 1u);
+        }
+    }
+    accumulate = 1u;
+    return next_ready;
 }
 
 __device__ __forceinline__ void umma_commit(uint32_t bar)
@@ -306,6 +372,8 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
         if (lane == 0) {
             int slot = 0, it = 0;
             uint32_t phase = 0, chunk = 0;
+            bool landed = false;                         // the next group's copies were seen complete by a poll
+            const uint32_t ring_lo = umma_desc_lo(smem_u32(smem));
             for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
                 const int buf = it & 1;
                 ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
@@ -322,23 +390,13 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
                     uint32_t accumulate = 0;
                     const int c1 = min(n, c0 + T_CHUNK);
                     for (int q = c0; q < c1; ++q) {
-                        ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
+                        if (!landed) ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
                         if (!ok) break;
-                        tc_fence_after();
-                        const uint32_t s0 = smem_u32(smem) + (uint32_t)slot * T_STAGE_BYTES;
-                        unsigned live = (unsigned)list[q] >> 12;
-                        while (live) {
-                            const uint32_t off = (uint32_t)(__ffs(live) - 1) * 32u;
-                            live &= live - 1;
-                            const uint64_t ah = umma_desc_k128(s0 + off);
-                            const uint64_t al = umma_desc_k128(s0 + T_PART_BYTES + off);
-                            const uint64_t bh = umma_desc_k128(s0 + 2 * T_PART_BYTES + off);
-                            const uint64_t bl = umma_desc_k128(s0 + 3 * T_PART_BYTES + off);
-                            umma_tf32(d, al, bh, accumulate);   // small terms first
-                            umma_tf32(d, ah, bl, 1u);
-                            umma_tf32(d, ah, bh, 1u);
-                            accumulate = 1u;
-                        }
+                        const uint32_t ah = ring_lo + (uint32_t)slot * (T_STAGE_BYTES >> 4);
+                        const int nslot = slot + 1 == T_STAGES ? 0 : slot + 1;
+                        landed = umma_group<false>(d, ah, ah + (T_PART_BYTES >> 4), ah + 2 * (T_PART_BYTES >> 4),
+                                                   ah + 3 * (T_PART_BYTES >> 4), (unsigned)list[q] >> 12, accumulate,
+                                                   full0 + 8 * nslot, nslot ? phase : phase ^ 1u);
                         umma_commit(empty0 + 8 * slot);          // the slot is free when these MMAs have read it
                         if (++slot == T_STAGES) {
                             slot = 0;
@@ -402,6 +460,289 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
     tc_fence_before();
     __syncthreads();
     if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(T_TMEM_COLS));
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// CTA-pair variant (cta_group::2): two CTAs of a cluster share one 256 x 128 tile.  CTA r of the pair holds rows
+// 128 r .. of A and columns 64 r .. of B in its own shared memory; the MMAs (M 256, N 128), issued by the even CTA,
+// read both halves, and each CTA ends up with its 128 rows of the accumulator in its own tensor memory.  A K block
+// then costs a CTA 8 KB of A and 4 KB of B instead of 8 + 8: operand delivery, the limit of the single-CTA kernel,
+// drops by a quarter at the same MMA work per SM.  Stage 48 KB, ring of four.
+// Barriers: `full` lives in the even CTA and counts the bytes of both CTAs' copies (the copies carry cta_group::2
+// and name the even CTA's barrier); `empty` and `acc_full` exist in both CTAs and are signalled by one
+// tcgen05.commit with a CTA mask; the even CTA's `acc_empty` takes the arrivals of both CTAs' epilogue warps.
+// Both CTAs build the same list of live groups from the same pattern bytes.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int P2_TILE_M = 256;
+constexpr int P2_A_PART = 128 * 128;          // 128 rows x 32 floats
+constexpr int P2_B_PART = 64 * 128;           // 64 rows x 32 floats
+constexpr int P2_STAGE_BYTES = 2 * P2_A_PART + 2 * P2_B_PART;   // 49152
+constexpr int P2_STAGES = 4;
+struct Tf32PairMaps {
+    CUtensorMap a_hi, a_lo;                   // boxes of 32 floats x 128 rows, 128-byte swizzle
+    CUtensorMap b_hi, b_lo;                   // boxes of 32 floats x 64 rows
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// the address, in the cluster's shared window, of this CTA's shared address `addr` in CTA `rank`
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// copy into this CTA's shared memory, bytes counted on a barrier that may live in the pair's other CTA
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// arrives on the barrier at this shared offset in both CTAs of the pair once the MMAs issued so far are complete
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"(mask)
+                 : "memory");
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T_THREADS, 1)
+esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, const Tf32Params p)
+{
+    extern __shared__ __align__(1024) char smem[];
+    // layout: ring (P2_STAGES x 48 KB) | group lists (2 x cap u16) | barriers | misc
+    const int list_stride = ((p.cap * 2 + 15) & ~15) / 2;
+    uint16_t *lists = reinterpret_cast<uint16_t *>(smem + P2_STAGES * P2_STAGE_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_STAGES * P2_STAGE_BYTES + 4 * list_stride);
+    // full[4], empty[4], acc_full[2], acc_empty[2], lfull[2], lempty[2]
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 4), accf0 = smem_u32(bars + 8),
+                   acce0 = smem_u32(bars + 10), lfull0 = smem_u32(bars + 12), lempty0 = smem_u32(bars + 14);
+    volatile int *nlive = reinterpret_cast<volatile int *>(bars + 16);
+    volatile int *abort_flag = nlive + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(const_cast<int *>(nlive + 3));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P2_STAGES; ++s) {
+            mbar_init(full0 + 8 * s, 1);         // the even CTA's producer; bytes of both CTAs' copies
+            mbar_init(empty0 + 8 * s, 1);        // one commit per stage, delivered to both CTAs
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(accf0 + 8 * b, 1);
+            mbar_init(acce0 + 8 * b, 8);         // (even CTA) the epilogue warps of both CTAs
+            mbar_init(lfull0 + 8 * b, 1);
+            mbar_init(lempty0 + 8 * b, leader ? 6 : 5);   // producer warp, MMA thread (even CTA), four epilogue warps
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(T_TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                          // both CTAs' barriers exist before anything remote touches them
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const int nGroups = (p.nKB + T_GROUP_KB - 1) / T_GROUP_KB;
+    bool ok = true;
+
+    if (warp == 2) {
+        // ---------------- mask warp: live groups of the pair's tile (8 row blocks of A, 4 column blocks of B) ----------------
+        int it = 0;
+        for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(lempty0 + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            uint16_t *list = lists + buf * list_stride;
+            int pos = 0;
+            for (int g0 = 0; g0 < nGroups; g0 += 32) {
+                const int g = g0 + lane;
+                unsigned live = 0;
+                if (g < nGroups) {
+                    unsigned au[T_GROUP_KB] = {0, 0, 0, 0}, bu[T_GROUP_KB] = {0, 0, 0, 0};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int mb = tm * 8 + i, nb = tn * 4 + (i & 3);
+#pragma unroll
+                        for (int j = 0; j < T_GROUP_KB; ++j) {
+                            const int kb = g * T_GROUP_KB + j;
+                            if (kb < p.nKB) {
+                                if (mb < p.a_rows) au[j] |= p.a_pat[(size_t)mb * p.nKB + kb];
+                                if (i < 4 && nb < p.b_rows) bu[j] |= p.b_pat[(size_t)nb * p.nKB + kb];
+                            }
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < T_GROUP_KB; ++j) live |= ((au[j] & bu[j]) != 0u ? 1u : 0u) << j;
+                }
+                const unsigned m = __ballot_sync(0xFFFFFFFFu, live != 0u);
+                if (live) list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
+                pos += __popc(m);
+            }
+            if (lane == 0) nlive[buf] = pos;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
+        }
+    } else if (warp == 0) {
+        // ---------------- producer: this CTA's halves of the group; bytes are counted in the even CTA ----------------
+        if (lane < 4) tma_prefetch_descriptor(&maps.a_hi + lane);
+        int slot = 0, it = 0;
+        uint32_t phase = 0;
+        for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+            const int buf = it & 1;
+            ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            if (!ok) break;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            const uint16_t *list = lists + buf * list_stride;
+            const int n = nlive[buf];
+            const int row0 = (lane & 2) ? tn * TILE_N + (int)rank * 64 : tm * P2_TILE_M + (int)rank * 128;
+            const uint32_t part_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)P2_A_PART
+                                    : lane == 2 ? 2u * P2_A_PART : 2u * P2_A_PART + P2_B_PART;
+            for (int q = 0; q < n; ++q) {
+                ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
+                ok = __all_sync(0xFFFFFFFFu, ok);
+                if (!ok) break;
+                const uint32_t full_leader = map_to_cta(full0 + 8 * slot, 0);
+                if (leader && lane == 0) mbar_arrive_expect_tx(full0 + 8 * slot, 2u * P2_STAGE_BYTES);
+                __syncwarp();
+                if (lane < 4) {
+                    const int k = (int)(list[q] & 0xFFFu) * (T_GROUP_KB * BK);
+                    tma_load_2d_pair(smem_u32(smem) + (uint32_t)slot * P2_STAGE_BYTES + part_off, &maps.a_hi + lane, k, row0,
+                                     full_leader);
+                }
+                if (++slot == P2_STAGES) {
+                    slot = 0;
+                    phase ^= 1;
+                }
+            }
+            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+        }
+    }
+    else if (warp == 1) {
+        // ---------------- MMA issue: one thread of the even CTA, for both CTAs ----------------
+        if (leader && lane == 0) {
+            int slot = 0, it = 0;
+            uint32_t phase = 0, chunk = 0;
+            bool landed = false;                         // the next group's copies were seen complete by a poll
+            const uint32_t ring_lo = umma_desc_lo(smem_u32(smem));
+            for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+                const int buf = it & 1;
+                ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+                if (!ok) break;
+                const uint16_t *list = lists + buf * list_stride;
+                const int n = nlive[buf];
+                for (int c0 = 0; c0 < n && ok; c0 += T_CHUNK, ++chunk) {
+                    const uint32_t ab = chunk & 1u;
+                    ok = mbar_wait(acce0 + 8 * ab, ((chunk >> 1) & 1u) ^ 1u, abort_flag);   // drained in both CTAs
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t d = tmem + ab * 128u;
+                    uint32_t accumulate = 0;
+                    const int c1 = min(n, c0 + T_CHUNK);
+                    for (int q = c0; q < c1; ++q) {
+                        if (!landed) ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);  // both CTAs' copies landed
+                        if (!ok) break;
+                        const uint32_t ah = ring_lo + (uint32_t)slot * (P2_STAGE_BYTES >> 4);
+                        const int nslot = slot + 1 == P2_STAGES ? 0 : slot + 1;
+                        landed = umma_group<true>(d, ah, ah + (P2_A_PART >> 4), ah + 2 * (P2_A_PART >> 4),
+                                                  ah + ((2 * P2_A_PART + P2_B_PART) >> 4), (unsigned)list[q] >> 12,
+                                                  accumulate, full0 + 8 * nslot, nslot ? phase : phase ^ 1u);
+                        umma_commit_pair(empty0 + 8 * slot);
+                        if (++slot == P2_STAGES) {
+                            slot = 0;
+                            phase ^= 1;
+                        }
+                    }
+                    if (!ok) break;
+                    umma_commit_pair(accf0 + 8 * ab);
+                }
+                if (!ok) break;
+                mbar_arrive(lempty0 + 8 * buf);
+            }
+        }
+    } else if (warp >= 4) {
+        // ---------------- epilogue: this CTA's 128 rows of the accumulator, one C row per thread ----------------
+        const int q = warp - 4;
+        int it = 0;
+        uint32_t chunk = 0;
+        for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+            const int buf = it & 1;
+            int tm, tn;
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            if (!ok) break;
+            const int n = nlive[buf];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+            float acc[TILE_N];
+#pragma unroll
+            for (int j = 0; j < TILE_N; ++j) acc[j] = 0.0f;
+            for (int c0 = 0; c0 < n && ok; c0 += T_CHUNK, ++chunk) {
+                const uint32_t ab = chunk & 1u;
+                ok = mbar_wait(accf0 + 8 * ab, (chunk >> 1) & 1u, abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+#pragma unroll
+                for (int cc = 0; cc < TILE_N; cc += 32) {
+                    uint32_t r[32];
+                    tmem_ld_32(tmem + ((uint32_t)(q * 32) << 16) + ab * 128u + (uint32_t)cc, r);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) acc[cc + j] += __uint_as_float(r[j]);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(map_to_cta(acce0 + 8 * ab, 0));
+            }
+            if (!ok) break;
+            const int row = tm * P2_TILE_M + (int)rank * 128 + q * 32 + lane;
+            if (row < p.M) {
+                float *dst = p.C + (size_t)row * p.N + tn * TILE_N;
+#pragma unroll
+                for (int j = 0; j < TILE_N; j += 4)
+                    if (tn * TILE_N + j < p.N)
+                        *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            }
+        }
+    }
+
+    if (!ok && lane == 0) atomicExch(p.status, (int)ESMM_ERR_TIMEOUT);
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();        // nothing of the other CTA (its barriers, shared memory, tensor memory) is touched after this
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(T_TMEM_COLS));
 }
 
 }  // namespace esmm
@@ -556,22 +897,44 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     p.status = device_status_ptr();
     if (!p.status) return ESMM_ERR_CUDA;
 
-    Tf32Maps maps;
     const float *bt_hi = b->d_bt, *bt_lo = b->d_bt + (size_t)N * Kc;
     const CUtensorMapL2promotion l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
     const uint32_t box_k = T_GROUP_KB * BK;
-    st = make_map_2d(&maps.a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, l2);
-    if (!st) st = make_map_2d(&maps.a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, CU_TENSOR_MAP_SWIZZLE_128B, l2);
-    if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, CU_TENSOR_MAP_SWIZZLE_128B, l2);
-    if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, CU_TENSOR_MAP_SWIZZLE_128B, l2);
-    if (st) return st;
-
-    const size_t smem = (size_t)T_STAGES * T_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 14 * 8 + 16;
-    if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
     int dev = 0, sms = 0;
     ESMM_CUDA_TRY(cudaGetDevice(&dev));
     if (dev != b->device) return record_cuda_error_text("esmm_sgemm_joint_tf32x3: B was prepared on another device");
     ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+
+    // 256-row tiles on CTA pairs where A has the rows for them (ESMM_TF32_PAIR=0: single-CTA kernel everywhere)
+    if (M >= 192 && env_int("ESMM_TF32_PAIR", 1) != 0) {
+        p.tiles_m = ceil_div(M, P2_TILE_M);
+        p.num_tiles = p.tiles_m * p.tiles_n;
+        Tf32PairMaps maps;
+        st = make_map_2d(&maps.a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
+        if (!st) st = make_map_2d(&maps.a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
+        if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, 64, sw, l2);
+        if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, 64, sw, l2);
+        if (st) return st;
+        const size_t smem = (size_t)P2_STAGES * P2_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 16;
+        if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        const int pairs = std::max(1, std::min(sms / 2, p.num_tiles));
+        esmm_joint_sgemm_tf32x3_pair_kernel<<<2 * pairs, T_THREADS, smem, stream>>>(maps, p);
+        ESMM_CUDA_TRY(cudaGetLastError());
+        return ESMM_OK;
+    }
+
+    Tf32Maps maps;
+    st = make_map_2d(&maps.a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, sw, l2);
+    if (!st) st = make_map_2d(&maps.a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, sw, l2);
+    if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, sw, l2);
+    if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, sw, l2);
+    if (st) return st;
+
+    const size_t smem = (size_t)T_STAGES * T_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 14 * 8 + 16;
+    if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
     ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)smem));
     const int grid = std::min(sms, p.num_tiles);
