@@ -76,11 +76,10 @@ struct Tf32Maps {
 constexpr uint32_t UMMA_DESC_HI_K128 = 64u | (1u << 14) | (2u << 29);
 __device__ __forceinline__ uint32_t umma_desc_lo(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
 
-// instruction descriptors: D = F32, A = B = TF32, both K-major; N = 128; M = 128 (one CTA) or 256 (CTA pair)
+// instruction descriptor: D = F32 (bit 4), A = B = TF32 (bits 7, 10), both K-major, N >> 3 at bit 17, M >> 4 at bit 24
 constexpr uint32_t UMMA_IDESC_TF32_128x128 = (1u << 4) | (2u << 7) | (2u << 10) | (16u << 17) | (8u << 24);
-constexpr uint32_t UMMA_IDESC_TF32_256x128 = (1u << 4) | (2u << 7) | (2u << 10) | (16u << 17) | (16u << 24);
 
-template <bool PAIR>
+template <bool PAIR, uint32_t IDESC>
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint32_t a_lo, uint32_t b_lo, uint32_t accumulate)
 {
     if constexpr (PAIR) {
@@ -88,26 +87,26 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint32_t a_lo, uint32
             "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
             "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::2.kind::tf32 [%0], da, db, %3, {%6, %6, %6, %6, %6, %6, %6, %6}, p;\n\t}\n" ::"r"(tmem_d),
-            "r"(a_lo), "r"(b_lo), "r"(UMMA_IDESC_TF32_256x128), "r"(accumulate), "r"(UMMA_DESC_HI_K128), "r"(0u)
+            "r"(a_lo), "r"(b_lo), "r"(IDESC), "r"(accumulate), "r"(UMMA_DESC_HI_K128), "r"(0u)
             : "memory");
     } else {
         asm volatile(
             "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
             "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\tsetp.ne.b32 p, %4, 0;\n\t"
             "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %3, {%6, %6, %6, %6}, p;\n\t}\n" ::"r"(tmem_d),
-            "r"(a_lo), "r"(b_lo), "r"(UMMA_IDESC_TF32_128x128), "r"(accumulate), "r"(UMMA_DESC_HI_K128), "r"(0u)
+            "r"(a_lo), "r"(b_lo), "r"(IDESC), "r"(accumulate), "r"(UMMA_DESC_HI_K128), "r"(0u)
             : "memory");
     }
 }
 
 // the three products of K block j of a group: small terms first
-template <bool PAIR>
+template <bool PAIR, uint32_t IDESC>
 __device__ __forceinline__ void umma_kblock(uint32_t d, uint32_t ah, uint32_t al, uint32_t bh, uint32_t bl, uint32_t j,
                                             uint32_t accumulate)
 {
-    umma_tf32<PAIR>(d, al + 2u * j, bh + 2u * j, accumulate);
-    umma_tf32<PAIR>(d, ah + 2u * j, bl + 2u * j, 1u);
-    umma_tf32<PAIR>(d, ah + 2u * j, bh + 2u * j, 1u);
+    umma_tf32<PAIR, IDESC>(d, al + 2u * j, bh + 2u * j, accumulate);
+    umma_tf32<PAIR, IDESC>(d, ah + 2u * j, bl + 2u * j, 1u);
+    umma_tf32<PAIR, IDESC>(d, ah + 2u * j, bh + 2u * j, 1u);
 }
 
 __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
@@ -126,26 +125,26 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
 // two MMAs take, and the tensor pipe runs dry meanwhile.  So the next group's barrier is polled (one
 // non-blocking test) right after this group's first K block is issued, while the pipe has work queued; the
 // caller skips its wait when the poll said "landed".
-template <bool PAIR>
+template <bool PAIR, uint32_t IDESC>
 __device__ __forceinline__ bool umma_group(uint32_t d, uint32_t ah, uint32_t al, uint32_t bh, uint32_t bl, unsigned live,
                                            uint32_t &accumulate, uint32_t next_bar, uint32_t next_parity)
 {
     bool next_ready;
     if (live == 0xFu) {
-        umma_kblock<PAIR>(d, ah, al, bh, bl, 0u, accumulate);
+        umma_kblock<PAIR, IDESC>(d, ah, al, bh, bl, 0u, accumulate);
         next_ready = mbar_test_wait(next_bar, next_parity);
-        umma_kblock<PAIR>(d, ah, al, bh, bl, 1u, 1u);
-        umma_kblock<PAIR>(d, ah, al, bh, bl, 2u, 1u);
-        umma_kblock<PAIR>(d, ah, al, bh, bl, 3u, 1u);
+        umma_kblock<PAIR, IDESC>(d, ah, al, bh, bl, 1u, 1u);
+        umma_kblock<PAIR, IDESC>(d, ah, al, bh, bl, 2u, 1u);
+        umma_kblock<PAIR, IDESC>(d, ah, al, bh, bl, 3u, 1u);
     } else {
         uint32_t j = (uint32_t)(__ffs(live) - 1);
         live &= live - 1;
-        umma_kblock<PAIR>(d, ah, al, bh, bl, j, accumulate);
+        umma_kblock<PAIR, IDESC>(d, ah, al, bh, bl, j, accumulate);
         next_ready = mbar_test_wait(next_bar, next_parity);
         while (live) {
             j = (uint32_t)(__ffs(live) - 1);
             live &= live - 1;
-            umma_kblock<PAIR>(d, ah, al, bh, bl, j, 1u);
+            umma_kblock<PAIR, IDESC>(d, ah, al, bh, bl, j, 1u);
         }
     }
     accumulate = 1u;
@@ -394,7 +393,7 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
                         if (!ok) break;
                         const uint32_t ah = ring_lo + (uint32_t)slot * (T_STAGE_BYTES >> 4);
                         const int nslot = slot + 1 == T_STAGES ? 0 : slot + 1;
-                        landed = umma_group<false>(d, ah, ah + (T_PART_BYTES >> 4), ah + 2 * (T_PART_BYTES >> 4),
+                        landed = umma_group<false, UMMA_IDESC_TF32_128x128>(d, ah, ah + (T_PART_BYTES >> 4), ah + 2 * (T_PART_BYTES >> 4),
                                                    ah + 3 * (T_PART_BYTES >> 4), (unsigned)list[q] >> 12, accumulate,
                                                    full0 + 8 * nslot, nslot ? phase : phase ^ 1u);
                         umma_commit(empty0 + 8 * slot);          // the slot is free when these MMAs have read it
@@ -475,12 +474,19 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int P2_TILE_M = 256;
 constexpr int P2_A_PART = 128 * 128;          // 128 rows x 32 floats
-constexpr int P2_B_PART = 64 * 128;           // 64 rows x 32 floats
-constexpr int P2_STAGE_BYTES = 2 * P2_A_PART + 2 * P2_B_PART;   // 49152
-constexpr int P2_STAGES = 4;
+// NB: columns of the pair's tile (the N of its MMAs), 128 or 256; each CTA holds NB / 2 of them
+template <int NB> struct PairCfg {
+    static constexpr int B_PART = (NB / 2) * 128;                  // NB / 2 rows x 32 floats
+    static constexpr int STAGE_BYTES = 2 * P2_A_PART + 2 * B_PART; // 48 KB or 64 KB
+    static constexpr int STAGES = NB == 128 ? 4 : 3;
+    static constexpr int EPI_WARPS = 4 * (NB / 128);               // a set of four warps per 128 columns
+    static constexpr int THREADS = (4 + EPI_WARPS) * 32;
+    static constexpr int TMEM_COLS = 2 * NB;                       // two accumulators
+    static constexpr uint32_t IDESC = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(NB >> 3) << 17) | (16u << 24);
+};
 struct Tf32PairMaps {
     CUtensorMap a_hi, a_lo;                   // boxes of 32 floats x 128 rows, 128-byte swizzle
-    CUtensorMap b_hi, b_lo;                   // boxes of 32 floats x 64 rows
+    CUtensorMap b_hi, b_lo;                   // boxes of 32 floats x NB / 2 rows
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank()
@@ -527,14 +533,16 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar)
                  : "memory");
 }
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(T_THREADS, 1)
+template <int NB>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<NB>::THREADS, 1)
 esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, const Tf32Params p)
 {
+    using Cfg = PairCfg<NB>;
     extern __shared__ __align__(1024) char smem[];
-    // layout: ring (P2_STAGES x 48 KB) | group lists (2 x cap u16) | barriers | misc
+    // layout: ring (STAGES x STAGE_BYTES) | group lists (2 x cap u16) | barriers | misc
     const int list_stride = ((p.cap * 2 + 15) & ~15) / 2;
-    uint16_t *lists = reinterpret_cast<uint16_t *>(smem + P2_STAGES * P2_STAGE_BYTES);
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + P2_STAGES * P2_STAGE_BYTES + 4 * list_stride);
+    uint16_t *lists = reinterpret_cast<uint16_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + Cfg::STAGES * Cfg::STAGE_BYTES + 4 * list_stride);
     // full[4], empty[4], acc_full[2], acc_empty[2], lfull[2], lempty[2]
     const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + 4), accf0 = smem_u32(bars + 8),
                    acce0 = smem_u32(bars + 10), lfull0 = smem_u32(bars + 12), lempty0 = smem_u32(bars + 14);
@@ -547,15 +555,15 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
     const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < P2_STAGES; ++s) {
+        for (int s = 0; s < Cfg::STAGES; ++s) {
             mbar_init(full0 + 8 * s, 1);         // the even CTA's producer; bytes of both CTAs' copies
             mbar_init(empty0 + 8 * s, 1);        // one commit per stage, delivered to both CTAs
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(accf0 + 8 * b, 1);
-            mbar_init(acce0 + 8 * b, 8);         // (even CTA) the epilogue warps of both CTAs
+            mbar_init(acce0 + 8 * b, 2 * Cfg::EPI_WARPS);   // (even CTA) the epilogue warps of both CTAs
             mbar_init(lfull0 + 8 * b, 1);
-            mbar_init(lempty0 + 8 * b, leader ? 6 : 5);   // producer warp, MMA thread (even CTA), four epilogue warps
+            mbar_init(lempty0 + 8 * b, Cfg::EPI_WARPS + (leader ? 2 : 1));   // producer warp, MMA thread (even CTA), epilogue warps
         }
         *abort_flag = 0;
         fence_barrier_init();
@@ -563,7 +571,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
-                     "r"(T_TMEM_COLS));
+                     "r"(Cfg::TMEM_COLS));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
     }
     tc_fence_before();
@@ -574,6 +582,11 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
     const int nGroups = (p.nKB + T_GROUP_KB - 1) / T_GROUP_KB;
     bool ok = true;
 
+    // With the wide tile, 12 warps leave 168 registers per thread and an epilogue thread keeps a 128-column row of
+    // run sums: the first four warps (producer, MMA, mask, idle) hand registers over to the eight epilogue warps.
+    // The instruction sits at the head of each side's own branch so that the code below it is compiled for its budget.
+    if (warp < 4) {
+    if constexpr (NB == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 2) {
         // ---------------- mask warp: live groups of the pair's tile (8 row blocks of A, 4 column blocks of B) ----------------
         int it = 0;
@@ -590,15 +603,15 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                 unsigned live = 0;
                 if (g < nGroups) {
                     unsigned au[T_GROUP_KB] = {0, 0, 0, 0}, bu[T_GROUP_KB] = {0, 0, 0, 0};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int mb = tm * 8 + i, nb = tn * 4 + (i & 3);
+#pragma unroll 1
+                    for (int i = 0; i < 8; ++i) {           // not unrolled: this warp runs on a small register budget
+                        const int mb = tm * 8 + i, nb = tn * (NB / 32) + i;
 #pragma unroll
                         for (int j = 0; j < T_GROUP_KB; ++j) {
                             const int kb = g * T_GROUP_KB + j;
                             if (kb < p.nKB) {
                                 if (mb < p.a_rows) au[j] |= p.a_pat[(size_t)mb * p.nKB + kb];
-                                if (i < 4 && nb < p.b_rows) bu[j] |= p.b_pat[(size_t)nb * p.nKB + kb];
+                                if (i < NB / 32 && nb < p.b_rows) bu[j] |= p.b_pat[(size_t)nb * p.nKB + kb];
                             }
                         }
                     }
@@ -626,22 +639,22 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
             const uint16_t *list = lists + buf * list_stride;
             const int n = nlive[buf];
-            const int row0 = (lane & 2) ? tn * TILE_N + (int)rank * 64 : tm * P2_TILE_M + (int)rank * 128;
+            const int row0 = (lane & 2) ? tn * NB + (int)rank * (NB / 2) : tm * P2_TILE_M + (int)rank * 128;
             const uint32_t part_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)P2_A_PART
-                                    : lane == 2 ? 2u * P2_A_PART : 2u * P2_A_PART + P2_B_PART;
+                                    : lane == 2 ? 2u * P2_A_PART : 2u * P2_A_PART + Cfg::B_PART;
             for (int q = 0; q < n; ++q) {
                 ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
                 const uint32_t full_leader = map_to_cta(full0 + 8 * slot, 0);
-                if (leader && lane == 0) mbar_arrive_expect_tx(full0 + 8 * slot, 2u * P2_STAGE_BYTES);
+                if (leader && lane == 0) mbar_arrive_expect_tx(full0 + 8 * slot, 2u * Cfg::STAGE_BYTES);
                 __syncwarp();
                 if (lane < 4) {
                     const int k = (int)(list[q] & 0xFFFu) * (T_GROUP_KB * BK);
-                    tma_load_2d_pair(smem_u32(smem) + (uint32_t)slot * P2_STAGE_BYTES + part_off, &maps.a_hi + lane, k, row0,
+                    tma_load_2d_pair(smem_u32(smem) + (uint32_t)slot * Cfg::STAGE_BYTES + part_off, &maps.a_hi + lane, k, row0,
                                      full_leader);
                 }
-                if (++slot == P2_STAGES) {
+                if (++slot == Cfg::STAGES) {
                     slot = 0;
                     phase ^= 1;
                 }
@@ -669,19 +682,19 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                     ok = mbar_wait(acce0 + 8 * ab, ((chunk >> 1) & 1u) ^ 1u, abort_flag);   // drained in both CTAs
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t d = tmem + ab * 128u;
+                    const uint32_t d = tmem + ab * (uint32_t)NB;
                     uint32_t accumulate = 0;
                     const int c1 = min(n, c0 + T_CHUNK);
                     for (int q = c0; q < c1; ++q) {
                         if (!landed) ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);  // both CTAs' copies landed
                         if (!ok) break;
-                        const uint32_t ah = ring_lo + (uint32_t)slot * (P2_STAGE_BYTES >> 4);
-                        const int nslot = slot + 1 == P2_STAGES ? 0 : slot + 1;
-                        landed = umma_group<true>(d, ah, ah + (P2_A_PART >> 4), ah + 2 * (P2_A_PART >> 4),
-                                                  ah + ((2 * P2_A_PART + P2_B_PART) >> 4), (unsigned)list[q] >> 12,
+                        const uint32_t ah = ring_lo + (uint32_t)slot * (Cfg::STAGE_BYTES >> 4);
+                        const int nslot = slot + 1 == Cfg::STAGES ? 0 : slot + 1;
+                        landed = umma_group<true, Cfg::IDESC>(d, ah, ah + (P2_A_PART >> 4), ah + 2 * (P2_A_PART >> 4),
+                                                  ah + ((2 * P2_A_PART + Cfg::B_PART) >> 4), (unsigned)list[q] >> 12,
                                                   accumulate, full0 + 8 * nslot, nslot ? phase : phase ^ 1u);
                         umma_commit_pair(empty0 + 8 * slot);
-                        if (++slot == P2_STAGES) {
+                        if (++slot == Cfg::STAGES) {
                             slot = 0;
                             phase ^= 1;
                         }
@@ -693,9 +706,11 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                 mbar_arrive(lempty0 + 8 * buf);
             }
         }
-    } else if (warp >= 4) {
+    }
+    } else {
+        if constexpr (NB == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // ---------------- epilogue: this CTA's 128 rows of the accumulator, one C row per thread ----------------
-        const int q = warp - 4;
+        const int q = (warp - 4) & 3, half = (warp - 4) >> 2;    // TMEM lanes 32 q .., columns 128 half ..
         int it = 0;
         uint32_t chunk = 0;
         for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
@@ -718,7 +733,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
 #pragma unroll
                 for (int cc = 0; cc < TILE_N; cc += 32) {
                     uint32_t r[32];
-                    tmem_ld_32(tmem + ((uint32_t)(q * 32) << 16) + ab * 128u + (uint32_t)cc, r);
+                    tmem_ld_32(tmem + ((uint32_t)(q * 32) << 16) + ab * (uint32_t)NB + (uint32_t)(half * 128 + cc), r);
 #pragma unroll
                     for (int j = 0; j < 32; ++j) acc[cc + j] += __uint_as_float(r[j]);
                 }
@@ -729,10 +744,11 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
             if (!ok) break;
             const int row = tm * P2_TILE_M + (int)rank * 128 + q * 32 + lane;
             if (row < p.M) {
-                float *dst = p.C + (size_t)row * p.N + tn * TILE_N;
+                const int col0 = tn * NB + half * 128;
+                float *dst = p.C + (size_t)row * p.N + col0;
 #pragma unroll
                 for (int j = 0; j < TILE_N; j += 4)
-                    if (tn * TILE_N + j < p.N)
+                    if (col0 + j < p.N)
                         *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
             }
         }
@@ -742,7 +758,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
     tc_fence_before();
     __syncthreads();
     cluster_sync_all();        // nothing of the other CTA (its barriers, shared memory, tensor memory) is touched after this
-    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(T_TMEM_COLS));
+    if (warp == 1) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(Cfg::TMEM_COLS));
 }
 
 }  // namespace esmm
@@ -906,22 +922,34 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     if (dev != b->device) return record_cuda_error_text("esmm_sgemm_joint_tf32x3: B was prepared on another device");
     ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
 
-    // 256-row tiles on CTA pairs where A has the rows for them (ESMM_TF32_PAIR=0: single-CTA kernel everywhere)
-    if (M >= 192 && env_int("ESMM_TF32_PAIR", 1) != 0) {
+    // CTA pairs (256-row tiles) where the problem has the rows and columns for them: 256 x 256 per pair by default,
+    // ESMM_TF32_PAIR=128 for 256 x 128 per pair, =0 for the single-CTA kernel everywhere
+    const int pair_env = env_int("ESMM_TF32_PAIR", 256);
+    const int nb = (M < 192 || pair_env == 0) ? 0 : (pair_env == 128 || N < 192) ? 128 : 256;
+    if (nb) {
         p.tiles_m = ceil_div(M, P2_TILE_M);
+        p.tiles_n = ceil_div(N, nb);
         p.num_tiles = p.tiles_m * p.tiles_n;
         Tf32PairMaps maps;
         st = make_map_2d(&maps.a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
         if (!st) st = make_map_2d(&maps.a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
-        if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, 64, sw, l2);
-        if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, 64, sw, l2);
+        if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, nb / 2, sw, l2);
+        if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, nb / 2, sw, l2);
         if (st) return st;
-        const size_t smem = (size_t)P2_STAGES * P2_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 16;
+        const int stage_bytes = nb == 128 ? PairCfg<128>::STAGE_BYTES * PairCfg<128>::STAGES
+                                          : PairCfg<256>::STAGE_BYTES * PairCfg<256>::STAGES;
+        const size_t smem = (size_t)stage_bytes + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 16;
         if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
-        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         const int pairs = std::max(1, std::min(sms / 2, p.num_tiles));
-        esmm_joint_sgemm_tf32x3_pair_kernel<<<2 * pairs, T_THREADS, smem, stream>>>(maps, p);
+        if (nb == 128) {
+            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel<128>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            esmm_joint_sgemm_tf32x3_pair_kernel<128><<<2 * pairs, PairCfg<128>::THREADS, smem, stream>>>(maps, p);
+        } else {
+            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel<256>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            esmm_joint_sgemm_tf32x3_pair_kernel<256><<<2 * pairs, PairCfg<256>::THREADS, smem, stream>>>(maps, p);
+        }
         ESMM_CUDA_TRY(cudaGetLastError());
         return ESMM_OK;
     }

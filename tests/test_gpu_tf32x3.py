@@ -65,6 +65,19 @@ def test_tile_random(cuda, pkg, oracle_mod, M, N, K, pa, pb):
     assert rel_inf(c, oracle_mod.gemm_joint(A, B)) <= TIGHT
 
 
+@pytest.mark.parametrize("pair", ["0", "128", "256"])
+def test_kernel_variants_agree(cuda, pkg, oracle_mod, monkeypatch, pair):
+    """ESMM_TF32_PAIR selects the kernel: 0 = one CTA per 128 x 128 tile, 128 / 256 = a CTA pair (cta_group::2) per
+    256 x 128 / 256 x 256 tile (the default where M and N allow).  Ragged sizes, dead K blocks, several tiles per CTA."""
+    monkeypatch.setenv("ESMM_TF32_PAIR", pair)
+    for (M, N, K, pa, pb, seed) in [(520, 776, 1032, 0.2, 0.2, 1), (256, 256, 64, 1.0, 1.0, 2), (2048, 2304, 512, 0.5, 0.5, 3)]:
+        A, B = workloads.tile_random(M, N, K, pa, pb, seed=seed, gran_a=32, gran_b=32)
+        A[300:460] = 0.0                     # a dead band of A: tiles and half-tiles without work
+        c, _ = run_tf32x3(cuda, pkg, A, B)
+        assert rel_inf(c, oracle_mod.gemm_joint(A, B)) <= TIGHT, (M, N, K)
+        assert not c[300:460].any()
+
+
 @pytest.mark.parametrize("compact", [True, False])
 def test_block_structured_and_dead_tiles(cuda, pkg, oracle_mod, compact):
     """Whole pattern blocks dead (K-block skipping does all the work), plus a band of A and a band of B that
