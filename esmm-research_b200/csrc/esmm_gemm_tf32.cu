@@ -9,8 +9,8 @@
 // Skipping happens at two levels.  (1) When B is prepared, every k whose row of B is all zero is dropped from both
 // operands (the split of A gathers the kept columns), so patterns that repeat in every K block, the reference's
 // benchmark patterns, shrink K itself.  (2) Of what is left, a K block (8 k, the K extent of one kind::tf32 MMA)
-// of a 128 x 128 tile is multiplied only if some k in it is live for the tile (OR of the tile's four A pattern
-// bytes AND OR of its four B pattern bytes), and a group of four K blocks is fetched only if one of them is.
+// of a tile is multiplied only if some k in it is live for the tile (OR of the A pattern bytes of the tile's row
+// blocks AND OR of the B pattern bytes of its column blocks), and a group of four K blocks is fetched only if one is.
 // Everything skipped multiplies exact zeros, so the sum is the one the reference's masked FMA chain forms
 // (src/kernels/esmm_ab_optimized_v3.cu:157, 183-203) up to rounding.
 //
@@ -25,17 +25,29 @@
 // 32 j bytes into the swizzled row.  (Boxes of one K block with the 32-byte swizzle were measured first: 1.6 x
 // slower, the copy engine handles about one box row per cycle whatever its width.)
 //
-// One persistent CTA per SM, 8 warps: a mask warp lists the live groups of the next tile, a producer warp fetches
-// one group per stage into a three-deep ring (64 KB per stage), one thread issues the MMAs and commits them to
-// the ring's and the accumulator's mbarriers, four epilogue warps drain one of two TMEM accumulators (128 lanes x
-// 128 columns each) while the other is being filled.  Every wait is bounded, as in the other kernels, and the
-// tensor memory is freed on every path out.
+// Kernels.  All persistent, one CTA per SM, warp-specialised: a mask warp lists the live groups of the next tile, a
+// producer warp fetches one group per ring stage, one thread issues the MMAs and commits them to the ring's and
+// the accumulator's mbarriers, epilogue warps drain one of two TMEM accumulators while the other is being filled.
+// Every wait is bounded, as in the other kernels, and the tensor memory is freed on every path out.
+//   esmm_joint_sgemm_tf32x3_pair_kernel<256>  default where M >= 192 and N >= 192.  Two CTAs of a cluster share a
+//       256 x 256 tile (cta_group::2 MMAs, M 256, N 256): each CTA fetches its 128 rows of A and its 128 columns of
+//       B, 16 KB per K block for two 128 x 128 tiles' worth of MMA work.  12 warps; the eight epilogue warps take
+//       registers over from the other four (setmaxnreg) for their 128-column rows of run sums.
+//   esmm_joint_sgemm_tf32x3_pair_kernel<128>  ESMM_TF32_PAIR=128 (and N < 192): 256 x 128 per pair.
+//   esmm_joint_sgemm_tf32x3_kernel            M < 192, or ESMM_TF32_PAIR=0: one CTA per 128 x 128 tile.
 //
-// Measured on one B200 at 4096^3 (whole call: split + A patterns + product): 0.67 ms dense against 2.36 ms for
-// the FP32 kernel; the tensor pipe is busy 58 % of the time and the rest is operand delivery (16 KB per K block
-// per SM, about 64 B per clock per SM: one MMA instead of three per K block is only 24 % faster, pulling groups
-// into L2 ahead of the ring changes nothing).  Halving the bytes per MMA needs a CTA pair sharing B halves
-// (cta_group::2), which is not built.
+// What was measured on the way (one B200, 4096^3 dense, cycles per group of four K blocks on one SM):
+//   * 128 x 128 tiles need 64 KB per group and the SM takes in about 64 bytes per clock from L2: 1024 cycles, more
+//     than the 813 cycles its twelve MMAs (128 x 128 x 8, 67.8 cycles each at the TF32 rate) take.  The single-CTA
+//     kernel runs at 1082.  Pulling groups into L2 ahead of the ring changes nothing (DRAM is not the limit).
+//   * The issuing thread's own instructions count: building two 64-bit descriptors per MMA cost 77 cycles per MMA
+//     (more than the MMA); with one precomputed word per operand it is 57.  A wait on a data barrier costs about
+//     170 cycles even when the data is there, so the next group's barrier is polled while the pipe has work.
+//   * 256 x 256 on a CTA pair: 64 KB per group feed 12 MMAs of 128 x 256 x 8 per SM; measured 1588 cycles per
+//     group in steady state, the tensor pipe's own time.  Over a whole 4096^3 call ncu shows the pipe 71 % busy:
+//     256 tiles on 74 pairs are 3.46 rounds, and a tile change costs a few thousand cycles.  In a long loop the
+//     GPU then sits at its 1000 W power cap (SM clock 1.6-1.7 GHz, sw_power_cap the only reason active).
+// Whole call (split + A patterns + product), bursts of 20 calls: 0.58 ms dense against 2.35 ms for the FP32 kernel.
 #include <algorithm>
 #include <cstring>
 #include <vector>
@@ -462,11 +474,12 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// CTA-pair variant (cta_group::2): two CTAs of a cluster share one 256 x 128 tile.  CTA r of the pair holds rows
-// 128 r .. of A and columns 64 r .. of B in its own shared memory; the MMAs (M 256, N 128), issued by the even CTA,
-// read both halves, and each CTA ends up with its 128 rows of the accumulator in its own tensor memory.  A K block
-// then costs a CTA 8 KB of A and 4 KB of B instead of 8 + 8: operand delivery, the limit of the single-CTA kernel,
-// drops by a quarter at the same MMA work per SM.  Stage 48 KB, ring of four.
+// CTA-pair variant (cta_group::2): two CTAs of a cluster share one 256 x NB tile, NB = 128 or 256.  CTA r of the pair
+// holds rows 128 r .. of A and columns (NB / 2) r .. of B in its own shared memory; the MMAs (M 256, N NB), issued by
+// the even CTA, read both halves, and each CTA ends up with its 128 rows of the accumulator in its own tensor
+// memory.  Per K block a CTA fetches 8 KB of A and NB / 32 KB of B: with NB = 256 that is the 16 KB of the
+// single-CTA kernel for twice its MMA work, which is what takes operand delivery off the critical path.
+// Ring: 4 stages of 48 KB (NB 128) or 3 of 64 KB (NB 256).
 // Barriers: `full` lives in the even CTA and counts the bytes of both CTAs' copies (the copies carry cta_group::2
 // and name the even CTA's barrier); `empty` and `acc_full` exist in both CTAs and are signalled by one
 // tcgen05.commit with a CTA mask; the even CTA's `acc_empty` takes the arrivals of both CTAs' epilogue warps.
