@@ -195,34 +195,58 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo)
     lo = __uint_as_float(l);
 }
 
-// A (M x K, row-major) -> A_hi, A_lo (M x Kc, row-major).  klist == nullptr: Kc == K, the same columns.
-// Otherwise column j of the output is column klist[j] of A (ascending; -1: a zero column of padding).
-__global__ void esmm_tf32_split_kernel(const float *__restrict__ A, int M, int K, const int *__restrict__ klist,
-                                       int Kc, float *__restrict__ hi, float *__restrict__ lo)
+// A (M x K, row-major) -> A_hi, A_lo (M x Kc, row-major) and the A pattern bytes of the result, in one pass.
+// klist == nullptr: Kc == K, the same columns.  Otherwise column j of the output is column klist[j] of A
+// (ascending; -1: a zero column of padding).  A value whose TF32 hi part is zero has a zero lo part too and
+// contributes nothing, so the pattern bit of (32-row block, k) is "some hi part is nonzero": the byte layout is the
+// one of esmm_preprocess_a (src/preprocessors/ab_preprocessor.cu:122-187), a_pat[mb * (Kc / 8) + kb], bit k.
+// One warp per 32 rows x 64 output columns: half-warp h takes the rows of parity h, lane c its float4 column.
+__global__ void __launch_bounds__(256)
+esmm_tf32_split_pattern_kernel(const float *__restrict__ A, int M, int K, const int *__restrict__ klist, int Kc,
+                               float *__restrict__ hi, float *__restrict__ lo, uint8_t *__restrict__ a_pat)
 {
-    const int q = Kc >> 2;                                     // float4 groups per output row
-    const size_t n4 = (size_t)M * q;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
-        float4 v;
-        if (klist == nullptr) {
-            v = __ldg(reinterpret_cast<const float4 *>(A) + i);
-        } else {
-            const size_t row = i / q;
-            const int4 k = __ldg(reinterpret_cast<const int4 *>(klist) + (i - row * q));
-            const float *a = A + row * K;
-            v.x = k.x >= 0 ? __ldg(a + k.x) : 0.0f;
-            v.y = k.y >= 0 ? __ldg(a + k.y) : 0.0f;
-            v.z = k.z >= 0 ? __ldg(a + k.z) : 0.0f;
-            v.w = k.w >= 0 ? __ldg(a + k.w) : 0.0f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int mb = blockIdx.y, col = (blockIdx.x * 8 + warp) * 64 + (lane & 15) * 4, h = lane >> 4;
+    if ((blockIdx.x * 8 + warp) * 64 >= Kc) return;               // the whole warp is past the last column
+    const bool in_cols = col < Kc;                                // Kc is a multiple of 8: a float4 is in or out
+    int4 k = make_int4(col, col + 1, col + 2, col + 3);
+    if (klist != nullptr && in_cols) k = __ldg(reinterpret_cast<const int4 *>(klist + col));
+    float4 v[16];
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr) {
+        const int row = mb * 32 + 2 * rr + h;
+        v[rr] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in_cols && row < M) {
+            const float *a = A + (size_t)row * K;
+            if (klist == nullptr) {
+                v[rr] = __ldg(reinterpret_cast<const float4 *>(a + col));
+            } else {
+                v[rr].x = k.x >= 0 ? __ldg(a + k.x) : 0.0f;
+                v[rr].y = k.y >= 0 ? __ldg(a + k.y) : 0.0f;
+                v[rr].z = k.z >= 0 ? __ldg(a + k.z) : 0.0f;
+                v[rr].w = k.w >= 0 ? __ldg(a + k.w) : 0.0f;
+            }
         }
-        float4 h, l;
-        split_tf32(v.x, h.x, l.x);
-        split_tf32(v.y, h.y, l.y);
-        split_tf32(v.z, h.z, l.z);
-        split_tf32(v.w, h.w, l.w);
-        reinterpret_cast<float4 *>(hi)[i] = h;
-        reinterpret_cast<float4 *>(lo)[i] = l;
     }
+    unsigned m = 0;
+#pragma unroll
+    for (int rr = 0; rr < 16; ++rr) {
+        const int row = mb * 32 + 2 * rr + h;
+        float4 hh, ll;
+        split_tf32(v[rr].x, hh.x, ll.x);
+        split_tf32(v[rr].y, hh.y, ll.y);
+        split_tf32(v[rr].z, hh.z, ll.z);
+        split_tf32(v[rr].w, hh.w, ll.w);
+        m |= ((__float_as_uint(hh.x) << 1) != 0u ? 1u : 0u) | ((__float_as_uint(hh.y) << 1) != 0u ? 2u : 0u) |
+             ((__float_as_uint(hh.z) << 1) != 0u ? 4u : 0u) | ((__float_as_uint(hh.w) << 1) != 0u ? 8u : 0u);
+        if (in_cols && row < M) {
+            *reinterpret_cast<float4 *>(hi + (size_t)row * Kc + col) = hh;
+            *reinterpret_cast<float4 *>(lo + (size_t)row * Kc + col) = ll;
+        }
+    }
+    m |= __shfl_xor_sync(0xFFFFFFFFu, m, 16);                     // both row parities
+    const unsigned other = __shfl_xor_sync(0xFFFFFFFFu, m, 1);    // the K block's other four k
+    if (lane < 16 && !(lane & 1) && in_cols) a_pat[(size_t)mb * (Kc >> 3) + (col >> 3)] = (uint8_t)(m | (other << 4));
 }
 
 // B (K x N, row-major) -> Bt_hi, Bt_lo (N x Kc, row-major): 32 x 32 tiles through shared memory; row j of the tile
@@ -899,14 +923,11 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     float *a_hi = reinterpret_cast<float *>(a_pat + ((esmm_a_pattern_bytes(M, K, 32) + 255) & ~(size_t)255));
     float *a_lo = a_hi + (size_t)M * Kc;
     {
-        const size_t n4 = (size_t)M * (Kc / 4);
-        const int blocks = (int)std::max<size_t>(1, std::min<size_t>((n4 + 255) / 256, 148 * 16));
-        esmm_tf32_split_kernel<<<blocks, 256, 0, stream>>>(d_A, M, K, b->d_klist, Kc, a_hi, a_lo);
+        dim3 grid((unsigned)ceil_div(Kc, 512), (unsigned)ceil_div(M, 32));
+        esmm_tf32_split_pattern_kernel<<<grid, 256, 0, stream>>>(d_A, M, K, b->d_klist, Kc, a_hi, a_lo, a_pat);
         ESMM_CUDA_TRY(cudaGetLastError());
     }
-    // a value whose TF32 parts are both zero contributes nothing, so the patterns are those of the hi part
-    int st = esmm_preprocess_a(a_hi, M, Kc, 32, a_pat, stream);
-    if (st != ESMM_OK) return st;
+    int st = ESMM_OK;
 
     Tf32Params p;
     memset(&p, 0, sizeof p);
@@ -930,10 +951,25 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     const CUtensorMapL2promotion l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
     const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
     const uint32_t box_k = T_GROUP_KB * BK;
-    int dev = 0, sms = 0;
+    int dev = 0;
     ESMM_CUDA_TRY(cudaGetDevice(&dev));
     if (dev != b->device) return record_cuda_error_text("esmm_sgemm_joint_tf32x3: B was prepared on another device");
-    ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    // per device, once: SM count and the opt-in to the kernels' dynamic shared memory (not thread-safe by design:
+    // like the rest of the library, one host thread per device)
+    static int sms_of[64];
+    static unsigned char opted[64];
+    if (dev < 0 || dev >= 64) return record_cuda_error_text("esmm_sgemm_joint_tf32x3: device ordinal out of range");
+    if (!sms_of[dev]) ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev));
+    const int sms = sms_of[dev];
+    if (!opted[dev]) {
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel<128>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel<256>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT));
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SMEM_LIMIT));
+        opted[dev] = 1;
+    }
 
     // CTA pairs (256-row tiles) where the problem has the rows and columns for them: 256 x 256 per pair by default,
     // ESMM_TF32_PAIR=128 for 256 x 128 per pair, =0 for the single-CTA kernel everywhere
@@ -955,12 +991,8 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
         if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
         const int pairs = std::max(1, std::min(sms / 2, p.num_tiles));
         if (nb == 128) {
-            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel<128>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             esmm_joint_sgemm_tf32x3_pair_kernel<128><<<2 * pairs, PairCfg<128>::THREADS, smem, stream>>>(maps, p);
         } else {
-            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_pair_kernel<256>,
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             esmm_joint_sgemm_tf32x3_pair_kernel<256><<<2 * pairs, PairCfg<256>::THREADS, smem, stream>>>(maps, p);
         }
         ESMM_CUDA_TRY(cudaGetLastError());
@@ -976,8 +1008,6 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
 
     const size_t smem = (size_t)T_STAGES * T_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 14 * 8 + 16;
     if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
-    ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_tf32x3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem));
     const int grid = std::min(sms, p.num_tiles);
     esmm_joint_sgemm_tf32x3_kernel<<<grid, T_THREADS, smem, stream>>>(maps, p);
     ESMM_CUDA_TRY(cudaGetLastError());

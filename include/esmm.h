@@ -242,7 +242,7 @@ int esmm_ffma_peak_tflops(double *tflops, int *sm_count);
  * esmm_tf32x3_b_create: the "B offline" step (beside esmm_preprocess_b): B patterns, the list of kept k, B
  *   transposed and split.  Allocates device memory, synchronises; the handle belongs to the current device.
  * esmm_tf32x3_b_live_k: k kept (K without compaction; else a multiple of 32, padding included).
- * esmm_sgemm_joint_tf32x3: split (and gather) of A + A patterns + product, three launches on `stream`, no
+ * esmm_sgemm_joint_tf32x3: split (and gather) of A with its A patterns + product, two launches on `stream`, no
  *   allocation.  d_A: M x K row-major; d_C: M x N; d_workspace: esmm_tf32x3_workspace_bytes(M, K) bytes,
  *   256-byte aligned. */
 typedef struct esmm_tf32x3_b esmm_tf32x3_b;
