@@ -66,6 +66,7 @@ constexpr int T_TMEM_COLS = 256;             // two accumulators of 128 columns
 
 struct Tf32Params {
     int M, N, K, nKB, cap;
+    int stage_off;                           // byte offset of the epilogue's staging squares in shared memory, 0: none
     int a_rows, b_rows, tiles_m, tiles_n, num_tiles;
     const uint8_t *a_pat;
     const uint8_t *b_pat;
@@ -273,6 +274,40 @@ __global__ void esmm_tf32_split_transpose_kernel(const float *__restrict__ B, in
     }
 }
 
+// A thread holds one C row of 128 run sums; written straight out, a warp's store touches 32 different rows (32
+// sectors of 16 useful bytes), and those scattered stores were seen to hold up the ring's copies for thousands
+// of cycles at every tile change.  Through a 32 x 33 float staging square per warp, every store instruction writes
+// one full 128-byte line of one row instead.  stage == nullptr (no shared memory left for it): the direct form.
+constexpr int T_STAGE_FLOATS = 32 * 33;
+__device__ __forceinline__ void store_row_block(const float (&acc)[TILE_N], float *stage, float *C, int row0, int col0,
+                                                int M, int N, int lane)
+{
+    if (stage == nullptr) {
+        const int row = row0 + lane;
+        if (row < M) {
+            float *dst = C + (size_t)row * N + col0;
+#pragma unroll
+            for (int j = 0; j < TILE_N; j += 4)
+                if (col0 + j < N) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+        }
+        return;
+    }
+#pragma unroll
+    for (int cc = 0; cc < TILE_N; cc += 32) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) stage[lane * 33 + j] = acc[cc + j];
+        __syncwarp();
+        const int col = col0 + cc + lane;
+        if (col < N) {
+            float *dst = C + (size_t)row0 * N + col;
+            const int rows = min(32, M - row0);
+#pragma unroll 8
+            for (int r = 0; r < rows; ++r) dst[(size_t)r * N] = stage[r * 33 + lane];
+        }
+        __syncwarp();
+    }
+}
+
 __global__ void __launch_bounds__(T_THREADS, 1)
 esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32Params p)
 {
@@ -449,6 +484,7 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
         // ---------------- epilogue: warp w owns TMEM lanes 32 (w - 4) .., one C row per thread; chunk sums are added
         // in registers with round-to-nearest, which keeps the tensor core's own accumulation runs short ----------------
         const int q = warp - 4;
+        float *stage = p.stage_off ? reinterpret_cast<float *>(smem + p.stage_off) + (warp - 4) * T_STAGE_FLOATS : nullptr;
         int it = 0;
         uint32_t chunk = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
@@ -480,14 +516,7 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
                 if (lane == 0) mbar_arrive(acce0 + 8 * ab);
             }
             if (!ok) break;
-            const int row = tm * TILE_M + q * 32 + lane;
-            if (row < p.M) {
-                float *dst = p.C + (size_t)row * p.N + tn * TILE_N;
-#pragma unroll
-                for (int j = 0; j < TILE_N; j += 4)
-                    if (tn * TILE_N + j < p.N)
-                        *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-            }
+            store_row_block(acc, stage, p.C, tm * TILE_M + q * 32, tn * TILE_N, p.M, p.N, lane);
         }
     }
 
@@ -748,6 +777,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
         if constexpr (NB == 256) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
         // ---------------- epilogue: this CTA's 128 rows of the accumulator, one C row per thread ----------------
         const int q = (warp - 4) & 3, half = (warp - 4) >> 2;    // TMEM lanes 32 q .., columns 128 half ..
+        float *stage = p.stage_off ? reinterpret_cast<float *>(smem + p.stage_off) + (warp - 4) * T_STAGE_FLOATS : nullptr;
         int it = 0;
         uint32_t chunk = 0;
         for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
@@ -779,15 +809,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(acce0 + 8 * ab, 0));
             }
             if (!ok) break;
-            const int row = tm * P2_TILE_M + (int)rank * 128 + q * 32 + lane;
-            if (row < p.M) {
-                const int col0 = tn * NB + half * 128;
-                float *dst = p.C + (size_t)row * p.N + col0;
-#pragma unroll
-                for (int j = 0; j < TILE_N; j += 4)
-                    if (col0 + j < p.N)
-                        *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
-            }
+            store_row_block(acc, stage, p.C, tm * P2_TILE_M + (int)rank * 128 + q * 32, tn * NB + half * 128, p.M, p.N, lane);
         }
     }
 
@@ -987,8 +1009,13 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
         if (st) return st;
         const int stage_bytes = nb == 128 ? PairCfg<128>::STAGE_BYTES * PairCfg<128>::STAGES
                                           : PairCfg<256>::STAGE_BYTES * PairCfg<256>::STAGES;
-        const size_t smem = (size_t)stage_bytes + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 16;
+        size_t smem = (size_t)stage_bytes + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 16;
         if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
+        const size_t staging = (size_t)(nb == 128 ? PairCfg<128>::EPI_WARPS : PairCfg<256>::EPI_WARPS) * T_STAGE_FLOATS * 4;
+        if (smem + staging <= (size_t)SMEM_LIMIT && env_int("ESMM_TF32_DIRECT_STORES", 0) == 0) {
+            p.stage_off = (int)smem;                           // a multiple of 16
+            smem += staging;
+        }
         const int pairs = std::max(1, std::min(sms / 2, p.num_tiles));
         if (nb == 128) {
             esmm_joint_sgemm_tf32x3_pair_kernel<128><<<2 * pairs, PairCfg<128>::THREADS, smem, stream>>>(maps, p);
@@ -1006,8 +1033,12 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, sw, l2);
     if (st) return st;
 
-    const size_t smem = (size_t)T_STAGES * T_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 14 * 8 + 16;
+    size_t smem = (size_t)T_STAGES * T_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 14 * 8 + 16;
     if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
+    if (smem + 4 * T_STAGE_FLOATS * 4 <= (size_t)SMEM_LIMIT && env_int("ESMM_TF32_DIRECT_STORES", 0) == 0) {
+        p.stage_off = (int)smem;
+        smem += 4 * T_STAGE_FLOATS * 4;
+    }
     const int grid = std::min(sms, p.num_tiles);
     esmm_joint_sgemm_tf32x3_kernel<<<grid, T_THREADS, smem, stream>>>(maps, p);
     ESMM_CUDA_TRY(cudaGetLastError());
