@@ -668,21 +668,36 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                 const int g = g0 + lane;
                 unsigned live = 0;
                 if (g < nGroups) {
-                    unsigned au[T_GROUP_KB] = {0, 0, 0, 0}, bu[T_GROUP_KB] = {0, 0, 0, 0};
-#pragma unroll 1
-                    for (int i = 0; i < 8; ++i) {           // not unrolled: this warp runs on a small register budget
-                        const int mb = tm * 8 + i, nb = tn * (NB / 32) + i;
+                    if ((p.nKB & 3) == 0) {
+                        // the group's four pattern bytes of a row block are one aligned word: 8 + NB / 32 independent loads
+                        unsigned aw = 0, bw = 0;
 #pragma unroll
-                        for (int j = 0; j < T_GROUP_KB; ++j) {
-                            const int kb = g * T_GROUP_KB + j;
-                            if (kb < p.nKB) {
-                                if (mb < p.a_rows) au[j] |= p.a_pat[(size_t)mb * p.nKB + kb];
-                                if (i < NB / 32 && nb < p.b_rows) bu[j] |= p.b_pat[(size_t)nb * p.nKB + kb];
+                        for (int i = 0; i < 8; ++i) {
+                            const int mb = tm * 8 + i, nb = tn * (NB / 32) + i;
+                            if (mb < p.a_rows) aw |= __ldg(reinterpret_cast<const unsigned *>(p.a_pat + (size_t)mb * p.nKB) + g);
+                            if (i < NB / 32 && nb < p.b_rows)
+                                bw |= __ldg(reinterpret_cast<const unsigned *>(p.b_pat + (size_t)nb * p.nKB) + g);
+                        }
+                        const unsigned j = aw & bw;
+                        live = ((j & 0xFFu) ? 1u : 0u) | ((j & 0xFF00u) ? 2u : 0u) | ((j & 0xFF0000u) ? 4u : 0u) |
+                               ((j & 0xFF000000u) ? 8u : 0u);
+                    } else {
+                        unsigned au[T_GROUP_KB] = {0, 0, 0, 0}, bu[T_GROUP_KB] = {0, 0, 0, 0};
+#pragma unroll 1
+                        for (int i = 0; i < 8; ++i) {       // not unrolled: this warp runs on a small register budget
+                            const int mb = tm * 8 + i, nb = tn * (NB / 32) + i;
+#pragma unroll
+                            for (int j = 0; j < T_GROUP_KB; ++j) {
+                                const int kb = g * T_GROUP_KB + j;
+                                if (kb < p.nKB) {
+                                    if (mb < p.a_rows) au[j] |= p.a_pat[(size_t)mb * p.nKB + kb];
+                                    if (i < NB / 32 && nb < p.b_rows) bu[j] |= p.b_pat[(size_t)nb * p.nKB + kb];
+                                }
                             }
                         }
-                    }
 #pragma unroll
-                    for (int j = 0; j < T_GROUP_KB; ++j) live |= ((au[j] & bu[j]) != 0u ? 1u : 0u) << j;
+                        for (int j = 0; j < T_GROUP_KB; ++j) live |= ((au[j] & bu[j]) != 0u ? 1u : 0u) << j;
+                    }
                 }
                 const unsigned m = __ballot_sync(0xFFFFFFFFu, live != 0u);
                 if (live) list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
