@@ -44,10 +44,11 @@
 //     (more than the MMA); with one precomputed word per operand it is 57.  A wait on a data barrier costs about
 //     170 cycles even when the data is there, so the next group's barrier is polled while the pipe has work.
 //   * 256 x 256 on a CTA pair: 64 KB per group feed 12 MMAs of 128 x 256 x 8 per SM; measured 1588 cycles per
-//     group in steady state, the tensor pipe's own time.  Over a whole 4096^3 call ncu shows the pipe 71 % busy:
-//     256 tiles on 74 pairs are 3.46 rounds, and a tile change costs a few thousand cycles.  In a long loop the
-//     GPU then sits at its 1000 W power cap (SM clock 1.6-1.7 GHz, sw_power_cap the only reason active).
-// Whole call (split + A patterns + product), bursts of 20 calls: 0.58 ms dense against 2.35 ms for the FP32 kernel.
+//     group in steady state, the tensor pipe's own time.  256 tiles on 74 pairs are 3.46 rounds: the 34 tiles of
+//     the last round are computed as two halves of K by 68 pairs (they add into a zeroed C), 3.5 rounds instead of
+//     4.  In a long loop the GPU sits at its 1000 W power cap (SM clock 1.6-1.7 GHz, sw_power_cap the only reason).
+// Whole call (split of A with its patterns + product), bursts of 20 calls: 0.51 ms dense against 2.35 ms for the
+// FP32 kernel.
 #include <algorithm>
 #include <cstring>
 #include <vector>
@@ -67,6 +68,7 @@ constexpr int T_TMEM_COLS = 256;             // two accumulators of 128 columns
 struct Tf32Params {
     int M, N, K, nKB, cap;
     int stage_off;                           // byte offset of the epilogue's staging squares in shared memory, 0: none
+    int num_items, split_first;              // pair kernels: work items; tiles >= split_first are two items (halves of K)
     int a_rows, b_rows, tiles_m, tiles_n, num_tiles;
     const uint8_t *a_pat;
     const uint8_t *b_pat;
@@ -279,16 +281,24 @@ __global__ void esmm_tf32_split_transpose_kernel(const float *__restrict__ B, in
 // of cycles at every tile change.  Through a 32 x 33 float staging square per warp, every store instruction writes
 // one full 128-byte line of one row instead.  stage == nullptr (no shared memory left for it): the direct form.
 constexpr int T_STAGE_FLOATS = 32 * 33;
+// add: the tile is computed as two halves of K by two CTA pairs; C was zeroed, both add their sums (two terms: the
+// result does not depend on who comes first).
 __device__ __forceinline__ void store_row_block(const float (&acc)[TILE_N], float *stage, float *C, int row0, int col0,
-                                                int M, int N, int lane)
+                                                int M, int N, int lane, bool add = false)
 {
     if (stage == nullptr) {
         const int row = row0 + lane;
         if (row < M) {
             float *dst = C + (size_t)row * N + col0;
+            if (add) {
 #pragma unroll
-            for (int j = 0; j < TILE_N; j += 4)
-                if (col0 + j < N) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+                for (int j = 0; j < TILE_N; ++j)     // fully unrolled: acc must stay in registers
+                    if (col0 + j < N) atomicAdd(dst + j, acc[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < TILE_N; j += 4)
+                    if (col0 + j < N) *reinterpret_cast<float4 *>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+            }
         }
         return;
     }
@@ -301,8 +311,13 @@ __device__ __forceinline__ void store_row_block(const float (&acc)[TILE_N], floa
         if (col < N) {
             float *dst = C + (size_t)row0 * N + col;
             const int rows = min(32, M - row0);
+            if (add) {
 #pragma unroll 8
-            for (int r = 0; r < rows; ++r) dst[(size_t)r * N] = stage[r * 33 + lane];
+                for (int r = 0; r < rows; ++r) atomicAdd(dst + (size_t)r * N, stage[r * 33 + lane]);
+            } else {
+#pragma unroll 8
+                for (int r = 0; r < rows; ++r) dst[(size_t)r * N] = stage[r * 33 + lane];
+            }
         }
         __syncwarp();
     }
@@ -599,6 +614,41 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar)
                  : "memory");
 }
 
+struct PairItem {
+    int tile, half;
+    bool split;
+};
+
+// Work items of the pair kernels: whole tiles first, then the tiles of the last, partly filled round as two items each
+// (halves of the tile's live groups), so that the round costs half a tile instead of a whole one.
+__device__ __forceinline__ PairItem pair_item(const Tf32Params &p, int item)
+{
+    PairItem w;
+    if (item < p.split_first) {
+        w.tile = item;
+        w.half = 0;
+        w.split = false;
+    } else {
+        w.tile = p.split_first + ((item - p.split_first) >> 1);
+        w.half = (item - p.split_first) & 1;
+        w.split = true;
+    }
+    return w;
+}
+
+// zeroes the C tiles that are computed as two halves (tiles >= split_first): one block per tile and 32-row band
+template <int NB>
+__global__ void esmm_tf32_zero_split_tiles_kernel(const Tf32Params p)
+{
+    int tm, tn;
+    tile_coords(p.split_first + (int)blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
+    const int row0 = tm * 256 + (int)blockIdx.y * 32, col0 = tn * NB;
+    for (int i = threadIdx.x; i < 32 * (NB / 4); i += blockDim.x) {
+        const int row = row0 + i / (NB / 4), col = col0 + (i % (NB / 4)) * 4;
+        if (row < p.M && col < p.N) *reinterpret_cast<float4 *>(p.C + (size_t)row * p.N + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
 template <int NB>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<NB>::THREADS, 1)
 esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, const Tf32Params p)
@@ -615,6 +665,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
     volatile int *nlive = reinterpret_cast<volatile int *>(bars + 16);
     volatile int *abort_flag = nlive + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(const_cast<int *>(nlive + 3));
+    volatile int *noff = nlive + 4;              // [2]: where the item's part of the listed tile's groups starts
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
@@ -656,7 +707,9 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
     if (warp == 2) {
         // ---------------- mask warp: live groups of the pair's tile (8 row blocks of A, 4 column blocks of B) ----------------
         int it = 0;
-        for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+        for (int item = pair; item < p.num_items && ok; item += num_pairs, ++it) {
+            const PairItem w = pair_item(p, item);
+            const int tile = w.tile;
             const int buf = it & 1;
             ok = mbar_wait(lempty0 + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag);
             if (!ok) break;
@@ -703,7 +756,12 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                 if (live) list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
                 pos += __popc(m);
             }
-            if (lane == 0) nlive[buf] = pos;
+            if (lane == 0) {
+                // a split tile: this item multiplies the first or the second half of the tile's live groups
+                const int lo = w.split && w.half ? pos / 2 : 0, hi = w.split && !w.half ? pos / 2 : pos;
+                noff[buf] = lo;
+                nlive[buf] = hi - lo;
+            }
             __syncwarp();
             if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
         }
@@ -712,13 +770,15 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
         if (lane < 4) tma_prefetch_descriptor(&maps.a_hi + lane);
         int slot = 0, it = 0;
         uint32_t phase = 0;
-        for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+        for (int item = pair; item < p.num_items && ok; item += num_pairs, ++it) {
+            const PairItem w = pair_item(p, item);
+            const int tile = w.tile;
             const int buf = it & 1;
             ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
             if (!ok) break;
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
-            const uint16_t *list = lists + buf * list_stride;
+            const uint16_t *list = lists + buf * list_stride + noff[buf];
             const int n = nlive[buf];
             const int row0 = (lane & 2) ? tn * NB + (int)rank * (NB / 2) : tm * P2_TILE_M + (int)rank * 128;
             const uint32_t part_off = lane == 0 ? 0u : lane == 1 ? (uint32_t)P2_A_PART
@@ -752,11 +812,11 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
             uint32_t phase = 0, chunk = 0;
             bool landed = false;                         // the next group's copies were seen complete by a poll
             const uint32_t ring_lo = umma_desc_lo(smem_u32(smem));
-            for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+            for (int item = pair; item < p.num_items && ok; item += num_pairs, ++it) {
                 const int buf = it & 1;
                 ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
                 if (!ok) break;
-                const uint16_t *list = lists + buf * list_stride;
+                const uint16_t *list = lists + buf * list_stride + noff[buf];
                 const int n = nlive[buf];
                 for (int c0 = 0; c0 < n && ok; c0 += T_CHUNK, ++chunk) {
                     const uint32_t ab = chunk & 1u;
@@ -795,7 +855,9 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
         float *stage = p.stage_off ? reinterpret_cast<float *>(smem + p.stage_off) + (warp - 4) * T_STAGE_FLOATS : nullptr;
         int it = 0;
         uint32_t chunk = 0;
-        for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs, ++it) {
+        for (int item = pair; item < p.num_items && ok; item += num_pairs, ++it) {
+            const PairItem w = pair_item(p, item);
+            const int tile = w.tile;
             const int buf = it & 1;
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
@@ -824,7 +886,9 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                 if (lane == 0) mbar_arrive_cluster(map_to_cta(acce0 + 8 * ab, 0));
             }
             if (!ok) break;
-            store_row_block(acc, stage, p.C, tm * P2_TILE_M + (int)rank * 128 + q * 32, tn * NB + half * 128, p.M, p.N, lane);
+            if (!(w.split && n == 0))     // a split tile's C was zeroed beforehand: nothing to add is nothing to do
+                store_row_block(acc, stage, p.C, tm * P2_TILE_M + (int)rank * 128 + q * 32, tn * NB + half * 128, p.M, p.N,
+                                lane, w.split);
         }
     }
 
@@ -1024,7 +1088,7 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
         if (st) return st;
         const int stage_bytes = nb == 128 ? PairCfg<128>::STAGE_BYTES * PairCfg<128>::STAGES
                                           : PairCfg<256>::STAGE_BYTES * PairCfg<256>::STAGES;
-        size_t smem = (size_t)stage_bytes + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 16;
+        size_t smem = (size_t)stage_bytes + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 32;
         if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
         const size_t staging = (size_t)(nb == 128 ? PairCfg<128>::EPI_WARPS : PairCfg<256>::EPI_WARPS) * T_STAGE_FLOATS * 4;
         if (smem + staging <= (size_t)SMEM_LIMIT && env_int("ESMM_TF32_DIRECT_STORES", 0) == 0) {
@@ -1032,6 +1096,22 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
             smem += staging;
         }
         const int pairs = std::max(1, std::min(sms / 2, p.num_tiles));
+        // The last round: `left` tiles for `pairs` pairs.  Where two halves per tile still fit in one round and the
+        // tiles are long enough for half a tile to outweigh the zeroing pass, those tiles are split along K.
+        p.num_items = p.num_tiles;
+        p.split_first = p.num_tiles;
+        const int left = p.num_tiles % pairs;
+        if (left > 0 && p.num_tiles > pairs && 2 * left <= pairs && ceil_div(nKB, T_GROUP_KB) >= 24 &&
+            env_int("ESMM_TF32_SPLIT_LAST", 1) != 0) {
+            p.split_first = p.num_tiles - left;
+            p.num_items = p.num_tiles + left;
+            dim3 zgrid((unsigned)left, 8);
+            if (nb == 128)
+                esmm_tf32_zero_split_tiles_kernel<128><<<zgrid, 256, 0, stream>>>(p);
+            else
+                esmm_tf32_zero_split_tiles_kernel<256><<<zgrid, 256, 0, stream>>>(p);
+            ESMM_CUDA_TRY(cudaGetLastError());
+        }
         if (nb == 128) {
             esmm_joint_sgemm_tf32x3_pair_kernel<128><<<2 * pairs, PairCfg<128>::THREADS, smem, stream>>>(maps, p);
         } else {

@@ -159,6 +159,32 @@ def test_full_size_agrees_with_fp32_path(cuda, pkg):
     assert rel_inf(c, ref.cpu().numpy()) <= TIGHT
 
 
+@pytest.mark.parametrize("pair", ["256", "128"])
+def test_last_round_split_along_k(cuda, pkg, monkeypatch, pair):
+    """Shapes whose tiles leave a partly filled last round: those tiles are computed as two halves of K by two CTA
+    pairs that add into a zeroed C.  Same result as without the split to rounding, the same bits on every call,
+    and stale contents of C do not leak in."""
+    torch = cuda
+    monkeypatch.setenv("ESMM_TF32_PAIR", pair)
+    M, N, K = (2560, 2560, 2048) if pair == "256" else (2560, 1280, 2048)     # 100 tiles for 74 pairs: 26 are split
+    A, B = workloads.tile_random(M, N, K, 0.6, 0.6, seed=12, gran_a=32, gran_b=32)
+    A[:, 1024:1536] = 0.0                                                     # dead groups in the middle of K
+    dA, dB = torch.from_numpy(A).cuda(), torch.from_numpy(B).cuda()
+    bp = torch.empty((N // 32, K // 8), dtype=torch.uint8, device="cuda")
+    pkg.preprocess_b(dB.data_ptr(), K, N, bp.data_ptr())
+    ws = torch.empty(pkg.sgemm_joint_workspace_bytes(M, K), dtype=torch.uint8, device="cuda")
+    ref = torch.empty((M, N), device="cuda")
+    pkg.sgemm_joint(M, N, K, dA.data_ptr(), dB.data_ptr(), ref.data_ptr(), bp.data_ptr(), ws.data_ptr())
+    pkg.device_status()
+    ref = ref.cpu().numpy()
+    (c1, c2), _ = run_tf32x3(torch, pkg, A, B, calls=2)                        # C starts as NaN in both calls
+    assert np.array_equal(c1, c2)
+    assert rel_inf(c1, ref) <= TIGHT
+    monkeypatch.setenv("ESMM_TF32_SPLIT_LAST", "0")
+    c3, _ = run_tf32x3(torch, pkg, A, B)
+    assert rel_inf(c3, ref) <= TIGHT and rel_inf(c1, c3) <= TIGHT
+
+
 def test_argument_checks(cuda, pkg):
     import ctypes as C
     torch = cuda
