@@ -29,12 +29,13 @@
 // producer warp fetches one group per ring stage, one thread issues the MMAs and commits them to the ring's and
 // the accumulator's mbarriers, epilogue warps drain one of two TMEM accumulators while the other is being filled.
 // Every wait is bounded, as in the other kernels, and the tensor memory is freed on every path out.
-//   esmm_joint_sgemm_tf32x3_pair_kernel<256>  default where M >= 192 and N >= 192.  Two CTAs of a cluster share a
+//   esmm_joint_sgemm_tf32x3_pair_kernel<256>  large problems (the host picks the kernel by an estimate of the time per
+//       SM: see esmm_sgemm_joint_tf32x3; ESMM_TF32_PAIR = 0 | 128 | 256 overrides).  Two CTAs of a cluster share a
 //       256 x 256 tile (cta_group::2 MMAs, M 256, N 256): each CTA fetches its 128 rows of A and its 128 columns of
 //       B, 16 KB per K block for two 128 x 128 tiles' worth of MMA work.  12 warps; the eight epilogue warps take
 //       registers over from the other four (setmaxnreg) for their 128-column rows of run sums.
-//   esmm_joint_sgemm_tf32x3_pair_kernel<128>  ESMM_TF32_PAIR=128 (and N < 192): 256 x 128 per pair.
-//   esmm_joint_sgemm_tf32x3_kernel            M < 192, or ESMM_TF32_PAIR=0: one CTA per 128 x 128 tile.
+//   esmm_joint_sgemm_tf32x3_pair_kernel<128>  256 x 128 per pair: problems with too few 256 x 256 tiles to fill the GPU.
+//   esmm_joint_sgemm_tf32x3_kernel            one CTA per 128 x 128 tile: M < 192, and where it fills its rounds best.
 //
 // What was measured on the way (one B200, 4096^3 dense, cycles per group of four K blocks on one SM):
 //   * 128 x 128 tiles need 64 KB per group and the SM takes in about 64 bytes per clock from L2: 1024 cycles, more
@@ -1072,10 +1073,31 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
         opted[dev] = 1;
     }
 
-    // CTA pairs (256-row tiles) where the problem has the rows and columns for them: 256 x 256 per pair by default,
-    // ESMM_TF32_PAIR=128 for 256 x 128 per pair, =0 for the single-CTA kernel everywhere
-    const int pair_env = env_int("ESMM_TF32_PAIR", 256);
-    const int nb = (M < 192 || pair_env == 0) ? 0 : (pair_env == 128 || N < 192) ? 128 : 256;
+    // Which kernel: the one with the smallest estimated time per SM, in units of one 128 x 128 tile's tensor time.
+    // A 256 x 256 tile is two units per SM at the tensor rate; a 256 x 128 tile one unit at 1.19 and a 128 x 128 tile
+    // on one CTA one unit at 1.24 (measured at 3072^3, where all three fill their rounds alike); a pair kernel's
+    // partly filled last round counts half when its tiles can be split along K.  Small problems therefore take the
+    // smaller tiles (1024^2 x 4096: 97 us on 256 x 128 pairs, 105 us on single CTAs, 137 us on 256 x 256 pairs), large
+    // ones the 256 x 256 pairs.  ESMM_TF32_PAIR = 0 | 128 | 256 overrides the choice.
+    const int pair_env = env_int("ESMM_TF32_PAIR", -1);
+    int nb = 0;
+    {
+        const int pairs_all = std::max(1, sms / 2), groups = ceil_div(nKB, T_GROUP_KB);
+        const bool can_split = groups >= 24 && env_int("ESMM_TF32_SPLIT_LAST", 1) != 0;
+        auto pair_rounds = [&](int tiles) {
+            const int full = tiles / pairs_all, left = tiles % pairs_all;
+            if (!left) return (double)full;
+            return full + ((full > 0 && 2 * left <= pairs_all && can_split) ? 0.5 : 1.0);
+        };
+        const double c1 = 1.24 * ceil_div(ceil_div(M, TILE_M) * ceil_div(N, TILE_N), sms);
+        const double c128 = 1.19 * pair_rounds(ceil_div(M, P2_TILE_M) * ceil_div(N, 128));
+        const double c256 = 2.0 * pair_rounds(ceil_div(M, P2_TILE_M) * ceil_div(N, 256));
+        if (M >= 192) {
+            nb = (N >= 192 && c256 <= c128 && c256 <= c1) ? 256 : (c128 <= c1 ? 128 : 0);
+            if (pair_env == 0 || pair_env == 128 || (pair_env == 256 && N >= 192)) nb = pair_env;
+            if (pair_env == 256 && N < 192) nb = 128;
+        }
+    }
     if (nb) {
         p.tiles_m = ceil_div(M, P2_TILE_M);
         p.tiles_n = ceil_div(N, nb);

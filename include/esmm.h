@@ -232,9 +232,9 @@ int esmm_ffma_peak_tflops(double *tflops, int *sm_count);
  * are FP32 FMA only.  Every operand is split as x = hi + lo (both TF32) and a product is formed as
  * a_hi b_hi + a_hi b_lo + a_lo b_hi; the tensor core accumulates runs of 256 k in FP32, the runs are added in
  * registers.  C agrees with esmm_gemm_ab to a few 1e-6 of max |C| (inside the 1e-4 bound the FP32 path is
- * held to) but is NOT bit-identical to it.  Requires K % 8 == 0, N % 4 == 0, finite inputs.  Tiles of 256 x 256
- * run on pairs of CTAs (cta_group::2) where M and N are at least 192 (environment ESMM_TF32_PAIR=0 | 128 | 256
- * forces the single-CTA kernel, 256 x 128 or 256 x 256 per pair).
+ * held to) but is NOT bit-identical to it.  Requires K % 8 == 0, N % 4 == 0, finite inputs.  Tiles of 256 x 256 or
+ * 256 x 128 run on pairs of CTAs (cta_group::2), tiles of 128 x 128 on one CTA; the library picks by the number of
+ * tiles (environment ESMM_TF32_PAIR=0 | 128 | 256 forces the single-CTA kernel, 256 x 128 or 256 x 256 per pair).
  * Work is skipped at two levels: k with an all-zero row of B are dropped from both operands when B is prepared
  * (compact != 0), and of what is left a tile multiplies only the 8-wide K blocks in which its A and
  * B patterns share a live k.
