@@ -506,6 +506,15 @@ def run_ours(args) -> None:
             "ffma_peak_tflops_measured": ffma_peak, "hbm_peak_gbs": hbm_peak, "hbm_peak_source": hbm_src,
             "sm_count": sms, "gather_c": gather, "scaling_base": scaling_base,
         }
+        # the optional 3xTF32 tensor-core entry point on the same inputs, as one step of the same cases: not `value`
+        # (its results are inside the 1e-4 tolerance but not the FP32 path's bits), rank 0's shard at N > 1
+        tf_ms = sum(v["tf32x3"]["ms_total"] for v in sweep.values())
+        line["tensor_core_variant"] = {
+            "entry": "esmm_sgemm_joint_tf32x3", "ms_per_step_this_rank": tf_ms,
+            "dense_equiv_tflops_this_rank": len(cases) * flops_dense_local / (tf_ms * 1e-3) / 1e12,
+            "speedup_vs_fp32_path": sum(v["ms_total"] for v in sweep.values()) / tf_ms,
+            "max_rel_inf_vs_fp32_path": max(v["tf32x3"]["rel_inf_vs_fp32_path"] for v in sweep.values()),
+        }
         print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
