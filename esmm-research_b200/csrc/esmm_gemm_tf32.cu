@@ -205,10 +205,32 @@ __device__ __forceinline__ void split_tf32(float x, float &hi, float &lo)
 // contributes nothing, so the pattern bit of (32-row block, k) is "some hi part is nonzero": the byte layout is the
 // one of esmm_preprocess_a (src/preprocessors/ab_preprocessor.cu:122-187), a_pat[mb * (Kc / 8) + kb], bit k.
 // One warp per 32 rows x 64 output columns: half-warp h takes the rows of parity h, lane c its float4 column.
+// Rows of blocks past the last 32-row block of A zero the C tiles that the product kernel computes as two halves
+// (ZeroJob; count 0: none): the pass is in the stream anyway and a launch of its own would cost more than the work.
+struct ZeroJob {
+    float *C;
+    int N, tiles_m, tiles_n, nb, first, count;    // nb: tile width; tiles first .. first + count - 1, 256 rows each
+};
+
 __global__ void __launch_bounds__(256)
 esmm_tf32_split_pattern_kernel(const float *__restrict__ A, int M, int K, const int *__restrict__ klist, int Kc,
-                               float *__restrict__ hi, float *__restrict__ lo, uint8_t *__restrict__ a_pat)
+                               float *__restrict__ hi, float *__restrict__ lo, uint8_t *__restrict__ a_pat,
+                               const ZeroJob zj)
 {
+    const int a_blocks = (M + 31) >> 5;
+    if ((int)blockIdx.y >= a_blocks) {
+        if (blockIdx.x != 0) return;
+        const int z = (int)blockIdx.y - a_blocks;                 // (tile, 32-row band)
+        int tm, tn;
+        tile_coords(zj.first + (z >> 3), zj.tiles_m, zj.tiles_n, tm, tn);
+        const int row0 = tm * 256 + (z & 7) * 32, col0 = tn * zj.nb, q = zj.nb >> 2;
+        for (int i = threadIdx.x; i < 32 * q; i += blockDim.x) {
+            const int row = row0 + i / q, col = col0 + (i % q) * 4;
+            if (row < M && col < zj.N)
+                *reinterpret_cast<float4 *>(zj.C + (size_t)row * zj.N + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+        return;
+    }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int mb = blockIdx.y, col = (blockIdx.x * 8 + warp) * 64 + (lane & 15) * 4, h = lane >> 4;
     if ((blockIdx.x * 8 + warp) * 64 >= Kc) return;               // the whole warp is past the last column
@@ -621,7 +643,8 @@ struct PairItem {
 };
 
 // Work items of the pair kernels: whole tiles first, then the tiles of the last, partly filled round as two items each
-// (halves of the tile's live groups), so that the round costs half a tile instead of a whole one.
+// (halves of the tile's live groups), so that the round costs half a tile instead of a whole one.  Their part of C
+// is zeroed by the split pass (ZeroJob) and both items add their sums.
 __device__ __forceinline__ PairItem pair_item(const Tf32Params &p, int item)
 {
     PairItem w;
@@ -635,19 +658,6 @@ __device__ __forceinline__ PairItem pair_item(const Tf32Params &p, int item)
         w.split = true;
     }
     return w;
-}
-
-// zeroes the C tiles that are computed as two halves (tiles >= split_first): one block per tile and 32-row band
-template <int NB>
-__global__ void esmm_tf32_zero_split_tiles_kernel(const Tf32Params p)
-{
-    int tm, tn;
-    tile_coords(p.split_first + (int)blockIdx.x, p.tiles_m, p.tiles_n, tm, tn);
-    const int row0 = tm * 256 + (int)blockIdx.y * 32, col0 = tn * NB;
-    for (int i = threadIdx.x; i < 32 * (NB / 4); i += blockDim.x) {
-        const int row = row0 + i / (NB / 4), col = col0 + (i % (NB / 4)) * 4;
-        if (row < p.M && col < p.N) *reinterpret_cast<float4 *>(p.C + (size_t)row * p.N + col) = make_float4(0.f, 0.f, 0.f, 0.f);
-    }
 }
 
 template <int NB>
@@ -1017,42 +1027,9 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     if (M <= 0) return ESMM_ERR_SHAPE;
     if (((uintptr_t)d_A | (uintptr_t)d_C) & 15) return ESMM_ERR_ALIGN;
     if (((uintptr_t)d_workspace) & 255) return ESMM_ERR_ALIGN;
-    const int nKB = Kc / BK;
-    if (ceil_div(nKB, T_GROUP_KB) > 4095) return ESMM_ERR_TOO_LARGE;   // 12-bit group index in the list entries
+    const int nKB = Kc / BK, groups = ceil_div(nKB, T_GROUP_KB);
+    if (groups > 4095) return ESMM_ERR_TOO_LARGE;   // 12-bit group index in the list entries
 
-    // workspace (sized for the uncompacted K): A patterns | A_hi | A_lo, all of the kept columns only
-    uint8_t *a_pat = static_cast<uint8_t *>(d_workspace);
-    float *a_hi = reinterpret_cast<float *>(a_pat + ((esmm_a_pattern_bytes(M, K, 32) + 255) & ~(size_t)255));
-    float *a_lo = a_hi + (size_t)M * Kc;
-    {
-        dim3 grid((unsigned)ceil_div(Kc, 512), (unsigned)ceil_div(M, 32));
-        esmm_tf32_split_pattern_kernel<<<grid, 256, 0, stream>>>(d_A, M, K, b->d_klist, Kc, a_hi, a_lo, a_pat);
-        ESMM_CUDA_TRY(cudaGetLastError());
-    }
-    int st = ESMM_OK;
-
-    Tf32Params p;
-    memset(&p, 0, sizeof p);
-    p.M = M;
-    p.N = N;
-    p.K = Kc;
-    p.nKB = nKB;
-    p.cap = ceil_div(nKB, T_GROUP_KB) + 32;
-    p.a_rows = ceil_div(M, 32);
-    p.b_rows = ceil_div(N, PAT_N);
-    p.tiles_m = ceil_div(M, TILE_M);
-    p.tiles_n = ceil_div(N, TILE_N);
-    p.num_tiles = p.tiles_m * p.tiles_n;
-    p.a_pat = a_pat;
-    p.b_pat = b->d_b_pat;
-    p.C = d_C;
-    p.status = device_status_ptr();
-    if (!p.status) return ESMM_ERR_CUDA;
-
-    const float *bt_hi = b->d_bt, *bt_lo = b->d_bt + (size_t)N * Kc;
-    const CUtensorMapL2promotion l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
-    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
-    const uint32_t box_k = T_GROUP_KB * BK;
     int dev = 0;
     ESMM_CUDA_TRY(cudaGetDevice(&dev));
     if (dev != b->device) return record_cuda_error_text("esmm_sgemm_joint_tf32x3: B was prepared on another device");
@@ -1080,10 +1057,10 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     // smaller tiles (1024^2 x 4096: 97 us on 256 x 128 pairs, 105 us on single CTAs, 137 us on 256 x 256 pairs), large
     // ones the 256 x 256 pairs.  ESMM_TF32_PAIR = 0 | 128 | 256 overrides the choice.
     const int pair_env = env_int("ESMM_TF32_PAIR", -1);
+    const int pairs_all = std::max(1, sms / 2);
+    const bool can_split = groups >= 12 && env_int("ESMM_TF32_SPLIT_LAST", 1) != 0;
     int nb = 0;
     {
-        const int pairs_all = std::max(1, sms / 2), groups = ceil_div(nKB, T_GROUP_KB);
-        const bool can_split = groups >= 24 && env_int("ESMM_TF32_SPLIT_LAST", 1) != 0;
         auto pair_rounds = [&](int tiles) {
             const int full = tiles / pairs_all, left = tiles % pairs_all;
             if (!left) return (double)full;
@@ -1099,66 +1076,99 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
             if (pair_env == 256 && N < 192) nb = 128;
         }
     }
+
+    // workspace (sized for the uncompacted K): A patterns | A_hi | A_lo, all of the kept columns only
+    uint8_t *a_pat = static_cast<uint8_t *>(d_workspace);
+    float *a_hi = reinterpret_cast<float *>(a_pat + ((esmm_a_pattern_bytes(M, K, 32) + 255) & ~(size_t)255));
+    float *a_lo = a_hi + (size_t)M * Kc;
+
+    Tf32Params p;
+    memset(&p, 0, sizeof p);
+    p.M = M;
+    p.N = N;
+    p.K = Kc;
+    p.nKB = nKB;
+    p.cap = groups + 32;
+    p.a_rows = ceil_div(M, 32);
+    p.b_rows = ceil_div(N, PAT_N);
+    p.tiles_m = ceil_div(M, nb ? P2_TILE_M : TILE_M);
+    p.tiles_n = ceil_div(N, nb ? nb : TILE_N);
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.num_items = p.num_tiles;
+    p.split_first = p.num_tiles;
+    p.a_pat = a_pat;
+    p.b_pat = b->d_b_pat;
+    p.C = d_C;
+    p.status = device_status_ptr();
+    if (!p.status) return ESMM_ERR_CUDA;
+
+    // The last round of a pair kernel: `left` tiles for `pairs` pairs.  Where two halves per tile still fit into one
+    // round, those tiles are split along K (their part of C is zeroed by the split pass below).
+    const int pairs = std::max(1, std::min(pairs_all, p.num_tiles));
+    ZeroJob zj;
+    memset(&zj, 0, sizeof zj);
     if (nb) {
-        p.tiles_m = ceil_div(M, P2_TILE_M);
-        p.tiles_n = ceil_div(N, nb);
-        p.num_tiles = p.tiles_m * p.tiles_n;
-        Tf32PairMaps maps;
-        st = make_map_2d(&maps.a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
-        if (!st) st = make_map_2d(&maps.a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
-        if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, nb / 2, sw, l2);
-        if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, nb / 2, sw, l2);
-        if (st) return st;
-        const int stage_bytes = nb == 128 ? PairCfg<128>::STAGE_BYTES * PairCfg<128>::STAGES
-                                          : PairCfg<256>::STAGE_BYTES * PairCfg<256>::STAGES;
-        size_t smem = (size_t)stage_bytes + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 32;
-        if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
-        const size_t staging = (size_t)(nb == 128 ? PairCfg<128>::EPI_WARPS : PairCfg<256>::EPI_WARPS) * T_STAGE_FLOATS * 4;
-        if (smem + staging <= (size_t)SMEM_LIMIT && env_int("ESMM_TF32_DIRECT_STORES", 0) == 0) {
-            p.stage_off = (int)smem;                           // a multiple of 16
-            smem += staging;
-        }
-        const int pairs = std::max(1, std::min(sms / 2, p.num_tiles));
-        // The last round: `left` tiles for `pairs` pairs.  Where two halves per tile still fit in one round and the
-        // tiles are long enough for half a tile to outweigh the zeroing pass, those tiles are split along K.
-        p.num_items = p.num_tiles;
-        p.split_first = p.num_tiles;
         const int left = p.num_tiles % pairs;
-        if (left > 0 && p.num_tiles > pairs && 2 * left <= pairs && ceil_div(nKB, T_GROUP_KB) >= 24 &&
-            env_int("ESMM_TF32_SPLIT_LAST", 1) != 0) {
+        if (left > 0 && p.num_tiles > pairs && 2 * left <= pairs && can_split) {
             p.split_first = p.num_tiles - left;
             p.num_items = p.num_tiles + left;
-            dim3 zgrid((unsigned)left, 8);
-            if (nb == 128)
-                esmm_tf32_zero_split_tiles_kernel<128><<<zgrid, 256, 0, stream>>>(p);
-            else
-                esmm_tf32_zero_split_tiles_kernel<256><<<zgrid, 256, 0, stream>>>(p);
-            ESMM_CUDA_TRY(cudaGetLastError());
+            zj.C = d_C;
+            zj.N = N;
+            zj.tiles_m = p.tiles_m;
+            zj.tiles_n = p.tiles_n;
+            zj.nb = nb;
+            zj.first = p.split_first;
+            zj.count = left;
         }
-        if (nb == 128) {
-            esmm_joint_sgemm_tf32x3_pair_kernel<128><<<2 * pairs, PairCfg<128>::THREADS, smem, stream>>>(maps, p);
-        } else {
-            esmm_joint_sgemm_tf32x3_pair_kernel<256><<<2 * pairs, PairCfg<256>::THREADS, smem, stream>>>(maps, p);
-        }
-        ESMM_CUDA_TRY(cudaGetLastError());
-        return ESMM_OK;
     }
 
-    Tf32Maps maps;
-    st = make_map_2d(&maps.a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, sw, l2);
-    if (!st) st = make_map_2d(&maps.a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, TILE_M, sw, l2);
-    if (!st) st = make_map_2d(&maps.b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, sw, l2);
-    if (!st) st = make_map_2d(&maps.b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, TILE_N, sw, l2);
+    // shared memory of the product kernel, checked before anything is launched
+    const size_t ring = nb == 128   ? (size_t)PairCfg<128>::STAGE_BYTES * PairCfg<128>::STAGES
+                        : nb == 256 ? (size_t)PairCfg<256>::STAGE_BYTES * PairCfg<256>::STAGES
+                                    : (size_t)T_STAGES * T_STAGE_BYTES;
+    const int epi_warps = nb == 256 ? PairCfg<256>::EPI_WARPS : 4;
+    size_t smem = ring + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 32;
+    if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
+    const size_t staging = (size_t)epi_warps * T_STAGE_FLOATS * 4;
+    if (smem + staging <= (size_t)SMEM_LIMIT && env_int("ESMM_TF32_DIRECT_STORES", 0) == 0) {
+        p.stage_off = (int)smem;                               // a multiple of 16
+        smem += staging;
+    }
+
+    const float *bt_hi = b->d_bt, *bt_lo = b->d_bt + (size_t)N * Kc;
+    const CUtensorMapL2promotion l2 = CU_TENSOR_MAP_L2_PROMOTION_L2_128B;
+    const CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_128B;
+    const uint32_t box_k = T_GROUP_KB * BK, b_rows_box = nb ? nb / 2 : TILE_N;
+    CUtensorMap m_a_hi, m_a_lo, m_b_hi, m_b_lo;
+    int st = make_map_2d(&m_a_hi, a_hi, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
+    if (!st) st = make_map_2d(&m_a_lo, a_lo, (uint64_t)Kc, (uint64_t)M, box_k, 128, sw, l2);
+    if (!st) st = make_map_2d(&m_b_hi, bt_hi, (uint64_t)Kc, (uint64_t)N, box_k, b_rows_box, sw, l2);
+    if (!st) st = make_map_2d(&m_b_lo, bt_lo, (uint64_t)Kc, (uint64_t)N, box_k, b_rows_box, sw, l2);
     if (st) return st;
 
-    size_t smem = (size_t)T_STAGES * T_STAGE_BYTES + 2 * ((p.cap * 2 + 15) & ~15) + 14 * 8 + 16;
-    if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
-    if (smem + 4 * T_STAGE_FLOATS * 4 <= (size_t)SMEM_LIMIT && env_int("ESMM_TF32_DIRECT_STORES", 0) == 0) {
-        p.stage_off = (int)smem;
-        smem += 4 * T_STAGE_FLOATS * 4;
+    {
+        dim3 grid((unsigned)ceil_div(Kc, 512), (unsigned)(ceil_div(M, 32) + 8 * zj.count));
+        esmm_tf32_split_pattern_kernel<<<grid, 256, 0, stream>>>(d_A, M, K, b->d_klist, Kc, a_hi, a_lo, a_pat, zj);
+        ESMM_CUDA_TRY(cudaGetLastError());
     }
-    const int grid = std::min(sms, p.num_tiles);
-    esmm_joint_sgemm_tf32x3_kernel<<<grid, T_THREADS, smem, stream>>>(maps, p);
+    if (nb) {
+        Tf32PairMaps maps;
+        maps.a_hi = m_a_hi;
+        maps.a_lo = m_a_lo;
+        maps.b_hi = m_b_hi;
+        maps.b_lo = m_b_lo;
+        if (nb == 128)
+            esmm_joint_sgemm_tf32x3_pair_kernel<128><<<2 * pairs, PairCfg<128>::THREADS, smem, stream>>>(maps, p);
+        else
+            esmm_joint_sgemm_tf32x3_pair_kernel<256><<<2 * pairs, PairCfg<256>::THREADS, smem, stream>>>(maps, p);
+    } else {
+        Tf32Maps maps;
+        maps.a_hi = m_a_hi;
+        maps.a_lo = m_a_lo;
+        maps.b_hi = m_b_hi;
+        maps.b_lo = m_b_lo;
+        esmm_joint_sgemm_tf32x3_kernel<<<std::min(sms, p.num_tiles), T_THREADS, smem, stream>>>(maps, p);
+    }
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;
 }
