@@ -35,7 +35,7 @@
 //       B, 16 KB per K block for two 128 x 128 tiles' worth of MMA work.  12 warps; the eight epilogue warps take
 //       registers over from the other four (setmaxnreg) for their 128-column rows of run sums.
 //   esmm_joint_sgemm_tf32x3_pair_kernel<128>  256 x 128 per pair: problems with too few 256 x 256 tiles to fill the GPU.
-//   esmm_joint_sgemm_tf32x3_kernel            one CTA per 128 x 128 tile: M < 192, and where it fills its rounds best.
+//   esmm_joint_sgemm_tf32x3_kernel            one CTA per 128 x 128 tile: M < 192, and where it fills its waves best.
 //
 // What was measured on the way (one B200, 4096^3 dense, cycles per group of four K blocks on one SM):
 //   * 128 x 128 tiles need 64 KB per group and the SM takes in about 64 bytes per clock from L2: 1024 cycles, more
@@ -45,8 +45,8 @@
 //     (more than the MMA); with one precomputed word per operand it is 57.  A wait on a data barrier costs about
 //     170 cycles even when the data is there, so the next group's barrier is polled while the pipe has work.
 //   * 256 x 256 on a CTA pair: 64 KB per group feed 12 MMAs of 128 x 256 x 8 per SM; measured 1588 cycles per
-//     group in steady state, the tensor pipe's own time.  256 tiles on 74 pairs are 3.46 rounds: the 34 tiles of
-//     the last round are computed as two halves of K by 68 pairs (they add into a zeroed C), 3.5 rounds instead of
+//     group in steady state, the tensor pipe's own time.  256 tiles on 74 pairs are 3.46 waves: the 34 tiles of
+//     the last wave are computed as two halves of K by 68 pairs (they add into a zeroed C), 3.5 waves instead of
 //     4.  In a long loop the GPU sits at its 1000 W power cap (SM clock 1.6-1.7 GHz, sw_power_cap the only reason).
 // Whole call (split of A with its patterns + product), bursts of 20 calls: 0.51 ms dense against 2.35 ms for the
 // FP32 kernel.
@@ -642,8 +642,8 @@ struct PairItem {
     bool split;
 };
 
-// Work items of the pair kernels: whole tiles first, then the tiles of the last, partly filled round as two items each
-// (halves of the tile's live groups), so that the round costs half a tile instead of a whole one.  Their part of C
+// Work items of the pair kernels: whole tiles first, then the tiles of the last, partly filled wave as two items each
+// (halves of the tile's live groups), so that the wave costs half a tile instead of a whole one.  Their part of C
 // is zeroed by the split pass (ZeroJob) and both items add their sums.
 __device__ __forceinline__ PairItem pair_item(const Tf32Params &p, int item)
 {
@@ -1052,8 +1052,8 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
 
     // Which kernel: the one with the smallest estimated time per SM, in units of one 128 x 128 tile's tensor time.
     // A 256 x 256 tile is two units per SM at the tensor rate; a 256 x 128 tile one unit at 1.19 and a 128 x 128 tile
-    // on one CTA one unit at 1.24 (measured at 3072^3, where all three fill their rounds alike); a pair kernel's
-    // partly filled last round counts half when its tiles can be split along K.  Small problems therefore take the
+    // on one CTA one unit at 1.24 (measured at 3072^3, where all three fill their waves alike); a pair kernel's
+    // partly filled last wave counts half when its tiles can be split along K.  Small problems therefore take the
     // smaller tiles (1024^2 x 4096: 97 us on 256 x 128 pairs, 105 us on single CTAs, 137 us on 256 x 256 pairs), large
     // ones the 256 x 256 pairs.  ESMM_TF32_PAIR = 0 | 128 | 256 overrides the choice.
     const int pair_env = env_int("ESMM_TF32_PAIR", -1);
@@ -1061,14 +1061,14 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     const bool can_split = groups >= 12 && env_int("ESMM_TF32_SPLIT_LAST", 1) != 0;
     int nb = 0;
     {
-        auto pair_rounds = [&](int tiles) {
+        auto pair_waves = [&](int tiles) {
             const int full = tiles / pairs_all, left = tiles % pairs_all;
             if (!left) return (double)full;
             return full + ((full > 0 && 2 * left <= pairs_all && can_split) ? 0.5 : 1.0);
         };
         const double c1 = 1.24 * ceil_div(ceil_div(M, TILE_M) * ceil_div(N, TILE_N), sms);
-        const double c128 = 1.19 * pair_rounds(ceil_div(M, P2_TILE_M) * ceil_div(N, 128));
-        const double c256 = 2.0 * pair_rounds(ceil_div(M, P2_TILE_M) * ceil_div(N, 256));
+        const double c128 = 1.19 * pair_waves(ceil_div(M, P2_TILE_M) * ceil_div(N, 128));
+        const double c256 = 2.0 * pair_waves(ceil_div(M, P2_TILE_M) * ceil_div(N, 256));
         if (M >= 192) {
             // near-ties go to the larger tile (512 x 11008 x 4096: 0.190 ms on 256 x 256 pairs, 0.202 on 256 x 128)
             nb = (N >= 192 && c256 <= 1.05 * c128 && c256 <= 1.05 * c1) ? 256 : (c128 <= c1 ? 128 : 0);
@@ -1102,8 +1102,8 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     p.status = device_status_ptr();
     if (!p.status) return ESMM_ERR_CUDA;
 
-    // The last round of a pair kernel: `left` tiles for `pairs` pairs.  Where two halves per tile still fit into one
-    // round, those tiles are split along K (their part of C is zeroed by the split pass below).
+    // The last wave of a pair kernel: `left` tiles for `pairs` pairs.  Where two halves per tile still fit into one
+    // wave, those tiles are split along K (their part of C is zeroed by the split pass below).
     const int pairs = std::max(1, std::min(pairs_all, p.num_tiles));
     ZeroJob zj;
     memset(&zj, 0, sizeof zj);

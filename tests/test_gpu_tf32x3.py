@@ -161,7 +161,7 @@ def test_full_size_agrees_with_fp32_path(cuda, pkg):
 
 @pytest.mark.parametrize("pair", ["256", "128"])
 def test_last_round_split_along_k(cuda, pkg, monkeypatch, pair):
-    """Shapes whose tiles leave a partly filled last round: those tiles are computed as two halves of K by two CTA
+    """Shapes whose tiles leave a partly filled last wave: those tiles are computed as two halves of K by two CTA
     pairs that add into a zeroed C.  Same result as without the split to rounding, the same bits on every call,
     and stale contents of C do not leak in."""
     torch = cuda
