@@ -712,7 +712,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
 
     // With the wide tile, 12 warps leave 168 registers per thread and an epilogue thread keeps a 128-column row of
     // run sums: the first four warps (producer, MMA, mask, idle) hand registers over to the eight epilogue warps.
-    // The instruction sits at the head of each side's own branch so that the code below it is compiled for its budget.
+    // The instruction sits at the head of each side's own branch so that the code below it is compiled for its register allowance.
     if (warp < 4) {
     if constexpr (NB == 256) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 2) {
@@ -748,7 +748,7 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                     } else {
                         unsigned au[T_GROUP_KB] = {0, 0, 0, 0}, bu[T_GROUP_KB] = {0, 0, 0, 0};
 #pragma unroll 1
-                        for (int i = 0; i < 8; ++i) {       // not unrolled: this warp runs on a small register budget
+                        for (int i = 0; i < 8; ++i) {       // not unrolled: this warp runs on a small register allowance
                             const int mb = tm * 8 + i, nb = tn * (NB / 32) + i;
 #pragma unroll
                             for (int j = 0; j < T_GROUP_KB; ++j) {
