@@ -138,3 +138,19 @@ def test_compute_entry_points_fail_loudly_without_gpu(pkg):
     out = np.zeros(4, np.uint8)
     assert pkg.lib().esmm_preprocess_a(a.ctypes.data, 32, 32, 32, out.ctypes.data, 0) == pkg.ERR_CUDA
     assert pkg.lib().esmm_last_cuda_error()
+
+
+def test_tf32x3_host_side_without_gpu(pkg):
+    """The parts of the optional tensor-core entry points that need no device: sizes and NULL handling."""
+    import ctypes as C
+    L = pkg.lib()
+    assert L.esmm_tf32x3_workspace_bytes(0, 64) == 0 and L.esmm_tf32x3_workspace_bytes(64, -8) == 0
+    M, K = 100, 72
+    pat = (int(L.esmm_a_pattern_bytes(M, K, 32)) + 255) & ~255
+    assert L.esmm_tf32x3_workspace_bytes(M, K) == pat + 2 * M * K * 4
+    assert L.esmm_tf32x3_b_live_k(None) == 0
+    L.esmm_tf32x3_b_destroy(None)
+    h = C.c_void_p()
+    assert L.esmm_tf32x3_b_create(None, 64, 64, 1, C.byref(h)) == 1 and not h.value          # ESMM_ERR_NULL before any CUDA call
+    assert L.esmm_sgemm_joint_tf32x3(32, None, None, None, None, None) == 1
+
