@@ -264,6 +264,20 @@ class PairTimer:
                     out[kid] = (ms, 0.0)
                     ref = dC.clone()
                     continue
+                if kid == 129:
+                    # optional tensor-core variant: B prepared once per weight matrix (kept with this timer), the call
+                    # does its own preprocessing of A, so the whole call is the "compute" column
+                    if getattr(self, "tf32_b", None) is None:
+                        self.tf32_b = pkg.Tf32x3B(pB, K, self.N, True)
+                    ws = t.empty(pkg.tf32x3_workspace_bytes(M, K), dtype=t.uint8, device="cuda")
+                    ms = self._time(lambda: pkg.sgemm_joint_tf32x3(M, pA, self.tf32_b, pC, ws.data_ptr()), runs)
+                    pkg.device_status()
+                    if check and ref is not None:
+                        err = float((dC - ref).abs().max()) / max(float(ref.abs().max()), 1e-30)
+                        if err > 1e-4:
+                            raise pkg.EsmmError(pkg.ERR_VERIFY, f"kernel {kid}: rel-inf error {err:.3g} against cuBLAS")
+                    out[kid] = (ms, 0.0)
+                    continue
                 if kid not in JOINT_IDS:
                     raise pkg.EsmmError(pkg.ERR_UNSUPPORTED, f"kernel id {kid}")
                 tile = A_TILE.get(kid, 32)

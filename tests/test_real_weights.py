@@ -103,13 +103,14 @@ def test_both_modes_on_stored_matrices(rw, cuda, tmp_path, capfd):
     B.tofile(wdir / f"w_{B.shape[0]}x{B.shape[1]}.bin")
     out = tmp_path / "pairs.csv"
     assert rw.main(["--weights-a", str(wdir), "--weights-b", str(wdir), "--filter-a", "act", "--filter-b", "w_",
-                    "--kernels", "15,29,20,21", "--runs", "2", "--out", str(out)]) == 0
+                    "--kernels", "15,29,20,21,129", "--runs", "2", "--out", str(out)]) == 0
     text = capfd.readouterr().out
     assert "B patterns: saved" in text and "FAILED" not in text
     with open(out) as f:
         rows = list(csv.DictReader(f))
     assert len(rows) == 1 and rows[0]["a_shape"] == "200x250" and rows[0]["b_shape"] == "250x352"
     assert float(rows[0]["k29_compute_ms"]) > 0 and float(rows[0]["k29_total_speedup"]) > 0
+    assert float(rows[0]["k129_compute_ms"]) > 0          # the optional tensor-core variant, verified against cuBLAS too
     # the cache holds the oracle's bytes for the padded B, and the second run loads it
     raw = (wdir / f"w_{B.shape[0]}x{B.shape[1]}.bin.bpat").read_bytes()
     Bp = rw.pad_to_tile(B, rw.BK, rw.BM)
