@@ -81,6 +81,11 @@ _SIGNATURES = {
     "esmm_fill_normal": (_i, [_vp, C.c_long, C.c_long, _i, C.c_uint64, _f, _f, _i, _i, C.c_uint8, _f, _i,
                               C.c_uint64, _vp]),
     "esmm_interleave_shards": (_i, [_vp, _vp, _i, _i, _i, _vp]),
+    "esmm_randomize_matrix_with_pattern": (_i, [_vp, _i, _i, C.c_char_p]),
+    "esmm_randomize_matrix_unstructured": (_i, [_vp, _i, _i, _f, C.c_uint]),
+    "esmm_randomize_matrix_a_blocklevel": (_i, [_vp, _i, _i, _i, _i, _f, C.c_uint]),
+    "esmm_randomize_matrix_b_blocklevel": (_i, [_vp, _i, _i, _i, _i, _f, C.c_uint]),
+    "esmm_print_usage": (None, [C.c_char_p, _i]),
     "esmm_skip_stats": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_longlong * 6)]),
     "esmm_kernel_id_valid": (_i, [_i]),
     "esmm_kernel_name": (C.c_char_p, [_i]),

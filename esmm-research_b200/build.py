@@ -18,10 +18,10 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo"] + ARCH
 
 LIB_SRCS = [os.path.join(HERE, "csrc", f) for f in
             ("esmm_gemm.cu", "esmm_gemm_packed.cu", "esmm_gemm_skinny.cu", "esmm_preprocess.cu", "esmm_api.cu", "esmm_noalloc.cu",
-             "esmm_cusparse.cu", "esmm_gemm_tf32.cu")]
+             "esmm_cusparse.cu", "esmm_gemm_tf32.cu", "esmm_host.cu")]
 LIB_DEPS = LIB_SRCS + [os.path.join(HERE, "csrc", "esmm_common.cuh"), os.path.join(HERE, "csrc", "esmm_gemm_shared.cuh"), os.path.join(ROOT, "include", "esmm.h")]
 EXE_SRCS = [os.path.join(HERE, "driver.cu")]
-EXE_DEPS = EXE_SRCS + [os.path.join(ROOT, "include", "runners.cuh"), os.path.join(ROOT, "include", "esmm.h")]
+EXE_DEPS = EXE_SRCS + [os.path.join(ROOT, "include", h) for h in ("runners.cuh", "utils.cuh", "esmm.h")]
 
 
 def _stale(target: str, deps: list[str]) -> bool:

@@ -27,114 +27,21 @@
 #include <cstring>
 #include <thread>
 
+#include "include/utils.cuh"
 #include "include/runners.cuh"
 
 namespace {
 
-const char *kUsageKernels[][2] = {
-    {"14", "A-Only Sparse (Offset List, Templated Dispatch)"},
-    {"15", "cuBLAS baseline"},
-    {"16", "A-Sparse Block-wise (Warp-Granularity Patterns)"},
-    {"17", "B-Sparse Warp-Granularity (32-col, Zero-Divergence)"},
-    {"20", "A+B Sparse OPTIMIZED (Zero-Overhead Inner Loop)"},
-    {"21", "A+B Sparse - 8x32 Granularity"},
-    {"25", "A+B Simple Fused (Main Contribution)"},
-    {"26", "A+B Optimized V2 (K20 + 32-row + Block Skip + Float4)"},
-    {"27", "A+B Ablation (32-row only, no Block Skip, no Float4)"},
-    {"28", "A+B GMem-32 (K25 with 32-row, global mem patterns)"},
-    {"29", "A+B Optimized V3 (K26 + templated smem + float2 A-loads)"},
-    {"30", "A+B Compressed-K (K29 + compressed K-list + set-bit dotIdx)"},
-    {"129", "A+B 3xTF32 on tensor cores (additive: not in the reference, not part of 'all')"},
-};
-
-void print_usage(const char *prog)
+// The reference's usage text plus the flags and the kernel id added here.
+void usage(const char *prog)
 {
-    using std::cout;
-    using std::endl;
-    cout << "Usage: " << prog << " [kernel_choice] [runs] [options]" << endl;
-    cout << "\nAvailable kernels: 14, 15, 16, 17, 20, 21, 25, 26, 27, 28, 29, 30 (and 129)" << endl;
-    for (auto &k : kUsageKernels) cout << "  " << k[0] << ": " << k[1] << endl;
-    cout << "\nKernel selection formats:" << endl;
-    cout << "  Single:   29          (run K29)" << endl;
-    cout << "  Multiple: \"29,15\"     (comma-separated)" << endl;
-    cout << "  Range:    \"14-17\"    (kernels in range that are valid)" << endl;
-    cout << "  All:      all         (all kernels)" << endl;
-    cout << "\nOptions:" << endl;
-    cout << "  --verbose, -v       Enable verbose output" << endl;
-    cout << "  --no-check, -n      Skip result verification (performance-only mode)" << endl;
-    cout << "  --random, -r        Use random unstructured sparsity" << endl;
-    cout << "  --blockwise, -b     Use block-level sparsity (random per-tile patterns)" << endl;
-    cout << "  --size <N>, -s <N>  Set matrix dimensions NxNxN (default: 4096)" << endl;
-    cout << "  --pattern <P>       Set 8-bit sparsity pattern for A and B (default: \"11000000\")" << endl;
-    cout << "  --pattern-a <P>     Set 8-bit sparsity pattern for A matrix only" << endl;
-    cout << "  --pattern-b <P>     Set 8-bit sparsity pattern for B matrix only" << endl;
-    cout << "  --load-a/--load-b <file>  Raw float32 row-major matrices (with --dims M K N)" << endl;
-    cout << "  --skip-stats        Print block / warp / k skip statistics" << endl;
-    cout << "  --uniform           N(0,1) values, pattern on A's K columns and B's K rows (device generator)" << endl;
-    cout << "  --tile-random pA pB N(0,1) values, independent 64-row / 64-column tile patterns" << endl;
-    cout << "  --seed <S>          Seed for --uniform / --tile-random" << endl;
-    cout << "  --cpu-check         Also verify against the CPU SGEMM (rel-inf tolerance 1e-4)" << endl;
-    cout << "  --cache-b           Cache B's pattern bytes next to the --load-b file (<file>.bpat)" << endl;
-    cout << "  --cache-b-file <f>  Cache B's pattern bytes in <f>" << endl;
-    cout << "  --json              One JSON line per kernel" << endl;
-    cout << "  --help, -h          Show this help message" << endl;
-    cout << "\nExamples:" << endl;
-    cout << "  " << prog << " 29,15 10 --blockwise --pattern 11110000 --size 4096 --verbose" << endl;
-    cout << "  " << prog << " 29 10 --uniform --pattern 10000000 --size 4096 --cpu-check" << endl;
-    cout << "  " << prog << " 29 5 --load-b W.bin --dims 2048 4096 11008 --no-check" << endl;
-}
-
-// One value of the reference's generators: {0..4} + 0.01 * {0..4} with a random sign
-// (include/utils.cuh:148-149, 332-333); three rand() draws.
-float draw_value()
-{
-    const int whole = rand() % 5;
-    const int frac = rand() % 5;
-    const float v = (float)whole + 0.01f * (float)frac;
-    return (rand() % 2) ? v : -v;
+    std::cout.flush();
+    esmm_print_usage(prog, 1);
 }
 
 bool pattern_ok(const std::string &p)
 {
     return p.size() == 8 && std::all_of(p.begin(), p.end(), [](char c) { return c == '0' || c == '1'; });
-}
-
-// Default driver mode (include/utils.cuh:142-156): the pattern masks the column index mod 8 of
-// whatever matrix it is given (for B that is the N index).
-void fill_column_pattern(float *mat, int rows, int cols, const std::string &pattern)
-{
-    for (long i = 0; i < (long)rows * cols; ++i) mat[i] = pattern[(i % cols) % 8] == '1' ? draw_value() : 0.0f;
-}
-
-// --random (include/utils.cuh:159-194): each element zero with probability sparsity_percent.
-void fill_unstructured(float *mat, int rows, int cols, float sparsity_percent, unsigned seed)
-{
-    if (seed) srand(seed);
-    const float thr = sparsity_percent / 100.0f;
-    for (long i = 0; i < (long)rows * cols; ++i)
-        mat[i] = ((float)rand() / (float)RAND_MAX < thr) ? 0.0f : draw_value();
-}
-
-// --blockwise (include/utils.cuh:303-381): an independent random 8-bit pattern per tile; A tiles are
-// tile_rows x 8 (K offsets are columns), B tiles are 8 x 32 (K offsets are rows).
-void fill_blockwise(float *mat, int outer, int K, bool k_is_row, int tile_outer, float sparsity_percent,
-                    unsigned seed)
-{
-    if (seed) srand(seed);
-    const float thr = sparsity_percent / 100.0f;
-    const int ld = k_is_row ? outer : K;
-    for (int ob = 0; ob < outer / tile_outer; ++ob)
-        for (int kb = 0; kb < K / 8; ++kb) {
-            unsigned pat = 0;
-            for (int bit = 0; bit < 8; ++bit)
-                if ((float)rand() / RAND_MAX >= thr) pat |= 1u << bit;
-            for (int o = 0; o < tile_outer; ++o)
-                for (int k = 0; k < 8; ++k) {
-                    const long r = k_is_row ? kb * 8 + k : ob * tile_outer + o;
-                    const long c = k_is_row ? ob * tile_outer + o : kb * 8 + k;
-                    mat[r * ld + c] = ((pat >> k) & 1u) ? draw_value() : 0.0f;
-                }
-        }
 }
 
 bool load_bin(const std::string &path, float *buf, size_t n)
@@ -196,7 +103,7 @@ int parse_args(int argc, char **argv, Options &o)
     for (int i = 1; i < argc; ++i) {
         const std::string a = argv[i];
         if (a == "--help" || a == "-h") {
-            print_usage(argv[0]);
+            usage(argv[0]);
             return 0;
         } else if (a == "--verbose" || a == "-v") o.verbose = true;
         else if (a == "--no-check" || a == "-n") o.check = false;
@@ -214,7 +121,7 @@ int parse_args(int argc, char **argv, Options &o)
         }
         else if (a == "--size" || a == "-s") {
             if (!need(i, 1, "--size requires an argument")) {
-                print_usage(argv[0]);
+                usage(argv[0]);
                 return 1;
             }
             const int s = atoi(argv[++i]);
@@ -227,7 +134,7 @@ int parse_args(int argc, char **argv, Options &o)
                    a == "-pb") {
             const std::string flag = (a == "-p") ? "--pattern" : (a == "-pa") ? "--pattern-a" : (a == "-pb") ? "--pattern-b" : a;
             if (!need(i, 1, (flag + " requires an argument").c_str())) {
-                print_usage(argv[0]);
+                usage(argv[0]);
                 return 1;
             }
             const std::string p = argv[++i];
@@ -262,7 +169,7 @@ int parse_args(int argc, char **argv, Options &o)
                 o.kernels = parse_kernel_selection(a);
                 if (o.kernels.empty()) {
                     cout << "Error: Invalid kernel selection '" << a << "'" << endl;
-                    print_usage(argv[0]);
+                    usage(argv[0]);
                     return 1;
                 }
             }
@@ -365,17 +272,21 @@ int main(int argc, char **argv)
             }
         } else if (o.blockwise) {
             auto sparsity_of = [](const std::string &p) {
-                return 100.0f - (float)std::count(p.begin(), p.end(), '1') / 8.0f * 100.0f;
+                return 100.0f - ((float)std::count(p.begin(), p.end(), '1') / 8.0f) * 100.0f;
             };
-            // A granularity: 8-row tiles if kernel 21 is selected last, else 32 (driver.cu:379-387)
-            for (int k : o.kernels) fill_blockwise(h_A, M, K, false, k == 21 ? 8 : 32, sparsity_of(o.pattern_a), o.seed);
-            fill_blockwise(h_B, N, K, true, 32, sparsity_of(o.pattern_b), o.seed + 1);
+            // A is regenerated once per selected id, 8-row tiles for id 21 and 32-row tiles otherwise, so the
+            // last id decides (driver.cu:379-387); the generators are the reference's own, by name
+            for (int k : o.kernels) {
+                if (k == 21) randomize_matrix_A<8, 8>(h_A, M, K, sparsity_of(o.pattern_a), o.seed);
+                else randomize_matrix_A_blocklevel<8, 32>(h_A, M, K, sparsity_of(o.pattern_a), o.seed);
+            }
+            randomize_matrix_B_blocklevel_fixed<8, 32>(h_B, K, N, sparsity_of(o.pattern_b), o.seed + 1);
         } else if (o.random_mode) {
-            fill_unstructured(h_A, M, K, o.random_sparsity, o.seed);
-            fill_unstructured(h_B, K, N, o.random_sparsity, o.seed + 1);
+            randomize_matrix_unstructured(h_A, M, K, o.random_sparsity, o.seed);
+            randomize_matrix_unstructured(h_B, K, N, o.random_sparsity, o.seed + 1);
         } else {
-            fill_column_pattern(h_A, M, K, o.pattern_a);
-            fill_column_pattern(h_B, K, N, o.pattern_b);
+            randomize_matrix_with_pattern(h_A, M, K, o.pattern_a);
+            randomize_matrix_with_pattern(h_B, K, N, o.pattern_b);
         }
         cudaCheckError(cudaMemcpy(d_A, h_A, nA * sizeof(float), cudaMemcpyHostToDevice));
         cudaCheckError(cudaMemcpy(d_B, h_B, nB * sizeof(float), cudaMemcpyHostToDevice));

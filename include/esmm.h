@@ -277,6 +277,36 @@ int esmm_fill_normal(float *d_out, long rows, long cols, int k_axis, uint64_t se
 /* Interleaves G column shards [g][M][N/G] into row-major M x N (used after an all-gather). */
 int esmm_interleave_shards(const float *d_shards, float *d_C, int M, int N, int G, void *stream);
 
+/* ---- harness data generators and usage text (host only) -------------------- */
+
+/*
+ * The driver's rand()-based generators, draw for draw: the same calls to the C library's rand() in
+ * the same order, rounding where the reference's expressions round, so that a seed gives the matrices
+ * the reference driver multiplies.  All take HOST pointers and need no device.
+ *   esmm_randomize_matrix_with_pattern   randomize_matrix_with_pattern (include/utils.cuh:142-156): the
+ *       default mode; element (i, j) is live when pattern[j % 8] == '1' (for B that is the N index,
+ *       driver.cu:404-405); does not seed.
+ *   esmm_randomize_matrix_unstructured   randomize_matrix_unstructured (include/utils.cuh:159-194):
+ *       --random; seeds when seed != 0; prints the reference's note when the achieved sparsity is more
+ *       than 2 points off.
+ *   esmm_randomize_matrix_a_blocklevel   randomize_matrix_A_blocklevel<BK, WM> (include/utils.cuh:303-341)
+ *       and randomize_matrix_A<BK, TILE_M> (:386-426), which differ only in the default tile height:
+ *       one random 8-bit pattern per (tile_m rows x bk columns) tile of A.
+ *   esmm_randomize_matrix_b_blocklevel   randomize_matrix_B_blocklevel_fixed<BK, WN> (:343-381): one
+ *       pattern per (bk rows x wn columns) tile of B.
+ * Values are {0..4} + 0.01 * {0..4} with a random sign.  Rows / columns beyond the last whole tile are
+ * left untouched, as in the reference.
+ */
+int esmm_randomize_matrix_with_pattern(float *h_mat, int M, int N, const char *pattern);
+int esmm_randomize_matrix_unstructured(float *h_mat, int M, int N, float sparsity_percent, unsigned seed);
+int esmm_randomize_matrix_a_blocklevel(float *h_mat, int M, int K, int bk, int tile_m,
+                                       float block_sparsity_percent, unsigned seed);
+int esmm_randomize_matrix_b_blocklevel(float *h_mat, int K, int N, int bk, int wn,
+                                       float block_sparsity_percent, unsigned seed);
+/* print_usage (include/utils.cuh:66-101) on stdout.  additive != 0 also lists the flags and the kernel
+ * id this library adds to the reference's command line. */
+void esmm_print_usage(const char *program_name, int additive);
+
 /* ---- skip statistics ------------------------------------------------------ */
 
 /* compute_and_print_skip_stats arithmetic (include/runners.cuh:636-706) on HOST pattern

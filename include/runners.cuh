@@ -11,8 +11,10 @@
 //   the single-operand runners (ids 14, 16, 17)                     include/runners.cuh:30-106, 150-275
 //   preprocess_ab<BK, TILE_M_A, WN>, ABPatternMetadata,
 //   free_ab_pattern_metadata                                        src/preprocessors/ab_preprocessor.cu:7-24, 297-326
-//   parse_kernel_selection, get_kernel_name, verifyResults,
-//   matrixMultiplyCPU, cudaCheckError, CEIL_DIV                     include/utils.cuh:10-254
+//
+// The helper half of the reference's surface (parse_kernel_selection, get_kernel_name, print_usage,
+// the generators, verifyResults, matrixMultiplyCPU, cudaCheckError, CEIL_DIV) is utils.cuh beside this
+// file, which this header includes.
 //
 // Argument naming follows the reference: rows = M, cols = N, inners = K.  Nothing here launches a
 // kernel itself; every call goes through the extern "C" entry points.
@@ -31,66 +33,7 @@
 
 #include "esmm.h"
 
-#ifndef CEIL_DIV
-#define CEIL_DIV(M, N) (((M) + (N)-1) / (N))
-#endif
-
-// ---- include/utils.cuh ------------------------------------------------------------------------
-#define cudaCheckError(ans)                      \
-    {                                            \
-        cudaAssert((ans), __FILE__, __LINE__);   \
-    }
-inline void cudaAssert(cudaError_t code, const char *file, int line)
-{
-    if (code != cudaSuccess) {
-        fprintf(stderr, "CUDA Error: %s %s %d\n", cudaGetErrorString(code), file, line);
-        exit(code);
-    }
-}
-
-inline std::vector<int> parse_kernel_selection(const std::string &input)
-{
-    int ids[32];
-    const int n = esmm_parse_kernel_selection(input.c_str(), ids, 32);
-    return std::vector<int>(ids, ids + (n < 0 ? 0 : (n > 32 ? 32 : n)));
-}
-
-inline const char *get_kernel_name(int kernel_choice) { return esmm_kernel_name(kernel_choice); }
-
-// The driver's CPU SGEMM: i-j-k loops, one sequential k loop per output.
-inline void matrixMultiplyCPU(const float *A, const float *B, float *C, int M, int N, int K)
-{
-    for (int i = 0; i < M; i++)
-        for (int j = 0; j < N; j++) {
-            float sum = 0.0f;
-            for (int k = 0; k < K; k++) sum += A[i * K + k] * B[k * N + j];
-            C[i * N + j] = sum;
-        }
-}
-
-// Absolute-tolerance check of the reference (default 1e-2), same messages.
-inline bool verifyResults(const float *gpuResults, const float *cpuResults, int size, float tolerance = 1e-2)
-{
-    int mismatchCount = 0, firstMismatchIdx = -1;
-    float maxDiff = 0.0f;
-    for (int i = 0; i < size; i++) {
-        const float diff = std::abs(gpuResults[i] - cpuResults[i]);
-        if (diff > tolerance) {
-            mismatchCount++;
-            if (firstMismatchIdx == -1) firstMismatchIdx = i;
-            maxDiff = std::max(maxDiff, diff);
-        }
-    }
-    if (mismatchCount > 0) {
-        std::cout << "Verification failed: " << mismatchCount << " mismatches out of " << size << " elements."
-                  << std::endl;
-        std::cout << "Max difference: " << maxDiff << std::endl;
-        std::cout << "First mismatch at index " << firstMismatchIdx << ": GPU=" << gpuResults[firstMismatchIdx]
-                  << ", CPU=" << cpuResults[firstMismatchIdx] << std::endl;
-        return false;
-    }
-    return true;
-}
+#include "utils.cuh"
 
 // ---- src/preprocessors/ab_preprocessor.cu ---------------------------------------------------------
 using ABPatternMetadata = esmm_ab_pattern_metadata;

@@ -23,16 +23,25 @@ _u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
 _i64p = np.ctypeslib.ndpointer(dtype=np.int64, flags="C_CONTIGUOUS")
 
 
+def ref_root() -> str:
+    """Where the reference tree is looked for: $ESMM_REF_ROOT, else a directory named `reference`
+    beside the repository."""
+    return os.environ.get("ESMM_REF_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+
+
+def have_ref_tree() -> bool:
+    return os.path.exists(os.path.join(ref_root(), "include", "runners.cuh"))
+
+
 def build(force: bool = False) -> None:
     """Compile liboracle.so (and oracle/_ref when the reference tree is present)."""
     src = os.path.join(_HERE, "esmm_oracle.c")
     if force or not os.path.exists(_LIB_PATH) or os.path.getmtime(_LIB_PATH) < os.path.getmtime(src):
         subprocess.check_call(["make", "-C", _HERE, "oracle"])
     shim = os.path.join(_HERE, "ref_shim.cu")
-    ref_root = os.environ.get("ESMM_REF_ROOT", "/root/reference")
-    if os.path.exists(os.path.join(ref_root, "include", "runners.cuh")):
+    if have_ref_tree():
         if force or not os.path.exists(_REF_PATH) or os.path.getmtime(_REF_PATH) < os.path.getmtime(shim):
-            subprocess.check_call(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root}"])
+            subprocess.check_call(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root()}"])
 
 
 _lib = None
@@ -191,6 +200,7 @@ def ref() -> C.CDLL:
         R.ref_verifyResults.argtypes = [_f32p, _f32p, C.c_int, C.c_float]
         R.ref_randomize_A_blocklevel_8_32.argtypes = [_f32p, C.c_int, C.c_int, C.c_float, C.c_uint]
         R.ref_randomize_B_blocklevel_8_32.argtypes = [_f32p, C.c_int, C.c_int, C.c_float, C.c_uint]
+        R.ref_randomize_A_8_8.argtypes = [_f32p, C.c_int, C.c_int, C.c_float, C.c_uint]
         R.ref_randomize_with_pattern.argtypes = [_f32p, C.c_int, C.c_int, C.c_char_p]
         R.ref_randomize_unstructured.argtypes = [_f32p, C.c_int, C.c_int, C.c_float, C.c_uint]
         R.ref_srand.argtypes = [C.c_uint]
@@ -201,6 +211,7 @@ def ref() -> C.CDLL:
         R.ref_preprocess_ab_32.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, vp, vp]
         R.ref_esmm_v3_launch.argtypes = [C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp]
         R.ref_run_esmm_ab_optimized_v3_no_check.argtypes = [C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_int]
+        R.ref_run_esmm_ab_optimized_v3_skip_stats.argtypes = [C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_int]
         _ref = R
     return _ref
 

@@ -43,7 +43,7 @@ int ref_verifyResults(const float *gpu, const float *cpu, int size, float tol)
     return verifyResults(gpu, cpu, size, tol) ? 1 : 0;
 }
 
-// include/utils.cuh:303-341, :343-381, :142-156, :159-194
+// include/utils.cuh:303-341, :343-381, :386-426, :142-156, :159-194
 void ref_randomize_A_blocklevel_8_32(float *mat, int M, int K, float sparsity_percent, unsigned seed)
 {
     randomize_matrix_A_blocklevel<8, 32>(mat, M, K, sparsity_percent, seed);
@@ -51,6 +51,10 @@ void ref_randomize_A_blocklevel_8_32(float *mat, int M, int K, float sparsity_pe
 void ref_randomize_B_blocklevel_8_32(float *mat, int K, int N, float sparsity_percent, unsigned seed)
 {
     randomize_matrix_B_blocklevel_fixed<8, 32>(mat, K, N, sparsity_percent, seed);
+}
+void ref_randomize_A_8_8(float *mat, int M, int K, float sparsity_percent, unsigned seed)
+{
+    randomize_matrix_A<8, 8>(mat, M, K, sparsity_percent, seed);
 }
 void ref_randomize_with_pattern(float *mat, int M, int N, const char *pattern)
 {
@@ -118,6 +122,18 @@ int ref_run_esmm_ab_optimized_v3_no_check(int rows, int cols, int inners, float 
                                           float *dC, int runs)
 {
     return run_esmm_ab_optimized_v3_no_check(rows, cols, inners, dA, dB, dC, runs) ? 1 : 0;
+}
+
+// The 11-argument runner with print_skip_stats = true and verify = false
+// (include/runners.cuh:827-887): prints the "=== Skip Stats: ... ===" block of
+// compute_and_print_skip_stats (:636-706) on stdout before its timed loop.
+int ref_run_esmm_ab_optimized_v3_skip_stats(int rows, int cols, int inners, float *dA, float *dB,
+                                            float *dC, int runs)
+{
+    const bool ok = run_esmm_ab_optimized_v3(rows, cols, inners, dA, dB, dC, nullptr, nullptr, runs,
+                                             /*verify=*/false, /*print_skip_stats=*/true);
+    fflush(stdout);
+    return ok ? 1 : 0;
 }
 
 }  // extern "C"

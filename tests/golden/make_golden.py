@@ -6,8 +6,9 @@
 
 cpu -> ref_cpu.npz : inputs drawn by the reference's own rand()-based generators
                      (randomize_matrix_A_blocklevel<8,32>, randomize_matrix_B_blocklevel_fixed<8,32>,
-                     randomize_matrix_with_pattern), the reference CPU SGEMM (matrixMultiplyCPU) of
-                     them, and the reference's kernel-selection parser / kernel names.
+                     randomize_matrix_with_pattern, randomize_matrix_unstructured, randomize_matrix_A<8,8>),
+                     the reference CPU SGEMM (matrixMultiplyCPU) of them, the reference's kernel-selection
+                     parser / kernel names, and its literal PatternLUT table.
 gpu -> ref_gpu.npz : for seeded inputs (recreated by seed in the tests, not stored), the pattern
                      bytes of preprocess_ab<8,32,32> and the C of esmm_ab_optimized_v3 as run on a B200.
 The gpu mode writes ref_gpu.npz into the output directory given (default: tests/golden/ itself), for the case
@@ -45,6 +46,19 @@ def make_case(gen: str, M: int, N: int, K: int, args: dict):
     return getattr(workloads, gen)(M, N, K, **args)
 
 
+def parse_pattern_lut(path: str):
+    """The 256 `{count, {o0, ..., o7}}` initialisers of PATTERN_LUT_BK8 (include/pattern_lut.cuh), in order."""
+    import re
+    text = open(path).read()
+    body = text[text.index("PATTERN_LUT_BK8"):]
+    rows = re.findall(r"\{\s*(\d+)\s*,\s*\{([^}]*)\}\s*\}", body)
+    assert len(rows) == 256, len(rows)
+    cnt = np.array([int(c) for c, _ in rows], np.uint8)
+    off = np.array([[int(x) for x in o.split(",")] for _, o in rows], np.uint8)
+    assert off.shape == (256, 8)
+    return cnt, off
+
+
 def cpu() -> None:
     R = oracle.ref()
     out = {}
@@ -66,6 +80,19 @@ def cpu() -> None:
     C2 = np.zeros((32, 32), np.float32)
     R.ref_matrixMultiplyCPU(A2, B2, C2, 32, 32, 64)
     out.update(pat_A=A2, pat_B=B2, pat_C=C2)
+    # driver.cu:401-402: --random (37.5 % unstructured, seeds 12345 / 12346)
+    A3 = np.zeros((48, 40), np.float32)
+    B3 = np.zeros((40, 56), np.float32)
+    R.ref_randomize_unstructured(A3, 48, 40, 37.5, 12345)
+    R.ref_randomize_unstructured(B3, 40, 56, 37.5, 12346)
+    out.update(rnd_A=A3, rnd_B=B3)
+    # driver.cu:382: --blockwise with kernel 21 selected: 8-row tiles of A
+    A4 = np.zeros((64, 64), np.float32)
+    R.ref_randomize_A_8_8(A4, 64, 64, 75.0, 12345)
+    out.update(a8_A=A4)
+    # include/pattern_lut.cuh: the literal table, read as text (it is __constant__ device data)
+    cnt, off = parse_pattern_lut(os.path.join(oracle.ref_root(), "include", "pattern_lut.cuh"))
+    out.update(lut_count=cnt, lut_offsets=off)
     # parser + names
     sels = ["29", "29,15", "14-17", "all", "20,21,25", "1-100", "99", "15,99,29"]
     buf = (ctypes.c_int * 32)()
