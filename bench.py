@@ -44,13 +44,37 @@ def measured_peaks() -> dict:
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons while the timed region runs: NVML queries (read-only) every 10 ms,
+    or, where the NVML binding is unusable, nvidia-smi as fast as it answers."""
 
-    def __init__(self, index: int):
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20), ("sw_power_cap", 0x4))
+
+    def __init__(self, index: int, uuid: str | None = None):
         super().__init__(daemon=True)
-        self.index, self.stop_flag, self.rows = index, threading.Event(), []
+        self.index, self.uuid, self.stop_flag, self.rows, self.source = index, uuid, threading.Event(), [], "nvml"
+
+    def _nvml_handle(self):
+        import pynvml
+        pynvml.nvmlInit()
+        if self.uuid:
+            try:
+                return pynvml, pynvml.nvmlDeviceGetHandleByUUID(self.uuid)
+            except Exception:
+                pass
+        return pynvml, pynvml.nvmlDeviceGetHandleByIndex(self.index)
 
     def run(self):
+        try:
+            nv, h = self._nvml_handle()
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            while not self.stop_flag.is_set():
+                sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.rows.append((sm, mx, [n for n, bit in self.REASONS if mask & bit]))
+                self.stop_flag.wait(0.01)
+            return
+        except Exception:
+            self.source = "nvidia-smi"
         q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
         while not self.stop_flag.is_set():
@@ -58,21 +82,21 @@ class ClockSampler(threading.Thread):
                 out = subprocess.run(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}",
                                       "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
                 parts = [p.strip() for p in out.strip().split(",")]
-                if len(parts) >= 6:
-                    self.rows.append(parts)
+                if len(parts) >= 6 and parts[0].isdigit() and parts[1].isdigit():
+                    self.rows.append((int(parts[0]), int(parts[1]),
+                                      [n for (n, _), v in zip(self.REASONS, parts[2:6]) if v.lower().startswith("active")]))
             except Exception:
                 pass
-            self.stop_flag.wait(0.1)
+            self.stop_flag.wait(0.05)
 
     def summary(self) -> dict:
         self.stop_flag.set()
         self.join(timeout=6)
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        sm = sorted(int(r[0]) for r in self.rows if r[0].isdigit())
-        mx = [int(r[1]) for r in self.rows if r[1].isdigit()]
-        reasons = sorted({n for r in self.rows for n, v in zip(names, r[2:6]) if v.lower().startswith("active")})
+        sm = sorted(r[0] for r in self.rows)
+        mx = [r[1] for r in self.rows]
+        reasons = sorted({n for r in self.rows for n in r[2]})
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.rows)}
+                "reasons": reasons, "samples": len(self.rows), "source": self.source}
 
 
 def host_threads() -> int:
@@ -159,6 +183,98 @@ def run_reference_arm(args) -> None:
 
 
 # ---------------------------------------------------------------------------------------------------
+# comparison columns and checks around the timed step (never inside it)
+# ---------------------------------------------------------------------------------------------------
+def ref_kernel_times(M, N, K, A, B, ours_ms, dev):
+    """The reference's own GPU kernels (its pattern preprocessors and kernel id 29, compiled for sm_100a from the
+    reference tree into oracle/_ref) timed with CUDA events on the same device buffers: a comparison column beside
+    cuBLAS.  None when oracle/_ref is absent or the shape is outside the reference kernel's limits."""
+    import torch
+    try:
+        import oracle
+        if not oracle.have_ref() or M % 64 or N % 128 or K % 8 or K > 8192:
+            return None
+        ra = torch.empty((M // 32) * (K // 8), dtype=torch.uint8, device=dev)
+        rb = torch.empty((N // 32) * (K // 8), dtype=torch.uint8, device=dev)
+        Cr = torch.empty((M, N), device=dev)
+        pre_a, pre_b, gemm = oracle.ref_time_kernels(M, N, K, A.data_ptr(), B.data_ptr(), Cr.data_ptr(), ra.data_ptr(),
+                                                     rb.data_ptr(), warmup=2, runs=5)
+        return {"ms_ref_pre_a": pre_a, "ms_ref_pre_b": pre_b, "ms_ref_pre": pre_a + pre_b, "ms_ref_id29": gemm,
+                "speedup_vs_ref_b_offline": (pre_a + gemm) / ours_ms,       # both sides: A patterns per call, B cached
+                "speedup_vs_ref_own_loop": (pre_a + pre_b + gemm) / ours_ms}  # the reference recomputes B every run
+    except Exception as e:  # a comparison column must not break the bench line
+        return {"error": str(e)[:200]}
+
+
+def other_config_rows(pkg, torch, dev, time_each):
+    """Configs 3 and 4 (not part of `value`): this library's per-call path, cuBLAS SGEMM and, where its shape limits
+    allow, the reference's kernels, on the same inputs."""
+    import numpy as np
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import workloads
+    L = pkg.lib()
+    rows = {}
+
+    def measure(name, A, B):
+        M, K = A.shape
+        N = B.shape[1]
+        bp = torch.empty(L.esmm_b_pattern_bytes(K, N), dtype=torch.uint8, device=dev)
+        pkg.preprocess_b(B.data_ptr(), K, N, bp.data_ptr())
+        ws = torch.empty(pkg.sgemm_joint_workspace_bytes(M, K), dtype=torch.uint8, device=dev)
+        Cm = torch.empty((M, N), device=dev)
+        ours, ours_min = time_each(lambda: pkg.sgemm_joint(M, N, K, A.data_ptr(), B.data_ptr(), Cm.data_ptr(),
+                                                           bp.data_ptr(), ws.data_ptr()), 10)
+        cub, _ = time_each(lambda: pkg.cublas_sgemm(M, N, K, A.data_ptr(), B.data_ptr(), Cm.data_ptr()), 10)
+        nmb, nkb = -(-M // 32), -(-K // 8)
+        ap = ws[:nmb * nkb].reshape(nmb, nkb).cpu().numpy()
+        bpat = bp.reshape(-1, nkb).cpu().numpy()
+        # executed multiply-adds = 32 * 32 * sum popcount(a & b) over (row block, column block, K block)
+        bits_a = np.unpackbits(ap, axis=1).astype(np.float32).T         # [nkb * 8, nmb]
+        bits_b = np.unpackbits(bpat, axis=1).astype(np.float32).T       # [nkb * 8, nnb]
+        joint = float((bits_a.sum(axis=1) * bits_b.sum(axis=1)).sum()) / (bits_a.shape[1] * bits_b.shape[1] * nkb * 8)
+        rows[name] = {"M": M, "N": N, "K": K, "joint_density": joint, "ms_total": ours, "ms_total_min": ours_min,
+                      "ms_cublas": cub, "speedup_vs_cublas_incl_pre": cub / ours,
+                      "dense_equiv_tflops_incl_pre": 2.0 * M * N * K / (ours * 1e-3) / 1e12,
+                      "executed_tflops_incl_pre": 2.0 * M * N * K * joint / (ours * 1e-3) / 1e12,
+                      "reference_kernels": ref_kernel_times(M, N, K, A, B, ours, dev)}
+
+    S = 4096
+    for pA, pB in ((0.5, 0.5), (0.3, 0.7), (0.2, 0.2)):
+        A = torch.empty((S, S), device=dev)
+        B = torch.empty((S, S), device=dev)
+        pkg.fill_normal(A.data_ptr(), S, S, 0, 11, mode=2, p_live=pA, gran=64, seed2=101)
+        pkg.fill_normal(B.data_ptr(), S, S, 1, 12, mode=2, p_live=pB, gran=64, seed2=102)
+        measure(f"c3 pA={pA} pB={pB} (64-granular tile patterns)", A, B)
+    for M4 in (2048, 16):
+        hA, hB = workloads.llm_mlp(M4, 11008, 4096, seed=40 + M4)
+        measure(f"c4 M={M4} K=4096 N=11008 (LLM MLP)", torch.from_numpy(hA).to(dev), torch.from_numpy(hB).to(dev))
+    pkg.device_status()
+    return rows
+
+
+def check_shard_against_oracle(pkg, torch, A, B, Cd, blocks=3):
+    """Untimed correctness check of one rank's column shard: pattern bytes of the B shard in full, and C on a few
+    32-row blocks, against the CPU oracle (the checker, never the thing measured).  Returns a small dict."""
+    import numpy as np
+    import oracle
+    M, K = A.shape
+    Nl = B.shape[1]
+    hB = B.cpu().numpy()
+    obp = oracle.preprocess_b(hB)
+    nb = M // 32
+    picks = sorted({0, nb - 1} | {int(x) for x in np.linspace(0, nb - 1, blocks + 2)[1:-1]})
+    worst, bits = 0.0, True
+    for blk in picks:
+        hA = A[blk * 32:(blk + 1) * 32].cpu().numpy()
+        want = oracle.gemm_joint(hA, hB, oracle.preprocess_a(hA), obp)
+        got = Cd[blk * 32:(blk + 1) * 32].cpu().numpy()
+        worst = max(worst, oracle.rel_inf_err(got, want))
+        bits = bits and bool(np.array_equal(got, want))
+    return {"passed": bool(worst <= 1e-4), "bit_identical": bits, "max_rel_inf": worst, "rows_checked": 32 * len(picks),
+            "columns": Nl, "row_blocks": picks}
+
+
+# ---------------------------------------------------------------------------------------------------
 # our arm
 # ---------------------------------------------------------------------------------------------------
 def run_ours(args) -> None:
@@ -233,7 +349,20 @@ def run_ours(args) -> None:
     for _ in range(max(args.warmup, 3)):
         step()
     pkg.device_status()
-    sampler = ClockSampler(local_rank)
+    shard_check = None
+    if dist is not None and not args.no_check:
+        # every rank checks its own shard (untimed); the line reports the all-ranks verdict
+        mine = check_shard_against_oracle(pkg, torch, cases[0]["A"], cases[0]["B"], Cd)
+        flags = torch.tensor([1 if mine["passed"] else 0, 1 if mine["bit_identical"] else 0], dtype=torch.int32, device=dev)
+        dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        shard_check = dict(mine, all_ranks_passed=bool(flags[0].item() == 1), all_ranks_bit_identical=bool(flags[1].item() == 1),
+                           what="C of this rank's column shard on sampled 32-row blocks and the B pattern bytes in full "
+                                "against the CPU oracle, before the timed region; flags all-reduced (MIN) over the ranks")
+    try:
+        gpu_uuid = "GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)
+    except Exception:
+        gpu_uuid = None
+    sampler = ClockSampler(local_rank, gpu_uuid)
     if rank == 0:
         sampler.start()
     barrier()
@@ -292,6 +421,7 @@ def run_ours(args) -> None:
         del ws_t, Ct
         density = bin(c["pat"]).count("1") / 8.0
         exec_flops = flops_dense_local * density           # uniform pattern: joint density = pattern density
+        ref_cols = ref_kernel_times(M, Nl, K, c["A"], c["B"], both_ms, dev) if world == 1 else None
         pre_bytes = 4.0 * M * K + ap_bytes + 4.0 * M * K * density   # read A, write patterns, write live packed rows
         sweep[c["name"]] = {
             "joint_density": density,
@@ -305,6 +435,7 @@ def run_ours(args) -> None:
             "frac_of_nominal_fp32_peak": exec_flops / (gemm_ms * 1e-3) / 1e12 / NOMINAL_FP32_TFLOPS,
             "preprocess_gbs": pre_bytes / (pre_ms * 1e-3) / 1e9,
             "preprocess_frac_of_hbm": pre_bytes / (pre_ms * 1e-3) / 1e9 / hbm_peak,
+            "reference_kernels": ref_cols,
             "tf32x3": {"ms_total": tf_ms, "speedup_vs_cublas_incl_pre": cub_ms / tf_ms,
                        "speedup_vs_fp32_path": both_ms / tf_ms, "live_k": tf_live_k,
                        "rel_inf_vs_fp32_path": tf_err,
@@ -314,6 +445,8 @@ def run_ours(args) -> None:
         pre_ms_sum += pre_ms
         exec_flops_sum += exec_flops
     pkg.device_status()
+    other = other_config_rows(pkg, torch, dev, time_each) if (world == 1 and workload == "c2" and not args.size
+                                                            and not args.no_other_configs) else None
     achieved = exec_flops_sum / (gemm_ms_sum * 1e-3) / 1e12
     roofline = {
         "kernel": "esmm_joint_sgemm_packed_kernel", "bound": "fp32",
@@ -501,11 +634,31 @@ def run_ours(args) -> None:
                       % (len(cases) * (2 * 4.0 * M * K + 4.0 * K * Nl) / 1e6 + 4.0 * M * Nl / 1e6),
                 "parallelism": "N-column shards, no collective" if world > 1 else "1 GPU",
             },
-            "sweep": sweep, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
+            "sweep": sweep, "other_configs": other, "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e,
             "gpu_launches": int(args.steps * len(cases) * 2), "clocks": clocks,
             "ffma_peak_tflops_measured": ffma_peak, "hbm_peak_gbs": hbm_peak, "hbm_peak_source": hbm_src,
             "sm_count": sms, "gather_c": gather, "scaling_base": scaling_base,
         }
+        cfg = line["config"]
+        # compact copies inside `config`: ours / cuBLAS / reference id 29 per density, the one-GPU base of the
+        # sharded workload, the shard check
+        cfg["ms_ours_cublas_ref29"] = {
+            k: [round(v["ms_total"], 4), round(v["ms_cublas"], 4),
+                round(v["reference_kernels"]["ms_ref_id29"], 4) if v.get("reference_kernels") and
+                "ms_ref_id29" in v["reference_kernels"] else None] for k, v in sweep.items()}
+        if other:
+            cfg["ms_ours_cublas_ref29_other"] = {
+                k: [round(v["ms_total"], 4), round(v["ms_cublas"], 4),
+                    round(v["reference_kernels"]["ms_ref_id29"], 4) if v.get("reference_kernels") and
+                    "ms_ref_id29" in v["reference_kernels"] else None] for k, v in other.items()}
+        if scaling_base:
+            cfg["scaling_base_tflops"] = scaling_base["value"]
+            cfg["scaling_base_ms_per_step"] = scaling_base["ms_per_step"]
+            cfg["scaling_base_workload"] = scaling_base["workload"]
+            if workload == "c5":
+                cfg["speedup_vs_1gpu"] = value / scaling_base["value"]
+        if shard_check is not None:
+            cfg["shard_check"] = shard_check
         # the optional 3xTF32 tensor-core entry point on the same inputs, as one step of the same cases: not `value`
         # (its results are inside the 1e-4 tolerance but not the FP32 path's bits), rank 0's shard at N > 1
         tf_ms = sum(v["tf32x3"]["ms_total"] for v in sweep.values())
@@ -537,6 +690,8 @@ def main() -> None:
     ap.add_argument("--chunks", type=int, default=8, help="row chunks of the host-buffer pipeline")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-scaling-base", action="store_true", help="skip the single-GPU run of the multi-GPU workload")
+    ap.add_argument("--no-check", action="store_true", help="skip the untimed oracle check of the shards (N > 1)")
+    ap.add_argument("--no-other-configs", action="store_true", help="skip the config 3 / config 4 comparison rows")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)

@@ -63,6 +63,8 @@ _SIGNATURES = {
     "esmm_sgemm_joint": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp]),
     "esmm_sgemm_joint_static": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp]),
     "esmm_device_status": (_i, [_vp]),
+    "esmm_tuning_set": (_i, [C.c_char_p, _i]),
+    "esmm_tuning_reset": (None, []),
     "esmm_selftest_bounded_wait": (_i, [C.c_uint, _vp]),
     "esmm_tf32x3_b_create": (_i, [_vp, _i, _i, _i, C.POINTER(_vp)]),
     "esmm_tf32x3_b_destroy": (None, [_vp]),

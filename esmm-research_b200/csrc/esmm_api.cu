@@ -4,6 +4,7 @@
 #include <cublas_v2.h>
 
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
@@ -40,6 +41,30 @@ int record_cuda_error(cudaError_t e, const char *what)
     snprintf(g_cuda_error, sizeof g_cuda_error, "%s: %s", what, cudaGetErrorString(e));
     cudaGetLastError();  // clear the sticky-free error state
     return ESMM_ERR_CUDA;
+}
+
+// ---------------------------------------------------------------------------
+// tuning / test hooks: a fixed table of named integers, unset by default
+// ---------------------------------------------------------------------------
+static const char *const kTuningNames[] = {"TILE_M", "STAGES", "BROW_BITS", "ROW_DENSITY", "FORCE_LISTED", "NO_RUN_TILES",
+                                           "VEC_PATTERNS", "NO_SKINNY", "GRID", "PACK", "SWIZZLE", "TF32_PAIR",
+                                           "TF32_SPLIT_LAST", "TF32_DIRECT_STORES"};
+constexpr int kTuningCount = (int)(sizeof kTuningNames / sizeof kTuningNames[0]);
+static std::atomic<int> g_tuning_value[kTuningCount];
+static std::atomic<bool> g_tuning_set[kTuningCount];
+
+static int tuning_index(const char *name)
+{
+    if (!name) return -1;
+    for (int i = 0; i < kTuningCount; ++i)
+        if (strcmp(name, kTuningNames[i]) == 0) return i;
+    return -1;
+}
+
+int tuning_get(const char *name, int dflt)
+{
+    const int i = tuning_index(name);
+    return (i >= 0 && g_tuning_set[i].load(std::memory_order_acquire)) ? g_tuning_value[i].load() : dflt;
 }
 
 __device__ int g_esmm_device_status;
@@ -263,7 +288,21 @@ const char *esmm_strerror(int status)
 }
 
 const char *esmm_last_cuda_error(void) { return esmm::g_cuda_error; }
-int esmm_version(void) { return 100; }
+int esmm_version(void) { return 110; }
+
+int esmm_tuning_set(const char *name, int value)
+{
+    const int i = esmm::tuning_index(name);
+    if (i < 0) return ESMM_ERR_UNSUPPORTED;
+    esmm::g_tuning_value[i].store(value);
+    esmm::g_tuning_set[i].store(true, std::memory_order_release);
+    return ESMM_OK;
+}
+
+void esmm_tuning_reset(void)
+{
+    for (int i = 0; i < esmm::kTuningCount; ++i) esmm::g_tuning_set[i].store(false, std::memory_order_release);
+}
 
 int esmm_pattern_from_string(const char *s)
 {
@@ -726,16 +765,28 @@ int esmm_run_kernel_pattern(int kernel_id, int rows, int cols, int inners, float
     if (kernel_id == 15) {
         // run_cuBlas (include/runners.cuh:109-139): handle per call, runs back to back, one sync.
         cublasHandle_t handle;
-        if (cublasCreate(&handle) != CUBLAS_STATUS_SUCCESS) return esmm::record_cuda_error_text("cublasCreate failed");
+        if (cublasCreate(&handle) != CUBLAS_STATUS_SUCCESS) {
+            cudaEventDestroy(start);
+            cudaEventDestroy(stop);
+            return esmm::record_cuda_error_text("cublasCreate failed");
+        }
         const float alpha = 1.0f, beta = 0.0f;
-        cudaEventRecord(start);
-        for (int i = 0; i < runs; ++i)
-            cublasSgemm(handle, CUBLAS_OP_N, CUBLAS_OP_N, cols, rows, inners, &alpha, d_B, cols, d_A, inners,
-                        &beta, d_C, cols);
-        cudaDeviceSynchronize();
-        cudaEventRecord(stop);
-        cudaEventSynchronize(stop);
+        cublasStatus_t cst = CUBLAS_STATUS_SUCCESS;
+        cudaError_t ce = cudaEventRecord(start);
+        for (int i = 0; i < runs && cst == CUBLAS_STATUS_SUCCESS; ++i)
+            cst = cublasSgemm(handle, CUBLAS_OP_N, CUBLAS_OP_N, cols, rows, inners, &alpha, d_B, cols, d_A, inners,
+                              &beta, d_C, cols);
+        if (ce == cudaSuccess) ce = cudaDeviceSynchronize();
+        if (ce == cudaSuccess) ce = cudaEventRecord(stop);
+        if (ce == cudaSuccess) ce = cudaEventSynchronize(stop);
         cublasDestroy(handle);
+        if (cst != CUBLAS_STATUS_SUCCESS) {
+            char buf[64];
+            snprintf(buf, sizeof buf, "cublasSgemm failed with status %d", (int)cst);
+            st = esmm::record_cuda_error_text(buf);
+        } else if (ce != cudaSuccess) {
+            st = esmm::record_cuda_error(ce, "cuBLAS baseline loop");
+        }
     } else {
         if (print_stats && !single_operand) {
             esmm_ab_pattern_metadata meta;
@@ -855,6 +906,9 @@ int esmm_run_kernel_pattern(int kernel_id, int rows, int cols, int inners, float
     cudaEventDestroy(start);
     cudaEventDestroy(stop);
     printf("Kernel time: %.3f ms (avg: %.3f ms)\n", ms, ms / runs);
+    if (kernel_id == 129)
+        printf("  (id 129: B is split and its patterns are prepared once, outside the timed loop; ids 20-30 recompute\n"
+               "   B's patterns in every run unless cached patterns are supplied)\n");
     if (avg_ms) *avg_ms = ms / runs;
 
     if (st != ESMM_OK) {

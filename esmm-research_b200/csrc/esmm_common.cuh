@@ -24,6 +24,10 @@ int record_cuda_error_text(const char *text);
         if (_e != cudaSuccess) return esmm::record_cuda_error(_e, #expr); \
     } while (0)
 
+// Tuning and test hooks (esmm_tuning_set): the value set for `name`, else `dflt`.  Nothing is read
+// from the process environment.
+int tuning_get(const char *name, int dflt);
+
 // Device status word shared by all kernels of the library (0 = ok).
 int *device_status_ptr();  // device address, valid after the first call on the current device
 

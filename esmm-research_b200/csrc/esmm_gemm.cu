@@ -478,8 +478,8 @@ int gemm_ab_launch(int M, int N, int K, const float *d_A, const float *d_B, floa
     p.tiles_m = ceil_div(M, TILE_M);
     p.tiles_n = ceil_div(N, TILE_N);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.swizzle = env_int("ESMM_SWIZZLE", 1) ? 1 : 0;
-    p.brow_bits = env_int("ESMM_BROW_BITS", 2);
+    p.swizzle = tuning_get("SWIZZLE", 1) ? 1 : 0;
+    p.brow_bits = tuning_get("BROW_BITS", 2);
     if (p.brow_bits < 0) p.brow_bits = 0;
     if (p.brow_bits > 8) p.brow_bits = 8;
     p.a_pat = d_a_pat;
@@ -487,7 +487,7 @@ int gemm_ab_launch(int M, int N, int K, const float *d_A, const float *d_B, floa
     p.C = d_C;
     if (p.nKB > 65535) return ESMM_ERR_TOO_LARGE;
 
-    int stages = env_int("ESMM_STAGES", MAX_STAGES);
+    int stages = tuning_get("STAGES", MAX_STAGES);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     if (stages < 2) stages = 2;
     while (stages > 2 && smem_layout(stages, p.nKBpad).total > SMEM_LIMIT) --stages;
@@ -517,7 +517,7 @@ int gemm_ab_launch(int M, int N, int K, const float *d_A, const float *d_B, floa
 
     ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        (int)L.total));
-    int grid = env_int("ESMM_GRID", sms);
+    int grid = tuning_get("GRID", sms);
     if (grid > p.num_tiles) grid = p.num_tiles;
     if (grid < 1) grid = 1;
     esmm_joint_sgemm_kernel<<<grid, GEMM_THREADS, L.total, stream>>>(map_a, map_b_box, map_b_row, p);

@@ -897,21 +897,21 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     const long t128 = (long)panels * p.tiles_n, t64 = (long)ceil_div(M, 64) * p.tiles_n;
     const double cost128 = (double)((t128 + sms - 1) / sms), cost64 = 0.55 * (double)((t64 + sms - 1) / sms);
     int tile_rows = cost64 < cost128 ? 64 : TILE_M;
-    const int forced_rows = env_int("ESMM_TILE_M", 0);
+    const int forced_rows = tuning_get("TILE_M", 0);
     if (forced_rows == 64 || forced_rows == TILE_M) tile_rows = forced_rows;
     p.tiles_m = ceil_div(M, tile_rows);
     p.num_tiles = p.tiles_m * p.tiles_n;
-    p.brow_bits = env_int("ESMM_BROW_BITS", 6);
+    p.brow_bits = tuning_get("BROW_BITS", 6);
     if (p.brow_bits < 0) p.brow_bits = 0;
     if (p.brow_bits > 8) p.brow_bits = 8;
-    p.row_density = env_int("ESMM_ROW_DENSITY", 6);
-    p.force_listed = env_int("ESMM_FORCE_LISTED", 0);
-    p.no_run_tiles = env_int("ESMM_NO_RUN_TILES", 0);
+    p.row_density = tuning_get("ROW_DENSITY", 6);
+    p.force_listed = tuning_get("FORCE_LISTED", 0);
+    p.no_run_tiles = tuning_get("NO_RUN_TILES", 0);
     const uintptr_t pat_bits = (uintptr_t)d_a_pat | (uintptr_t)d_b_pat;
     p.vec_patterns = 0;
     if (p.nKB % 4 == 0 && (pat_bits & 3) == 0) p.vec_patterns = 4;
     if (p.nKB % 16 == 0 && (pat_bits & 15) == 0 && p.nKB >= 512) p.vec_patterns = 16;
-    const int forced_vec = env_int("ESMM_VEC_PATTERNS", -1);   // 0, 4, 16: tuning and tests
+    const int forced_vec = tuning_get("VEC_PATTERNS", -1);   // 0, 4, 16: tuning and tests
     if (forced_vec == 0 || (forced_vec == 4 && p.vec_patterns >= 4) ||
         (forced_vec == 16 && p.nKB % 16 == 0 && (pat_bits & 15) == 0))
         p.vec_patterns = forced_vec;
@@ -919,7 +919,7 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     p.b_pat = d_b_pat;
     p.C = d_C;
 
-    int stages = env_int("ESMM_STAGES", P_MAX_STAGES);
+    int stages = tuning_get("STAGES", P_MAX_STAGES);
     if (stages > P_MAX_STAGES) stages = P_MAX_STAGES;
     if (stages < 2) stages = 2;
     while (stages > 2 && packed_smem_layout(stages, p.cap).total > SMEM_LIMIT) --stages;
@@ -960,7 +960,7 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     }
     if (st) return st;
 
-    int grid = env_int("ESMM_GRID", sms);
+    int grid = tuning_get("GRID", sms);
     if (grid > p.num_tiles) grid = p.num_tiles;
     if (grid < 1) grid = 1;
     if (tile_rows == 64) {

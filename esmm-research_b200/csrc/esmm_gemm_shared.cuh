@@ -101,10 +101,4 @@ inline int make_map_3d(CUtensorMap *map, const void *base, uint64_t d0, uint64_t
     return ESMM_OK;
 }
 
-inline int env_int(const char *name, int dflt)
-{
-    const char *s = getenv(name);
-    return (s && *s) ? atoi(s) : dflt;
-}
-
 }  // namespace esmm

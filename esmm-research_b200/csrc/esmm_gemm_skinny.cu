@@ -216,7 +216,7 @@ extern "C" int esmm_sk_trace_read(unsigned long long *host, int n)
 bool gemm_ab_skinny_applies(int M, int N, int K)
 {
     const int kp = ceil_div(K, BK) * BK;
-    return M <= SK_ROWS && kp <= SK_MAX_KP && N >= 4 * SK_COLS && env_int("ESMM_NO_SKINNY", 0) == 0;
+    return M <= SK_ROWS && kp <= SK_MAX_KP && N >= 4 * SK_COLS && tuning_get("NO_SKINNY", 0) == 0;
 }
 
 int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,

@@ -1056,9 +1056,9 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     // partly filled last wave counts half when its tiles can be split along K.  Small problems therefore take the
     // smaller tiles (1024^2 x 4096: 97 us on 256 x 128 pairs, 105 us on single CTAs, 137 us on 256 x 256 pairs), large
     // ones the 256 x 256 pairs.  ESMM_TF32_PAIR = 0 | 128 | 256 overrides the choice.
-    const int pair_env = env_int("ESMM_TF32_PAIR", -1);
+    const int pair_env = tuning_get("TF32_PAIR", -1);
     const int pairs_all = std::max(1, sms / 2);
-    const bool can_split = groups >= 12 && env_int("ESMM_TF32_SPLIT_LAST", 1) != 0;
+    const bool can_split = groups >= 12 && tuning_get("TF32_SPLIT_LAST", 1) != 0;
     int nb = 0;
     {
         auto pair_waves = [&](int tiles) {
@@ -1130,7 +1130,7 @@ int esmm_sgemm_joint_tf32x3(int M, const float *d_A, const esmm_tf32x3_b *b, flo
     size_t smem = ring + 2 * ((p.cap * 2 + 15) & ~15) + 16 * 8 + 32;
     if (smem > (size_t)SMEM_LIMIT) return ESMM_ERR_TOO_LARGE;
     const size_t staging = (size_t)epi_warps * T_STAGE_FLOATS * 4;
-    if (smem + staging <= (size_t)SMEM_LIMIT && env_int("ESMM_TF32_DIRECT_STORES", 0) == 0) {
+    if (smem + staging <= (size_t)SMEM_LIMIT && tuning_get("TF32_DIRECT_STORES", 0) == 0) {
         p.stage_off = (int)smem;                               // a multiple of 16
         smem += staging;
     }

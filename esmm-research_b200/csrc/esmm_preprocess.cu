@@ -15,13 +15,6 @@ namespace esmm {
 constexpr int PRE_THREADS = 128;
 
 // `v != 0.0f` as an integer test: -0.0f is zero, NaN and denormals are nonzero.
-// environment knob for tuning (read at every launch)
-static int env_int_pre(const char *name, int dflt)
-{
-    const char *v = getenv(name);
-    return v && *v ? atoi(v) : dflt;
-}
-
 __device__ __forceinline__ unsigned nz(float v) { return (__float_as_uint(v) << 1) != 0u; }
 
 __device__ __forceinline__ unsigned nz4(const float4 &v)
@@ -322,7 +315,7 @@ int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, flo
     const int nMB = ceil_div(M, 32), nKB = ceil_div(K, BK);
     const int sms = sm_count();
     if (sms <= 0) return record_cuda_error_text("no CUDA device");
-    if (env_int_pre("ESMM_PACK", 64) == 64) {
+    if (tuning_get("PACK", 64) == 64) {
         const int k_chunks = ceil_div(K, 64);
         const long tasks = (long)nMB * k_chunks;
         static bool attr64_set[64] = {false};

@@ -173,7 +173,10 @@ int esmm_sgemm_joint(int M, int N, int K, const float *d_A, const float *d_B, fl
  *   - Cost: every GPU that loads the library holds the 32 MiB + 64 KiB array until the library
  *     is unloaded.
  *   - The first call on each device looks up the array's device address (with that device
- *     current); make that first call before any stream capture begins.
+ *     current); make that first call before any stream capture begins.  It is also the call
+ *     that may make the CUDA runtime load this library's device code, which is when the driver
+ *     sets the array aside: a host whose allocator is about to claim all free memory should make
+ *     one (small) call first, at initialisation.
  *   - All calls on a GPU share the array and it keeps the previous call's contents (nothing in it
  *     needs clearing).  Calls whose kernels overlap on one GPU race on it: serialise them.
  */
@@ -193,6 +196,20 @@ int esmm_device_status(void *stream);
  * has no device-side waits and no counterpart.
  */
 int esmm_selftest_bounded_wait(unsigned budget_us, void *stream);
+
+/*
+ * Tuning and test hooks.  The launch heuristics (tile height, ring depth, row-fetch policy, grid size,
+ * which kernel variant runs) can be overridden per process by name; tests use this to force every
+ * variant through the same parity cases.  Nothing is read from the environment: a caller's
+ * environment cannot change what the library does.  No counterpart in the reference, whose tile
+ * shapes are compile-time template constants (include/runners.cuh:830-838).
+ * Names: TILE_M (64 | 128), STAGES, BROW_BITS, ROW_DENSITY, FORCE_LISTED, NO_RUN_TILES, VEC_PATTERNS
+ * (0 | 4 | 16), NO_SKINNY, GRID, PACK (64 | 128), SWIZZLE, TF32_PAIR (0 | 128 | 256), TF32_SPLIT_LAST,
+ * TF32_DIRECT_STORES.  esmm_tuning_set returns ESMM_ERR_UNSUPPORTED for any other name;
+ * esmm_tuning_reset returns every hook to "unset" (the library's own choice).
+ */
+int esmm_tuning_set(const char *name, int value);
+void esmm_tuning_reset(void);
 
 /* ---- host-buffer (end-to-end) path -------------------------------------- */
 
@@ -234,7 +251,7 @@ int esmm_ffma_peak_tflops(double *tflops, int *sm_count);
  * registers.  C agrees with esmm_gemm_ab to a few 1e-6 of max |C| (inside the 1e-4 bound the FP32 path is
  * held to) but is NOT bit-identical to it.  Requires K % 8 == 0, N % 4 == 0, finite inputs.  Tiles of 256 x 256 or
  * 256 x 128 run on pairs of CTAs (cta_group::2), tiles of 128 x 128 on one CTA; the library picks by the number of
- * tiles (environment ESMM_TF32_PAIR=0 | 128 | 256 forces the single-CTA kernel, 256 x 128 or 256 x 256 per pair).
+ * tiles (esmm_tuning_set("TF32_PAIR", 0 | 128 | 256) forces the single-CTA kernel, 256 x 128 or 256 x 256 per pair).
  * Work is skipped at two levels: k with an all-zero row of B are dropped from both operands when B is prepared
  * (compact != 0), and of what is left a tile multiplies only the 8-wide K blocks in which its A and
  * B patterns share a live k.

@@ -211,9 +211,22 @@ def ref() -> C.CDLL:
         R.ref_preprocess_ab_32.argtypes = [vp, vp, C.c_int, C.c_int, C.c_int, vp, vp]
         R.ref_esmm_v3_launch.argtypes = [C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp]
         R.ref_run_esmm_ab_optimized_v3_no_check.argtypes = [C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_int]
+        fp = C.POINTER(C.c_float)
+        R.ref_time_kernels_v3.argtypes = [C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp, C.c_int, C.c_int, fp, fp, fp]
         R.ref_run_esmm_ab_optimized_v3_skip_stats.argtypes = [C.c_int, C.c_int, C.c_int, vp, vp, vp, C.c_int]
         _ref = R
     return _ref
+
+
+def ref_time_kernels(M, N, K, d_A, d_B, d_C, d_a_pat, d_b_pat, warmup=2, runs=5):
+    """(ms preprocess A, ms preprocess B, ms kernel id 29) of the reference's own kernels on device buffers
+    (raw pointers), CUDA-event averages; raises if the shape is outside the reference kernel's limits."""
+    a, b, g = C.c_float(0), C.c_float(0), C.c_float(0)
+    e = ref().ref_time_kernels_v3(M, N, K, d_A, d_B, d_C, d_a_pat, d_b_pat, warmup, runs,
+                                  C.byref(a), C.byref(b), C.byref(g))
+    if e != 0:
+        raise RuntimeError(f"reference kernels failed or shape unsupported: cudaError {e}")
+    return float(a.value), float(b.value), float(g.value)
 
 
 def ref_sgemm_cpu(A, B, rows=None, threads: int = 1) -> np.ndarray:

@@ -124,6 +124,51 @@ int ref_run_esmm_ab_optimized_v3_no_check(int rows, int cols, int inners, float 
     return run_esmm_ab_optimized_v3_no_check(rows, cols, inners, dA, dB, dC, runs) ? 1 : 0;
 }
 
+// CUDA-event times of the reference's own kernels on caller-provided buffers, each averaged over
+// `runs` back-to-back launches after `warmup`: preprocess_a_patterns_kernel<8,32,256> and
+// preprocess_b_patterns_kernel<8,32,256> with preprocess_ab's launch shapes
+// (src/preprocessors/ab_preprocessor.cu:317-323) and kernel id 29 through dispatch_v3 with
+// its runner's grid (include/runners.cuh:830-841).  The pattern arrays are written by the
+// preprocessors and read by the GEMM.  Shapes must satisfy the reference kernel's own limits
+// (M % 64 == 0, N % 128 == 0, K % 8 == 0, K <= 8192); returns a cudaError_t.
+int ref_time_kernels_v3(int M, int N, int K, float *dA, float *dB, float *dC, uint8_t *d_a_pat,
+                        uint8_t *d_b_pat, int warmup, int runs, float *ms_pre_a, float *ms_pre_b,
+                        float *ms_gemm)
+{
+    if (M % 64 || N % 128 || K % 8 || K > 8192 || runs <= 0) return (int)cudaErrorInvalidValue;
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    float *outs[3] = {ms_pre_a, ms_pre_b, ms_gemm};
+    const dim3 blockDim(256), gridDim(CEIL_DIV(N, 128), CEIL_DIV(M, 64));
+    for (int which = 0; which < 3; ++which) {
+        for (int i = 0; i < warmup + runs; ++i) {
+            if (i == warmup) cudaEventRecord(e0);
+            if (which == 0)
+                preprocess_a_patterns_kernel<8, 32, 256><<<M / 32, 256>>>(M, K, dA, d_a_pat);
+            else if (which == 1)
+                preprocess_b_patterns_kernel<8, 32, 256><<<N / 32, 256>>>(K, N, dB, d_b_pat);
+            else
+                dispatch_v3<64, 128, 8, 32, 32, 2, 1, 8, 256>(gridDim, blockDim, K / 8, M, N, K, dA, dB, dC,
+                                                              d_a_pat, d_b_pat);
+        }
+        cudaEventRecord(e1);
+        cudaError_t e = cudaEventSynchronize(e1);
+        if (e == cudaSuccess) e = cudaGetLastError();
+        if (e != cudaSuccess) {
+            cudaEventDestroy(e0);
+            cudaEventDestroy(e1);
+            return (int)e;
+        }
+        float ms = 0.f;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (outs[which]) *outs[which] = ms / runs;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return 0;
+}
+
 // The 11-argument runner with print_skip_stats = true and verify = false
 // (include/runners.cuh:827-887): prints the "=== Skip Stats: ... ===" block of
 // compute_and_print_skip_stats (:636-706) on stdout before its timed loop.

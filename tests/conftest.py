@@ -39,3 +39,20 @@ def cuda():
         pytest.skip("no CUDA device")
     torch.cuda.set_device(0)
     return torch
+
+
+@pytest.fixture
+def tuning(pkg):
+    """Sets the library's named tuning / test hooks (esmm_tuning_set) for one test and clears them afterwards."""
+    L = pkg.lib()
+
+    class Tuning:
+        def __call__(self, name: str, value: int) -> None:
+            assert L.esmm_tuning_set(name.encode(), int(value)) == 0, name
+
+        def reset(self) -> None:
+            L.esmm_tuning_reset()
+    t = Tuning()
+    t.reset()
+    yield t
+    t.reset()

@@ -54,3 +54,12 @@ def test_product_arm_line(pkg, cuda):
         assert row["ms_cublas"] > 0 and row["ms_total"] >= row["ms_gemm"] * 0.98
     assert d["clocks"]["sm_max_mhz"] >= d["clocks"]["sm_mhz"] > 0 and isinstance(d["clocks"]["reasons"], list)
     assert d["cpu_baseline"] is None and d["scaling_base"] is None      # both skipped by the flags above
+    # comparison columns kept inside `config`: [ours, cuBLAS, reference kernel id 29] in ms per density
+    import oracle
+    for pat, (ours, cublas, ref29) in d["config"]["ms_ours_cublas_ref29"].items():
+        assert ours > 0 and cublas > 0
+        if oracle.have_ref():
+            assert ref29 > ours, pat                  # the recompiled reference kernel is the bar to beat
+    assert len(d["other_configs"]) == 5 and any(k.startswith("c4 M=16") for k in d["other_configs"])
+    for row in d["other_configs"].values():
+        assert row["ms_total"] > 0 and 0 < row["joint_density"] < 1

@@ -154,3 +154,16 @@ def test_tf32x3_host_side_without_gpu(pkg):
     assert L.esmm_tf32x3_b_create(None, 64, 64, 1, C.byref(h)) == 1 and not h.value          # ESMM_ERR_NULL before any CUDA call
     assert L.esmm_sgemm_joint_tf32x3(32, None, None, None, None, None) == 1
 
+
+
+def test_tuning_hooks_are_explicit_not_environment(pkg, monkeypatch):
+    """Hooks are set by name through the C ABI; unknown names are refused; the environment is not consulted
+    (no source file of the library calls getenv)."""
+    import glob
+    L = pkg.lib()
+    assert L.esmm_tuning_set(b"TILE_M", 64) == 0 and L.esmm_tuning_set(b"TF32_PAIR", 0) == 0
+    assert L.esmm_tuning_set(b"NO_SUCH_HOOK", 1) == pkg.ERR_UNSUPPORTED and L.esmm_tuning_set(None, 1) == pkg.ERR_UNSUPPORTED
+    L.esmm_tuning_reset()
+    csrc = os.path.join(os.path.dirname(pkg.LIB_PATH), "csrc")
+    for path in glob.glob(os.path.join(csrc, "*")):
+        assert "getenv" not in open(path).read(), path

@@ -158,15 +158,15 @@ def test_preprocess_ab_metadata(cuda, pkg, oracle_mod):
 
 # ---- joint-sparse GEMM: both kernels against the oracle ----------------------------------------------
 @pytest.mark.parametrize("pat", [0xFF, 0x0F, 0x03, 0x01, 0xA5, 0x80, 0x3C])
-def test_gemm_uniform_patterns(cuda, pkg, oracle_mod, monkeypatch, pat):
+def test_gemm_uniform_patterns(cuda, pkg, oracle_mod, tuning, pat):
     """Tiles whose K blocks all hold the same run of 1, 2, 4 or 8 consecutive live k need no row list (0xFF,
     0x0F, 0x03, 0x01, 0x80, 0x3C here); the same inputs with that shortcut switched off, and patterns that
     are no such run (0xA5), take the general listing."""
     A, B = workloads.uniform_pattern(256, 256, 512, pat, seed=pat)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
-    monkeypatch.setenv("ESMM_NO_RUN_TILES", "1")
+    tuning("NO_RUN_TILES", 1)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
-    monkeypatch.delenv("ESMM_NO_RUN_TILES")
+    tuning.reset()
     # K blocks not a multiple of the stage depth (last stage partial) and a ragged edge tile
     A, B = workloads.uniform_pattern(200, 160, 8 * 21, pat, seed=pat + 1)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
@@ -209,23 +209,23 @@ def test_gemm_llm_mlp_shapes(cuda, pkg, oracle_mod):
         check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
-def test_gemm_long_k_multi_tile_per_cta(cuda, pkg, oracle_mod, monkeypatch):
+def test_gemm_long_k_multi_tile_per_cta(cuda, pkg, oracle_mod, tuning):
     """2048 K blocks (the reference kernel stops at 1024) and several tiles per CTA."""
-    monkeypatch.setenv("ESMM_GRID", "3")
+    tuning("GRID", 3)
     A, B = workloads.tile_random(256, 512, 16384, 0.15, 0.5, seed=4)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
 @pytest.mark.parametrize("stages", [2, 3])
-def test_gemm_shallow_ring(cuda, pkg, oracle_mod, monkeypatch, stages):
-    monkeypatch.setenv("ESMM_STAGES", str(stages))
+def test_gemm_shallow_ring(cuda, pkg, oracle_mod, tuning, stages):
+    tuning("STAGES", int(stages))
     A, B = workloads.tile_random(256, 256, 1024, 0.5, 0.5, seed=11)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
 @pytest.mark.parametrize("brow", [0, 1, 8])
-def test_gemm_row_fetch_policies(cuda, pkg, oracle_mod, monkeypatch, brow):
-    monkeypatch.setenv("ESMM_BROW_BITS", str(brow))
+def test_gemm_row_fetch_policies(cuda, pkg, oracle_mod, tuning, brow):
+    tuning("BROW_BITS", int(brow))
     A, B = workloads.tile_random(256, 256, 512, 0.3, 0.4, seed=12, gran_a=32, gran_b=32)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
     A, B = workloads.uniform_pattern(128, 128, 256, 0x03, seed=1)
@@ -233,11 +233,11 @@ def test_gemm_row_fetch_policies(cuda, pkg, oracle_mod, monkeypatch, brow):
 
 
 @pytest.mark.parametrize("rows", [64, 128])
-def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, monkeypatch, rows):
+def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, tuning, rows):
     """The packed kernel tiles C in 128 x 128 or, where that fills the GPU better, 64 x 128 (a 64-row tile is
     one half of a 128-row panel of packed A).  Both tilings, forced, on uniform, random, ragged and small-M
     inputs: same bits as the oracle."""
-    monkeypatch.setenv("ESMM_TILE_M", str(rows))
+    tuning("TILE_M", int(rows))
     for pat in (0xFF, 0x0F, 0x01, 0x24):
         A, B = workloads.uniform_pattern(384, 256, 512, pat, seed=pat)
         check_all_paths(cuda, pkg, oracle_mod, A, B)
@@ -250,17 +250,17 @@ def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, monkeypatch, rows):
     for M in (16, 48, 96):
         A, B = workloads.llm_mlp(M, 512, 1024, seed=M)
         check_all_paths(cuda, pkg, oracle_mod, A, B)
-    monkeypatch.setenv("ESMM_FORCE_LISTED", "1")
+    tuning("FORCE_LISTED", 1)
     A, B = workloads.uniform_pattern(192, 256, 256, 0x0F, seed=2)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
 @pytest.mark.parametrize("skinny", [1, 0])
-def test_gemm_few_rows(cuda, pkg, oracle_mod, monkeypatch, skinny):
+def test_gemm_few_rows(cuda, pkg, oracle_mod, tuning, skinny):
     """M <= 32 (one pattern block of A) and N >= 128 runs the strip kernel (one CTA per 32 columns); the same
     inputs with that kernel switched off go through the tiled kernel.  Same bits as the oracle either way."""
     if not skinny:
-        monkeypatch.setenv("ESMM_NO_SKINNY", "1")
+        tuning("NO_SKINNY", 1)
     for M, N, K, pa, pb in [(16, 256, 256, 0.5, 0.5), (32, 1408, 1024, 0.4, 0.6), (1, 128, 64, 1.0, 1.0),
                             (31, 132, 8 * 37, 0.7, 0.3), (8, 512, 4096, 0.2, 0.9), (32, 160, 76, 0.8, 0.8),
                             (24, 256, 2048, 0.0, 0.5)]:
@@ -276,10 +276,10 @@ def test_gemm_few_rows(cuda, pkg, oracle_mod, monkeypatch, skinny):
 
 
 @pytest.mark.parametrize("rows", [128, 64])
-def test_gemm_block_structured(cuda, pkg, oracle_mod, monkeypatch, rows):
+def test_gemm_block_structured(cuda, pkg, oracle_mod, tuning, rows):
     """Whole 8-deep blocks live or dead (pattern bytes 0x00 / 0xFF), what pruning at the pattern granularity gives:
     the producers fetch whole K blocks, the consumers' masks come in bytes.  Both tilings, same bits as the oracle."""
-    monkeypatch.setenv("ESMM_TILE_M", str(rows))
+    tuning("TILE_M", int(rows))
     for M, N, K, pa, pb in [(256, 384, 1024, 0.4, 0.5), (384, 256, 8 * 37, 0.7, 0.3), (200, 132, 512, 0.5, 0.9),
                             (128, 128, 2048, 0.15, 0.15), (256, 256, 512, 1.0, 0.5), (256, 256, 512, 0.5, 1.0)]:
         A, B = workloads.block_random(M, N, K, pa, pb, seed=M + N + K)
@@ -293,12 +293,12 @@ def test_gemm_block_structured(cuda, pkg, oracle_mod, monkeypatch, rows):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
-def test_packing_kernel_variants(cuda, pkg, oracle_mod, monkeypatch):
+def test_packing_kernel_variants(cuda, pkg, oracle_mod, tuning):
     """The packing preprocessor has a 32 x 64 task per warp (default) and a 32 x 128 one; both must give the
     oracle's pattern bytes and a packed copy the GEMM turns into the oracle's C (workspace poisoned with NaN
     bit patterns: a dead entry that were read would show)."""
     for variant in ("128", "64"):
-        monkeypatch.setenv("ESMM_PACK", variant)
+        tuning("PACK", int(variant))
         for M, N, K, pa, pb in [(256, 256, 512, 0.5, 0.5), (100, 132, 8 * 37, 0.3, 0.7), (384, 128, 4 * 75, 0.8, 0.4),
                                 (16, 256, 256, 0.5, 0.5), (200, 64, 64, 1.0, 1.0)]:
             A, B = workloads.tile_random(M, N, K, pa, pb, seed=M + K, gran_a=32, gran_b=32)
@@ -371,6 +371,44 @@ def test_against_reference_kernels_live(cuda, pkg, oracle_mod):
     cuda.cuda.synchronize()
     assert np.array_equal(d.gemm_rowmajor(), cref.cpu().numpy())
     assert np.array_equal(d.sgemm_joint()[0], cref.cpu().numpy())
+
+
+def test_skip_stats_against_reference_printout(cuda, pkg, oracle_mod, capfd):
+    """The reference's own runner with print_skip_stats = true (include/runners.cuh:843-850) prints the block of
+    compute_and_print_skip_stats (:636-706); this library's runner must print the same block, character for
+    character, and esmm_skip_stats must return the numbers in it."""
+    if not oracle_mod.have_ref():
+        pytest.skip("oracle/_ref not built")
+    import re
+    R = oracle_mod.ref()
+    L = pkg.lib()
+    M, N, K = 256, 512, 1024
+    A, B = workloads.tile_random(M, N, K, 0.25, 0.3, seed=77, gran_a=32, gran_b=32)
+    A[64:128] = 0.0                                            # whole CTA rows that skip every K tile
+    d = Dev(cuda, pkg, A, B)
+    dC = d.C()
+    capfd.readouterr()
+    assert R.ref_run_esmm_ab_optimized_v3_skip_stats(M, N, K, d.A.data_ptr(), d.B.data_ptr(), dC.data_ptr(), 1) == 1
+    cuda.cuda.synchronize()
+    C.CDLL(None).fflush(None)
+    ref_out = capfd.readouterr().out
+    passed, avg = C.c_int(0), C.c_float(0)
+    assert L.esmm_run_kernel(29, M, N, K, d.A.data_ptr(), d.B.data_ptr(), dC.data_ptr(), None, None, 1, 0, 1,
+                             C.byref(passed), C.byref(avg)) == 0
+    C.CDLL(None).fflush(None)                                  # the library prints through C stdio
+    our_out = capfd.readouterr().out
+
+    def block(text):
+        m = re.search(r"=== Skip Stats: K29 ===\n(.*?\n)\n", text, flags=re.S)
+        assert m, text
+        return m.group(1)
+    assert block(ref_out) == block(our_out)
+    nums = [int(x) for x in re.findall(r":\s+(\d+) / (\d+)", block(ref_out))[0:3] for x in x]
+    ap, bp = oracle_mod.preprocess_a(A), oracle_mod.preprocess_b(B)
+    out = (C.c_longlong * 6)()
+    assert L.esmm_skip_stats(ap.ctypes.data, bp.ctypes.data, M // 64, N // 128, K // 8, 2, 4, 8, C.byref(out)) == 0
+    assert list(out) == nums
+    assert out[0] >= 4 * (K // 8)                              # the zeroed CTA row skips every K tile
 
 
 # ---- config 1 in full: against the driver's CPU SGEMM -----------------------------------------------
@@ -585,13 +623,13 @@ def test_bounded_wait_reports_timeout_and_context_survives(cuda, pkg, oracle_mod
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
-def test_gemm_mask_builder_paths_agree(cuda, pkg, oracle_mod, monkeypatch):
+def test_gemm_mask_builder_paths_agree(cuda, pkg, oracle_mod, tuning):
     """The tile's row list is built from 16-byte pattern loads (long K), 4-byte loads (shorter K) or byte
     by byte (pattern rows that are not a multiple of 4 bytes); all must give the same C."""
     A, B = workloads.tile_random(256, 384, 8192 + 128, 0.3, 0.5, seed=17, gran_a=32, gran_b=32)  # 1040 K blocks
     for mode in ("0", "4", "16"):
-        monkeypatch.setenv("ESMM_VEC_PATTERNS", mode)
+        tuning("VEC_PATTERNS", int(mode))
         check_all_paths(cuda, pkg, oracle_mod, A, B)
-    monkeypatch.delenv("ESMM_VEC_PATTERNS")
+    tuning.reset()
     A, B = workloads.tile_random(256, 256, 8 * 37, 0.5, 0.5, seed=18, gran_a=32, gran_b=32)      # 37 K blocks: bytes
     check_all_paths(cuda, pkg, oracle_mod, A, B)

@@ -66,10 +66,10 @@ def test_tile_random(cuda, pkg, oracle_mod, M, N, K, pa, pb):
 
 
 @pytest.mark.parametrize("pair", ["0", "128", "256"])
-def test_kernel_variants_agree(cuda, pkg, oracle_mod, monkeypatch, pair):
+def test_kernel_variants_agree(cuda, pkg, oracle_mod, tuning, pair):
     """ESMM_TF32_PAIR selects the kernel: 0 = one CTA per 128 x 128 tile, 128 / 256 = a CTA pair (cta_group::2) per
     256 x 128 / 256 x 256 tile (the default where M and N allow).  Ragged sizes, dead K blocks, several tiles per CTA."""
-    monkeypatch.setenv("ESMM_TF32_PAIR", pair)
+    tuning("TF32_PAIR", int(pair))
     for (M, N, K, pa, pb, seed) in [(520, 776, 1032, 0.2, 0.2, 1), (256, 256, 64, 1.0, 1.0, 2), (2048, 2304, 512, 0.5, 0.5, 3)]:
         A, B = workloads.tile_random(M, N, K, pa, pb, seed=seed, gran_a=32, gran_b=32)
         A[300:460] = 0.0                     # a dead band of A: tiles and half-tiles without work
@@ -160,12 +160,12 @@ def test_full_size_agrees_with_fp32_path(cuda, pkg):
 
 
 @pytest.mark.parametrize("pair", ["256", "128"])
-def test_last_round_split_along_k(cuda, pkg, monkeypatch, pair):
+def test_last_round_split_along_k(cuda, pkg, tuning, pair):
     """Shapes whose tiles leave a partly filled last wave: those tiles are computed as two halves of K by two CTA
     pairs that add into a zeroed C.  Same result as without the split to rounding, the same bits on every call,
     and stale contents of C do not leak in."""
     torch = cuda
-    monkeypatch.setenv("ESMM_TF32_PAIR", pair)
+    tuning("TF32_PAIR", int(pair))
     M, N, K = (2560, 2560, 2048) if pair == "256" else (2560, 1280, 2048)     # 100 tiles for 74 pairs: 26 are split
     A, B = workloads.tile_random(M, N, K, 0.6, 0.6, seed=12, gran_a=32, gran_b=32)
     A[:, 1024:1536] = 0.0                                                     # dead groups in the middle of K
@@ -180,7 +180,7 @@ def test_last_round_split_along_k(cuda, pkg, monkeypatch, pair):
     (c1, c2), _ = run_tf32x3(torch, pkg, A, B, calls=2)                        # C starts as NaN in both calls
     assert np.array_equal(c1, c2)
     assert rel_inf(c1, ref) <= TIGHT
-    monkeypatch.setenv("ESMM_TF32_SPLIT_LAST", "0")
+    tuning("TF32_SPLIT_LAST", 0)
     c3, _ = run_tf32x3(torch, pkg, A, B)
     assert rel_inf(c3, ref) <= TIGHT and rel_inf(c1, c3) <= TIGHT
 

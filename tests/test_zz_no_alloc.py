@@ -14,7 +14,7 @@ import workloads
 TOL = 1e-4  # same bound as the other parity tests; the two entry points are in fact bit-identical
 
 
-def _both(cuda, pkg, A, B):
+def _both(cuda, pkg, A, B, expect_no_driver_allocation):
     M, K = A.shape
     N = B.shape[1]
     dA, dB = cuda.from_numpy(A).cuda(), cuda.from_numpy(B).cuda()
@@ -27,10 +27,15 @@ def _both(cuda, pkg, A, B):
     got = cuda.full((M, N), float("nan"), device="cuda")
     cuda.cuda.synchronize()
     before = cuda.cuda.memory_allocated()
+    free_before = cuda.cuda.mem_get_info()[0]      # cudaMemGetInfo: sees every allocation on the device, not only torch's
     pkg.check(pkg.lib().esmm_sgemm_joint_static(M, N, K, dA.data_ptr(), dB.data_ptr(), got.data_ptr(),
                                                 bp.data_ptr(), None), "esmm_sgemm_joint_static")
     pkg.device_status()
     assert cuda.cuda.memory_allocated() == before
+    if expect_no_driver_allocation:
+        # the first call on a device may still load the library's device code (which is when the driver sets the
+        # static array aside); from the second call on the device's free memory must not move at all
+        assert cuda.cuda.mem_get_info()[0] == free_before
     return got.cpu().numpy(), want.cpu().numpy()
 
 
@@ -40,8 +45,8 @@ def test_static_scratch_entry_matches_workspace_entry_twice(cuda, pkg, oracle_mo
     # bytes and stale packed rows of the first call lie all around what the second one writes
     A1, B1 = workloads.tile_random(512, 384, 1024, 0.7, 0.6, seed=51, gran_a=32, gran_b=32)
     A2, B2 = workloads.tile_random(160, 256, 264, 0.2, 0.5, seed=52, gran_a=32, gran_b=32)
-    for A, B in ((A1, B1), (A2, B2), (A1, B1)):
-        got, want = _both(cuda, pkg, A, B)
+    for call, (A, B) in enumerate(((A1, B1), (A2, B2), (A1, B1))):
+        got, want = _both(cuda, pkg, A, B, expect_no_driver_allocation=call > 0)
         assert not np.isnan(got).any()
         assert oracle_mod.rel_inf_err(got, want) <= TOL
         assert np.array_equal(got, want)
