@@ -88,6 +88,16 @@ _SIGNATURES = {
     "esmm_randomize_matrix_a_blocklevel": (_i, [_vp, _i, _i, _i, _i, _f, C.c_uint]),
     "esmm_randomize_matrix_b_blocklevel": (_i, [_vp, _i, _i, _i, _i, _f, C.c_uint]),
     "esmm_print_usage": (None, [C.c_char_p, _i]),
+    "esmm_multi_shard_columns": (_i, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "esmm_multi_create": (_i, [_i, _i, _i, _i, C.POINTER(_i), C.POINTER(_vp)]),
+    "esmm_multi_num_gpus": (_i, [_vp]),
+    "esmm_multi_upload": (_i, [_vp, _vp, _vp]),
+    "esmm_multi_fill": (_i, [_vp, C.c_uint64, _i, C.c_uint8, C.c_uint8, _f, _f, _i]),
+    "esmm_multi_run": (_i, [_vp, _i, C.POINTER(_f), C.POINTER(_f)]),
+    "esmm_multi_download": (_i, [_vp, _vp]),
+    "esmm_multi_gather": (_i, [_vp, _vp, C.POINTER(_f)]),
+    "esmm_multi_gathered_c": (_vp, [_vp]),
+    "esmm_multi_destroy": (_i, [_vp]),
     "esmm_skip_stats": (_i, [_vp, _vp, _i, _i, _i, _i, _i, _i, C.POINTER(C.c_longlong * 6)]),
     "esmm_kernel_id_valid": (_i, [_i]),
     "esmm_kernel_name": (C.c_char_p, [_i]),

@@ -18,7 +18,7 @@ COMMON = ["-O3", "-std=c++17", "-lineinfo"] + ARCH
 
 LIB_SRCS = [os.path.join(HERE, "csrc", f) for f in
             ("esmm_gemm.cu", "esmm_gemm_packed.cu", "esmm_gemm_skinny.cu", "esmm_preprocess.cu", "esmm_api.cu", "esmm_noalloc.cu",
-             "esmm_cusparse.cu", "esmm_gemm_tf32.cu", "esmm_host.cu")]
+             "esmm_cusparse.cu", "esmm_gemm_tf32.cu", "esmm_host.cu", "esmm_multi.cu")]
 LIB_DEPS = LIB_SRCS + [os.path.join(HERE, "csrc", "esmm_common.cuh"), os.path.join(HERE, "csrc", "esmm_gemm_shared.cuh"), os.path.join(ROOT, "include", "esmm.h")]
 EXE_SRCS = [os.path.join(HERE, "driver.cu")]
 EXE_DEPS = EXE_SRCS + [os.path.join(ROOT, "include", h) for h in ("runners.cuh", "utils.cuh", "esmm.h")]
@@ -35,7 +35,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     srcs = [s for s in LIB_SRCS if os.path.exists(s)]
     if force or _stale(LIB, LIB_DEPS):
         cmd = [NVCC] + COMMON + (["-Xptxas", "-v"] if verbose else []) + \
-              ["-Xcompiler", "-fPIC", "-shared", "-o", LIB] + srcs + ["-lcublas", "-lcusparse"]
+              ["-Xcompiler", "-fPIC", "-shared", "-o", LIB] + srcs + ["-lcublas", "-lcusparse", "-ldl"]
         print("+", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)
     if os.path.exists(EXE_SRCS[0]) and (force or _stale(EXE, EXE_DEPS + [LIB])):

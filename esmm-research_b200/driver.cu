@@ -15,12 +15,18 @@
 //   --uniform            N(0,1) values, the pattern applied to A's K columns AND B's K rows of every
 //                        8-slice (joint density = pattern density), generated on the device
 //   --tile-random pA pB  N(0,1) values, independent per-tile patterns at 64-row / 64-column granularity
+//   --tile-gran G        rows of A / columns of B per tile of --tile-random (default 64; a multiple of 32)
+//   --shape M K N        generated data on a non-cubic problem (the reference's --size is cubic only)
 //   --seed S             seed of the two modes above (A uses S, B uses S + 1)
 //   --cpu-check          also compare C with the driver's CPU SGEMM (matrixMultiplyCPU, all host
 //                        threads, relative inf-norm tolerance 1e-4)
 //   --cache-b            keep B's pattern bytes in "<load-b file>.bpat" (or the file given with
 //                        --cache-b-file): loaded when present and matching, else computed once
 //                        and saved; the timed loop then preprocesses A only ("B offline")
+//   --gpus G [--gather]  kernel 29 with B, its patterns and C sharded by columns over G GPUs of this machine, A
+//                        replicated; one process, one host thread per GPU; whole-box time = slowest GPU's device
+//                        time.  --gather collects C on GPU 0 with an NCCL all-gather (timed separately),
+//                        otherwise the shards are copied back device by device
 //   --json               one machine-readable line per kernel
 #include <algorithm>
 #include <cctype>
@@ -82,6 +88,10 @@ struct Options {
     bool uniform = false, tile_random = false, cpu_check = false, json = false, cache_b = false;
     std::string cache_b_file;
     float p_a = 0.5f, p_b = 0.5f;
+    int tile_gran = 64;
+    int gpus = 0;          // 0 = the single-GPU path
+    bool gather = false;
+    int shape_M = 0, shape_K = 0, shape_N = 0;
     unsigned seed = 12345;
     float random_sparsity = 37.5f;
     std::string load_a, load_b;
@@ -160,6 +170,31 @@ int parse_args(int argc, char **argv, Options &o)
             o.tile_random = true;
             o.p_a = (float)atof(argv[++i]);
             o.p_b = (float)atof(argv[++i]);
+        } else if (a == "--gpus") {
+            if (!need(i, 1, "--gpus requires an argument")) return 1;
+            o.gpus = atoi(argv[++i]);
+            if (o.gpus <= 0) {
+                cout << "Error: --gpus must be positive" << endl;
+                return 1;
+            }
+        } else if (a == "--gather") {
+            o.gather = true;
+        } else if (a == "--tile-gran") {
+            if (!need(i, 1, "--tile-gran requires an argument")) return 1;
+            o.tile_gran = atoi(argv[++i]);
+            if (o.tile_gran <= 0 || o.tile_gran % 32) {
+                cout << "Error: --tile-gran must be a positive multiple of 32" << endl;
+                return 1;
+            }
+        } else if (a == "--shape") {
+            if (!need(i, 3, "--shape requires M K N")) return 1;
+            o.shape_M = atoi(argv[++i]);
+            o.shape_K = atoi(argv[++i]);
+            o.shape_N = atoi(argv[++i]);
+            if (o.shape_M <= 0 || o.shape_K <= 0 || o.shape_N <= 0) {
+                cout << "Error: --shape needs three positive sizes" << endl;
+                return 1;
+            }
         } else if (a == "--seed") {
             if (!need(i, 1, "--seed requires an argument")) return 1;
             o.seed = (unsigned)strtoul(argv[++i], nullptr, 10);
@@ -214,7 +249,27 @@ int main(int argc, char **argv)
         o.inners = o.load_K;
         o.cols = o.load_N;
     }
+    if (!load_mode && o.shape_M > 0) {  // generated data on a non-cubic problem (the reference's --size is cubic only)
+        o.rows = o.shape_M;
+        o.inners = o.shape_K;
+        o.cols = o.shape_N;
+    }
     const int M = o.rows, N = o.cols, K = o.inners;
+    if (o.gpus > 0) {
+        // host-side pre-flight, before any device is touched
+        if (esmm_multi_shard_columns(N, o.gpus, 0, nullptr, nullptr) != ESMM_OK) {
+            cout << "Error: N = " << N << " does not split into " << o.gpus << " column shards of a multiple of 128" << endl;
+            return 1;
+        }
+        for (int k : o.kernels)
+            if (k != 29) {
+                cout << "Error: --gpus runs kernel 29 only (got " << k << ")" << endl;
+                return 1;
+            }
+    } else if (o.gather) {
+        cout << "Error: --gather needs --gpus" << endl;
+        return 1;
+    }
 
     if (o.verbose) {
         cout << "Matrix dimensions: " << M << "x" << K << " * " << K << "x" << N << endl;
@@ -250,9 +305,9 @@ int main(int argc, char **argv)
     if (device_generated) {
         const int mode = o.uniform ? 1 : 2;
         const int pa = esmm_pattern_from_string(o.pattern_a.c_str()), pb = esmm_pattern_from_string(o.pattern_b.c_str());
-        int st = esmm_fill_normal(d_A, M, K, 0, o.seed, 0.f, 1.f, 0, mode, (uint8_t)pa, o.p_a, 64, o.seed * 7919u + 1, nullptr);
+        int st = esmm_fill_normal(d_A, M, K, 0, o.seed, 0.f, 1.f, 0, mode, (uint8_t)pa, o.p_a, o.tile_gran, o.seed * 7919u + 1, nullptr);
         if (st == ESMM_OK)
-            st = esmm_fill_normal(d_B, K, N, 1, o.seed + 1, 0.f, 1.f, 0, mode, (uint8_t)pb, o.p_b, 64, o.seed * 7919u + 2, nullptr);
+            st = esmm_fill_normal(d_B, K, N, 1, o.seed + 1, 0.f, 1.f, 0, mode, (uint8_t)pb, o.p_b, o.tile_gran, o.seed * 7919u + 2, nullptr);
         if (st != ESMM_OK) {
             cout << "Error: generator failed: " << esmm_strerror(st) << " " << esmm_last_cuda_error() << endl;
             return 1;
@@ -343,7 +398,54 @@ int main(int argc, char **argv)
     }
 
     int passed = 0;
+    if (o.gpus > 0) {
+        // Kernel 29 on column shards: one process, one host thread per device, A replicated, no exchange in
+        // the compute; the blocks of C come back device by device, or through an NCCL all-gather with --gather.
+        esmm_multi *mg = nullptr;
+        int st = esmm_multi_create(M, N, K, o.gpus, nullptr, &mg);
+        if (st == ESMM_OK) st = esmm_multi_upload(mg, h_A, h_B);
+        std::vector<float> ms_gpu((size_t)o.gpus, 0.f);
+        float ms_max = 0.f, ms_gather = 0.f;
+        if (st == ESMM_OK) st = esmm_multi_run(mg, o.runs, &ms_max, ms_gpu.data());
+        if (st == ESMM_OK) st = o.gather ? esmm_multi_gather(mg, h_C, &ms_gather) : esmm_multi_download(mg, h_C);
+        esmm_multi_destroy(mg);
+        if (st != ESMM_OK) {
+            cout << "Error: multi-GPU run failed: " << esmm_strerror(st) << " " << esmm_last_cuda_error() << endl;
+            return 1;
+        }
+        printf("Kernel time: %.3f ms (avg: %.3f ms)\n", ms_max * o.runs, ms_max);
+        printf("  %d GPUs, column shards of %d; per-GPU avg ms:", o.gpus, N / o.gpus);
+        for (float t : ms_gpu) printf(" %.3f", t);
+        printf("; whole-box dense-equivalent %.1f TFLOP/s\n", 2.0 * M * N * K / (ms_max * 1e-3) / 1e12);
+        if (o.gather) printf("  gather of C to GPU 0 (NCCL all-gather + interleave): %.3f ms\n", ms_gather);
+        bool res = true;
+        if (o.check) res = verifyResults(h_C, h_C_ref, (int)nC);
+        double cpu_rel = -1.0;
+        if (o.cpu_check) {
+            double num = 0.0, den = 0.0;
+            for (size_t i = 0; i < nC; ++i) {
+                num = std::max(num, (double)std::fabs(h_C[i] - h_cpu[i]));
+                den = std::max(den, (double)std::fabs(h_cpu[i]));
+            }
+            cpu_rel = den > 0 ? num / den : num;
+            cout << "CPU SGEMM check: rel-inf error " << cpu_rel << (cpu_rel <= 1e-4 ? " (ok)" : " (FAILED)") << endl;
+            if (cpu_rel > 1e-4) res = false;
+        }
+        if (res) ++passed;
+        cout << "Kernel 29 (" << get_kernel_name(29) << "): "
+             << ((o.check || o.cpu_check) ? (res ? "PASSED" : "FAILED") : "COMPLETED (no verification)") << endl;
+        if (o.json) {
+            printf("{\"kernel\": 29, \"gpus\": %d, \"M\": %d, \"N\": %d, \"K\": %d, \"runs\": %d, \"avg_ms\": %.6f, "
+                   "\"dense_equiv_tflops\": %.3f, \"gather_ms\": %.6f, \"passed\": %s, \"cpu_rel_inf\": %g, \"ms_per_gpu\": [",
+                   o.gpus, M, N, K, o.runs, ms_max, 2.0 * M * N * K / (ms_max * 1e-3) / 1e12, ms_gather, res ? "true" : "false",
+                   cpu_rel);
+            for (int g = 0; g < o.gpus; ++g) printf("%s%.6f", g ? ", " : "", ms_gpu[g]);
+            printf("]}\n");
+        }
+        o.kernels.assign(1, 29);
+    }
     for (int id : o.kernels) {
+        if (o.gpus > 0) break;
         cudaCheckError(cudaMemset(d_C, 0, nC * sizeof(float)));
         if (o.verbose) cout << "Running kernel " << id << ": " << get_kernel_name(id) << (o.check ? "" : " (Performance-only mode)") << endl;
         int ok_flag = 0;

@@ -324,6 +324,50 @@ int esmm_randomize_matrix_b_blocklevel(float *h_mat, int K, int N, int bk, int w
  * id this library adds to the reference's command line. */
 void esmm_print_usage(const char *program_name, int additive);
 
+/* ---- several GPUs of one machine ------------------------------------------ */
+
+/*
+ * N-column sharding from ONE process: C[:, n0:n1] = A * B[:, n0:n1] needs no exchange between the GPUs.
+ * Every device holds all of A (and preprocesses its own replica per run), a contiguous K x N/G block of B's
+ * columns with that block's cached patterns, and the matching M x N/G block of C; one host thread per device
+ * launches its work on a stream of its own.  No counterpart in the reference, which is single-GPU throughout
+ * (no cudaSetDevice, stream or communication call anywhere in its tree); this is what `exec_b200 --gpus G`
+ * runs.  No kernel reads another GPU's memory.
+ *   esmm_multi_shard_columns  columns [n0, n1) of rank `rank`: equal blocks, N % (G * 128) == 0 (whole GEMM
+ *                             tiles and pattern blocks per shard), else ESMM_ERR_SHAPE.  Host arithmetic only.
+ *   esmm_multi_create         validates, allocates every device's buffers (devices == NULL: 0 .. G-1; a device
+ *                             may be named twice, e.g. to exercise the sharding on one GPU - esmm_multi_gather
+ *                             then refuses).  ESMM_ERR_UNSUPPORTED if a device does not exist.
+ *   esmm_multi_upload         host A (M x K) to every device, host B (K x N) column block by column block, and
+ *                             the B patterns of each block ("B offline").  Either pointer may be NULL to keep
+ *                             what is there.
+ *   esmm_multi_fill           device-side generator instead of an upload (esmm_fill_normal): the same A on every
+ *                             device (seed), B's block on rank g from seed + 1 + g.
+ *   esmm_multi_run            `runs` times esmm_sgemm_joint on every device, the devices' loops started together;
+ *                             ms_per_gpu[g] = that device's CUDA-event time per run, *ms_max the slowest (the
+ *                             whole-box time).  A bounded device wait that gave up returns ESMM_ERR_TIMEOUT.
+ *   esmm_multi_download       the blocks of C into a host M x N matrix, device by device, no collective.
+ *   esmm_multi_gather         all of C on the first device: NCCL all-gather of the blocks (NCCL is looked up with
+ *                             dlopen at the first call) + esmm_interleave_shards there; h_C != NULL also copies it
+ *                             to the host; *ms = device time of gather + interleave (slowest device).  Before NCCL
+ *                             is entered every device has reported, on the host, that its buffers exist: a device
+ *                             that failed never enters a collective the others would wait in.  ESMM_ERR_UNSUPPORTED
+ *                             without NCCL or with a device named twice.
+ *   esmm_multi_gathered_c     device pointer (first device) of the gathered M x N matrix, NULL before a gather.
+ */
+typedef struct esmm_multi esmm_multi;
+int esmm_multi_shard_columns(int N, int num_gpus, int rank, int *n0, int *n1);
+int esmm_multi_create(int M, int N, int K, int num_gpus, const int *devices, esmm_multi **out);
+int esmm_multi_num_gpus(const esmm_multi *m);
+int esmm_multi_upload(esmm_multi *m, const float *h_A, const float *h_B);
+int esmm_multi_fill(esmm_multi *m, uint64_t seed, int mode, uint8_t pattern_a, uint8_t pattern_b, float p_a,
+                    float p_b, int gran);
+int esmm_multi_run(esmm_multi *m, int runs, float *ms_max, float *ms_per_gpu);
+int esmm_multi_download(esmm_multi *m, float *h_C);
+int esmm_multi_gather(esmm_multi *m, float *h_C, float *ms);
+const float *esmm_multi_gathered_c(const esmm_multi *m);
+int esmm_multi_destroy(esmm_multi *m);
+
 /* ---- skip statistics ------------------------------------------------------ */
 
 /* compute_and_print_skip_stats arithmetic (include/runners.cuh:636-706) on HOST pattern

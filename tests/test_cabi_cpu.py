@@ -167,3 +167,21 @@ def test_tuning_hooks_are_explicit_not_environment(pkg, monkeypatch):
     csrc = os.path.join(os.path.dirname(pkg.LIB_PATH), "csrc")
     for path in glob.glob(os.path.join(csrc, "*")):
         assert "getenv" not in open(path).read(), path
+
+
+def test_multi_gpu_host_side_validation(pkg):
+    """The sharded entry points validate on the host before touching a device (or NCCL)."""
+    import ctypes as C
+    L = pkg.lib()
+    n0, n1 = C.c_int(-1), C.c_int(-1)
+    assert L.esmm_multi_shard_columns(16384, 8, 3, C.byref(n0), C.byref(n1)) == 0 and (n0.value, n1.value) == (6144, 8192)
+    assert L.esmm_multi_shard_columns(4096, 3, 0, None, None) == pkg.ERR_SHAPE        # not whole tiles per shard
+    assert L.esmm_multi_shard_columns(4096, 2, 2, None, None) == pkg.ERR_SHAPE        # rank out of range
+    assert L.esmm_multi_shard_columns(4096, 0, 0, None, None) == pkg.ERR_SHAPE
+    h = C.c_void_p()
+    assert L.esmm_multi_create(256, 4096, 256, 3, None, C.byref(h)) == pkg.ERR_SHAPE and not h.value
+    assert L.esmm_multi_create(256, 256, 258, 2, None, C.byref(h)) == pkg.ERR_SHAPE
+    assert L.esmm_multi_create(256, 256, 256, 2, None, None) == pkg.ERR_NULL
+    assert L.esmm_multi_run(None, 1, None, None) == pkg.ERR_NULL and L.esmm_multi_gather(None, None, None) == pkg.ERR_NULL
+    assert L.esmm_multi_download(None, None) == pkg.ERR_NULL and L.esmm_multi_destroy(None) == 0
+    assert L.esmm_multi_num_gpus(None) == 0 and not L.esmm_multi_gathered_c(None)

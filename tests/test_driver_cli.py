@@ -34,6 +34,15 @@ def test_help_and_argument_errors(pkg):
     assert rc == 1 and "--size requires an argument" in out
     rc, out = run(pkg, "29", "1", "--load-b", "w.bin")
     assert rc == 1 and "--dims M K N required with --load-a / --load-b" in out
+    # the multi-GPU flags are checked on the host before any device is touched
+    rc, out = run(pkg, "29", "1", "--gpus", "3", "--size", "4096")
+    assert rc == 1 and "does not split into 3 column shards" in out
+    rc, out = run(pkg, "29,15", "1", "--gpus", "2", "--size", "4096")
+    assert rc == 1 and "--gpus runs kernel 29 only" in out
+    rc, out = run(pkg, "29", "1", "--gather", "--size", "256")
+    assert rc == 1 and "--gather needs --gpus" in out
+    rc, out = run(pkg, "29", "1", "--gpus", "0")
+    assert rc == 1 and "--gpus must be positive" in out
 
 
 # ---- runs ---------------------------------------------------------------------------------------
@@ -115,3 +124,14 @@ def test_b_pattern_cache_file(pkg, cuda, tmp_path):
     assert rc == 0 and "B patterns: loaded from" in out and "PASSED" in out
     rc, out = run(pkg, "29", "1", "--load-b", str(path), "--dims", str(M), str(K // 2), str(2 * N), "--cache-b")
     assert "written for another shape, recomputing" in out
+
+
+@pytest.mark.gpu
+def test_gpus_flag_on_one_gpu(pkg, cuda):
+    """--gpus 1: the sharded launcher's degenerate case (one shard) through the CLI, verified against cuBLAS and
+    the CPU SGEMM like any other run."""
+    rc, out = run(pkg, "29", "2", "--gpus", "1", "--uniform", "--pattern", "11000000", "--size", "512", "--cpu-check", "--json")
+    assert rc == 0, out
+    assert "1 GPUs, column shards of 512" in out and "Kernel 29" in out and "PASSED" in out
+    line = json.loads([l for l in out.splitlines() if l.startswith("{")][0])
+    assert line["gpus"] == 1 and line["passed"] is True and len(line["ms_per_gpu"]) == 1 and 0 <= line["cpu_rel_inf"] <= 1e-4

@@ -62,8 +62,9 @@ def test_config3_full_size(cuda, pkg, oracle_mod, pA, pB):
     pkg.fill_normal(dB.data_ptr(), S, S, 1, 12, mode=2, p_live=pB, gran=64, seed2=102)
     _, ap, bp = check_problem(cuda, pkg, oracle_mod, dA, dB)
     # generator granularity 64 against pattern granularity 32: pattern rows come in identical pairs
-    assert np.array_equal(ap[0::2], ap[1::2]) and np.array_equal(bp[0::2], bp[1::2])
-    dens = np.unpackbits(ap).mean(), np.unpackbits(bp).mean()
+    bpn = bp.cpu().numpy()
+    assert np.array_equal(ap[0::2], ap[1::2]) and np.array_equal(bpn[0::2], bpn[1::2])
+    dens = np.unpackbits(ap).mean(), np.unpackbits(bpn).mean()
     assert abs(dens[0] - pA) < 0.01 and abs(dens[1] - pB) < 0.01
 
 
@@ -75,7 +76,7 @@ def test_config4_full_size(cuda, pkg, oracle_mod, M):
     A, B = workloads.llm_mlp(M, N, K, seed=40 + M)
     dA, dB = cuda.from_numpy(A).cuda(), cuda.from_numpy(B).cuda()
     _, ap, bp = check_problem(cuda, pkg, oracle_mod, dA, dB)
-    assert 0.30 < (ap != 0).mean() < 0.50 and 0.40 < (bp != 0).mean() < 0.60
+    assert 0.30 < (ap != 0).mean() < 0.50 and 0.40 < (bp.cpu().numpy() != 0).mean() < 0.60
 
 
 def test_config5_one_shard_full_size(cuda, pkg, oracle_mod):

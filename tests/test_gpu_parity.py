@@ -633,3 +633,33 @@ def test_gemm_mask_builder_paths_agree(cuda, pkg, oracle_mod, tuning):
     tuning.reset()
     A, B = workloads.tile_random(256, 256, 8 * 37, 0.5, 0.5, seed=18, gran_a=32, gran_b=32)      # 37 K blocks: bytes
     check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
+def test_multi_launcher_two_ranks_on_one_gpu(cuda, pkg, oracle_mod):
+    """The C++ sharded launcher (esmm_multi_*) with both ranks placed on device 0: column shards computed by two host
+    threads on two streams must reproduce the unsharded result bit for bit (the shards' kernels are independent -
+    none waits on another).  The NCCL gather refuses a device named twice; the shards come back by download."""
+    L = pkg.lib()
+    M, N, K = 256, 512, 512
+    A, B = workloads.tile_random(M, N, K, 0.5, 0.5, seed=91, gran_a=32, gran_b=32)
+    want = Dev(cuda, pkg, A, B)
+    want.patterns()
+    Cwant, _ = want.sgemm_joint()
+    h = C.c_void_p()
+    devs = (C.c_int * 2)(0, 0)
+    pkg.check(L.esmm_multi_create(M, N, K, 2, devs, C.byref(h)), "esmm_multi_create")
+    try:
+        assert L.esmm_multi_num_gpus(h) == 2
+        assert L.esmm_multi_run(h, 1, None, None) == pkg.ERR_NULL                 # nothing uploaded yet
+        pkg.check(L.esmm_multi_upload(h, A.ctypes.data, B.ctypes.data), "esmm_multi_upload")
+        ms_max, ms = C.c_float(0), (C.c_float * 2)()
+        pkg.check(L.esmm_multi_run(h, 3, C.byref(ms_max), ms), "esmm_multi_run")
+        assert ms_max.value > 0 and ms_max.value == max(ms[0], ms[1])
+        got = np.full((M, N), np.nan, np.float32)
+        pkg.check(L.esmm_multi_download(h, got.ctypes.data), "esmm_multi_download")
+        assert np.array_equal(got, Cwant) and np.array_equal(got, oracle_mod.gemm_joint(A, B))
+        assert L.esmm_multi_gather(h, None, None) == pkg.ERR_UNSUPPORTED            # one rank per device only
+    finally:
+        L.esmm_multi_destroy(h)
+    bad = (C.c_int * 2)(0, 99)
+    assert L.esmm_multi_create(M, N, K, 2, bad, C.byref(h)) == pkg.ERR_UNSUPPORTED
