@@ -15,11 +15,12 @@ import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libesmm_b200.so")
+CHECKED_LIB_PATH = os.path.join(_HERE, "libesmm_b200_checked.so")
 EXE_PATH = os.path.join(_HERE, "exec_b200")
 HEADER_PATH = os.path.join(os.path.dirname(_HERE), "include", "esmm.h")
 
 OK, ERR_NULL, ERR_SHAPE, ERR_ALIGN, ERR_CUDA, ERR_TIMEOUT, ERR_IO, ERR_UNSUPPORTED, ERR_VERIFY, \
-    ERR_TOO_LARGE, ERR_MISMATCH = range(11)
+    ERR_TOO_LARGE, ERR_MISMATCH, ERR_BOUNDS = range(12)
 
 
 class EsmmError(RuntimeError):
@@ -65,6 +66,8 @@ _SIGNATURES = {
     "esmm_device_status": (_i, [_vp]),
     "esmm_tuning_set": (_i, [C.c_char_p, _i]),
     "esmm_tuning_reset": (None, []),
+    "esmm_checked_build": (_i, []),
+    "esmm_selftest_bounds_report": (_i, [_vp]),
     "esmm_selftest_bounded_wait": (_i, [C.c_uint, _vp]),
     "esmm_tf32x3_b_create": (_i, [_vp, _i, _i, _i, C.POINTER(_vp)]),
     "esmm_tf32x3_b_destroy": (None, [_vp]),
@@ -127,6 +130,18 @@ def lib() -> C.CDLL:
             fn.argtypes = args
         _lib = L
     return _lib
+
+
+def load_library(path: str) -> C.CDLL:
+    """Another build of the same ABI (the bounds-checked one) with the typed signatures applied."""
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} is missing: run `python esmm-research_b200/build.py`")
+    L = C.CDLL(path)
+    for name, (res, args) in _SIGNATURES.items():
+        fn = getattr(L, name)
+        fn.restype = res
+        fn.argtypes = args
+    return L
 
 
 def exported_names() -> list[str]:

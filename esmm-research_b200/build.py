@@ -1,4 +1,5 @@
-"""Builds libesmm_b200.so (the C-ABI library), exec_b200 (the driver CLI) and cusparse_bench in-tree with
+"""Builds libesmm_b200.so (the C-ABI library), libesmm_b200_checked.so (the same sources with every computed
+shared- and global-memory index bounds-checked), exec_b200 (the driver CLI) and cusparse_bench in-tree with
 nvcc for sm_100a.  Usage: `python build.py [--force] [--verbose]`."""
 from __future__ import annotations
 
@@ -10,6 +11,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(HERE)
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 LIB = os.path.join(HERE, "libesmm_b200.so")
+LIB_CHECKED = os.path.join(HERE, "libesmm_b200_checked.so")   # same sources with -DESMM_CHECKED: the sanitizer substitute
 EXE = os.path.join(HERE, "exec_b200")
 SPARSE_EXE = os.path.join(HERE, "cusparse_bench")
 SPARSE_SRC = os.path.join(HERE, "cusparse_bench.cu")
@@ -36,6 +38,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if force or _stale(LIB, LIB_DEPS):
         cmd = [NVCC] + COMMON + (["-Xptxas", "-v"] if verbose else []) + \
               ["-Xcompiler", "-fPIC", "-shared", "-o", LIB] + srcs + ["-lcublas", "-lcusparse", "-ldl"]
+        print("+", " ".join(cmd), flush=True)
+        subprocess.check_call(cmd)
+    if force or _stale(LIB_CHECKED, LIB_DEPS):
+        cmd = [NVCC] + COMMON + ["-DESMM_CHECKED", "-Xcompiler", "-fPIC", "-shared", "-o", LIB_CHECKED] + srcs + \
+              ["-lcublas", "-lcusparse", "-ldl"]
         print("+", " ".join(cmd), flush=True)
         subprocess.check_call(cmd)
     if os.path.exists(EXE_SRCS[0]) and (force or _stale(EXE, EXE_DEPS + [LIB])):

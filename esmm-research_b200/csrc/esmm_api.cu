@@ -47,7 +47,7 @@ int record_cuda_error(cudaError_t e, const char *what)
 // tuning / test hooks: a fixed table of named integers, unset by default
 // ---------------------------------------------------------------------------
 static const char *const kTuningNames[] = {"TILE_M", "STAGES", "BROW_BITS", "ROW_DENSITY", "FORCE_LISTED", "NO_RUN_TILES",
-                                           "VEC_PATTERNS", "NO_SKINNY", "GRID", "PACK", "SWIZZLE", "TF32_PAIR",
+                                           "VEC_PATTERNS", "NO_SKINNY", "SKINNY_ROWS", "SKINNY_SHARED", "GRID", "PACK", "SWIZZLE", "TF32_PAIR",
                                            "TF32_SPLIT_LAST", "TF32_DIRECT_STORES"};
 constexpr int kTuningCount = (int)(sizeof kTuningNames / sizeof kTuningNames[0]);
 static std::atomic<int> g_tuning_value[kTuningCount];
@@ -186,6 +186,10 @@ __global__ void esmm_selftest_bounded_wait_kernel(int *status, unsigned long lon
     if (!ok && (threadIdx.x & 31) == 0) atomicExch(status, (int)ESMM_ERR_TIMEOUT);
 }
 
+// Reports a failed bounds check (site 99) without making any access: exercises the checked build's
+// reporting path; in the product build bounds_ok() is the constant true and nothing is recorded.
+__global__ void esmm_selftest_bounds_kernel(int *status) { (void)bounds_ok(false, status, 99); }
+
 static cublasHandle_t cublas_handle_for_device()
 {
     static cublasHandle_t handles[64] = {nullptr};
@@ -283,6 +287,7 @@ const char *esmm_strerror(int status)
     case ESMM_ERR_VERIFY: return "verification failed";
     case ESMM_ERR_TOO_LARGE: return "K too large for the kernel's shared-memory masks";
     case ESMM_ERR_MISMATCH: return "cached patterns do not match the requested shape";
+    case ESMM_ERR_BOUNDS: return "checked build: a kernel computed an index outside its buffer (access skipped)";
     default: return "unknown status";
     }
 }
@@ -355,7 +360,23 @@ int esmm_device_status(void *stream)
     int v = 0;
     ESMM_CUDA_TRY(cudaMemcpy(&v, p, sizeof v, cudaMemcpyDeviceToHost));
     if (v != 0) ESMM_CUDA_TRY(cudaMemset(p, 0, sizeof v));
-    return v;
+    if ((v & 0xFF) == ESMM_ERR_BOUNDS) {
+        char buf[96];
+        snprintf(buf, sizeof buf, "bounds check failed at site %d (see the site numbers beside bounds_ok() in csrc/)", v >> 8);
+        esmm::record_cuda_error_text(buf);
+    }
+    return v & 0xFF;
+}
+
+int esmm_checked_build(void) { return esmm::kCheckedBuild ? 1 : 0; }
+
+int esmm_selftest_bounds_report(void *stream)
+{
+    int *status = esmm::device_status_ptr();
+    if (!status) return ESMM_ERR_CUDA;
+    esmm::esmm_selftest_bounds_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(status);
+    ESMM_CUDA_TRY(cudaGetLastError());
+    return ESMM_OK;
 }
 
 int esmm_selftest_bounded_wait(unsigned budget_us, void *stream)

@@ -33,6 +33,26 @@ int *device_status_ptr();  // device address, valid after the first call on the 
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------
+// Checked build (-DESMM_CHECKED; libesmm_b200_checked.so): the index of every access to shared or
+// global memory that the kernels compute themselves (everything but the copy engine's boxes, which
+// the tensor maps bound in hardware) is tested first.  A failed test records ESMM_ERR_BOUNDS and
+// the number of the site in the device status word - the first failure wins - and the access is
+// skipped: no trap, no fault, the context stays usable and esmm_device_status() reports it.  In the
+// product build bounds_ok() is the constant true and the tests compile away.
+// ---------------------------------------------------------------------------
+#ifdef ESMM_CHECKED
+constexpr bool kCheckedBuild = true;
+#else
+constexpr bool kCheckedBuild = false;
+#endif
+
+__device__ __forceinline__ bool bounds_ok(bool in_bounds, int *status, int site)
+{
+    if (kCheckedBuild && !in_bounds && status) atomicCAS(status, 0, (int)ESMM_ERR_BOUNDS | (site << 8));
+    return !kCheckedBuild || in_bounds;
+}
+
+// ---------------------------------------------------------------------------
 // PTX wrappers: mbarrier, TMA (cp.async.bulk.tensor), timers.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
@@ -73,6 +93,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
         "{\n"
         ".reg .pred p;\n"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// non-blocking: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
         "selp.u32 %0, 1, 0, p;\n"
         "}\n"
         : "=r"(ok)

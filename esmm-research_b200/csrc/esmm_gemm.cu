@@ -276,7 +276,7 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
                         m[4 * i] = (uint8_t)(aw >> (8 * i));
                         m[16 + 4 * i] = (uint8_t)(bw >> (8 * i));
                     }
-                    klist[pos] = (uint16_t)kb;
+                    if (bounds_ok(pos < p.nKBpad, p.status, 40)) klist[pos] = (uint16_t)kb;   // checked build: site 40
                 }
                 base += __popc(bal);
             }
@@ -287,7 +287,7 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
                     uint8_t *m = cmask + (pos >> 2) * MASK_STAGE_BYTES + (pos & 3);
 #pragma unroll
                     for (int i = 0; i < 8; ++i) m[4 * i] = 0;
-                    klist[pos] = 0;
+                    if (bounds_ok(pos < p.nKBpad, p.status, 40)) klist[pos] = 0;
                 }
             }
             if (lane == 0) nlive[buf] = base;
@@ -442,9 +442,10 @@ esmm_joint_sgemm_kernel(const __grid_constant__ CUtensorMap map_a,
                 const int row = row0 + 8 * i;
                 if (row < p.M) {
                     float *c = p.C + (size_t)row * p.N + col0;
-                    if (col0 < p.N)
+                    const size_t c_floats = (size_t)p.M * p.N, off = (size_t)row * p.N + col0;   // checked build: site 41
+                    if (col0 < p.N && bounds_ok(off + 4 <= c_floats, p.status, 41))
                         *reinterpret_cast<float4 *>(c) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
-                    if (col0 + 16 < p.N)
+                    if (col0 + 16 < p.N && bounds_ok(off + 20 <= c_floats, p.status, 41))
                         *reinterpret_cast<float4 *>(c + 16) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
                 }
             }

@@ -103,6 +103,8 @@ struct PackedParams {
     int vec_patterns;  // K blocks per lane and load in the mask warp: 16, 4 (alignment permitting) or 0 = bytes
     const uint8_t *a_pat;
     const uint8_t *b_pat;
+    const float *a_packed;   // the operands themselves, for the producers' plain row copies
+    const float *B;
     float *C;
     int *status;
 };
@@ -113,6 +115,38 @@ struct PackedMaps {
     CUtensorMap a_row, a_kb, a_run[4];
     CUtensorMap b_row, b_kb, b_run[4];
 };
+
+// 16-byte asynchronous copy global -> shared by the executing thread; src_bytes = 0 writes zeros instead
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, int src_bytes)
+{
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// Ties the completion of all cp.async copies the executing thread has issued so far to the barrier's current
+// phase: the pending count goes up by one now and down by one when the copies have landed.
+__device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar)
+{
+    asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// How the producers fetch single rows (rows that are neither part of a whole-stage run nor of an 8-row box):
+//   0  one 2-D tensor copy per row and operand, one lane per row
+//   1  the whole warp copies each row with 16-byte cp.async, completion tied to the stage's barrier
+//   2  one untiled bulk copy (cp.async.bulk) per row and operand, one lane per row; rows that would leave the
+//      matrix (ragged last tile of columns, padding rows of K) take the tensor copy, which fills with zeros
+#ifndef ESMM_ROW_COPY
+#define ESMM_ROW_COPY 0
+#endif
+// arrivals a stage's full barrier expects: the byte count posted by producer 0, plus - when rows come by
+// cp.async - one arrival per other producer warp after it has tied its copies to the barrier
+constexpr int FULL_ARRIVALS = ESMM_ROW_COPY == 1 ? P_TMA_WARPS : 1;
+
+__device__ __forceinline__ void bulk_copy_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
 
 constexpr int RUN_TILE = 0x100;
 
@@ -173,16 +207,28 @@ struct Acc {
     float2 diag[4][4], anti[4][4];
 };
 
+#ifndef ESMM_ANTI_SCALAR
+#define ESMM_ANTI_SCALAR 0
+#endif
+// One 2 x 2 block: the diagonal pair as one two-wide FMA; the anti-diagonal pair either as a second two-wide FMA on
+// the swapped column pair or (ESMM_ANTI_SCALAR) as two scalar FMAs, which need no swapped pair.
+__device__ __forceinline__ void fma_block(float2 &diag, float2 &anti, float2 ar, float bx, float by)
+{
+    diag = __ffma2_rn(ar, make_float2(bx, by), diag);
+#if ESMM_ANTI_SCALAR
+    anti.x = fmaf(ar.x, by, anti.x);
+    anti.y = fmaf(ar.y, bx, anti.y);
+#else
+    anti = __ffma2_rn(ar, make_float2(by, bx), anti);
+#endif
+}
+
 __device__ __forceinline__ void fma_pair_row(Acc &c, int p, float2 ar, const KFrag &f)
 {
-    c.diag[p][0] = __ffma2_rn(ar, make_float2(f.b0.x, f.b0.y), c.diag[p][0]);
-    c.anti[p][0] = __ffma2_rn(ar, make_float2(f.b0.y, f.b0.x), c.anti[p][0]);
-    c.diag[p][1] = __ffma2_rn(ar, make_float2(f.b0.z, f.b0.w), c.diag[p][1]);
-    c.anti[p][1] = __ffma2_rn(ar, make_float2(f.b0.w, f.b0.z), c.anti[p][1]);
-    c.diag[p][2] = __ffma2_rn(ar, make_float2(f.b1.x, f.b1.y), c.diag[p][2]);
-    c.anti[p][2] = __ffma2_rn(ar, make_float2(f.b1.y, f.b1.x), c.anti[p][2]);
-    c.diag[p][3] = __ffma2_rn(ar, make_float2(f.b1.z, f.b1.w), c.diag[p][3]);
-    c.anti[p][3] = __ffma2_rn(ar, make_float2(f.b1.w, f.b1.z), c.anti[p][3]);
+    fma_block(c.diag[p][0], c.anti[p][0], ar, f.b0.x, f.b0.y);
+    fma_block(c.diag[p][1], c.anti[p][1], ar, f.b0.z, f.b0.w);
+    fma_block(c.diag[p][2], c.anti[p][2], ar, f.b1.x, f.b1.y);
+    fma_block(c.diag[p][3], c.anti[p][3], ar, f.b1.z, f.b1.w);
 }
 
 __device__ __forceinline__ void fma_top(Acc &c, const KFrag &f)
@@ -201,13 +247,17 @@ __device__ __forceinline__ void fma_bottom(Acc &c, const KFrag &f)
 // loop trip (measured: 4 rows 1 % slower than 8, 16 rows 1.6 % faster, 32 no better than 16),
 // so that the compiler can issue the loads of a row under the multiply-adds of the row before.
 template <int WMB>
-__device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char *sB)
+__device__ __forceinline__ bool dense_rows(Acc &acc, const char *sA, const char *sB, uint32_t next_full, uint32_t next_parity)
 {
     constexpr int A_ROW = 256 * WMB;   // bytes of one k of the A tile
     // (A rolling prefetch across the loop's back edge was measured slower than this form.)
 #ifndef ESMM_DENSE_UNROLL
 #define ESMM_DENSE_UNROLL 16
 #endif
+#ifndef ESMM_POLL_NEXT
+#define ESMM_POLL_NEXT 0
+#endif
+    bool next_ready = false;
 #pragma unroll 1
     for (int r0 = 0; r0 < ROWS_PER_STAGE; r0 += ESMM_DENSE_UNROLL) {
 #pragma unroll
@@ -216,7 +266,11 @@ __device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char 
             fma_top(acc, f);
             if (WMB == 2) fma_bottom(acc, f);
         }
+        // has the next stage landed already?  One non-blocking look while the multiply-adds above are still in the
+        // pipe: the wait at the stage change is then skipped.
+        if (ESMM_POLL_NEXT && r0 + ESMM_DENSE_UNROLL >= ROWS_PER_STAGE) next_ready = mbar_test_wait(next_full, next_parity);
     }
+    return next_ready;
 }
 
 // ---- stages that are not all-live ------------------------------------------------------------------
@@ -328,11 +382,12 @@ __device__ __forceinline__ void listed_rows(Acc &acc, const char *sA, const char
 }
 
 // Lanes write the list of the rows whose bit is set in `m`; returns the count.
-__device__ __forceinline__ int build_list(uint16_t *list, unsigned m, int lane)
+__device__ __forceinline__ int build_list(uint16_t *list, unsigned m, int lane, int *status)
 {
     const int cnt = __popc(m);
-    if ((m >> lane) & 1u) list[__popc(m & ((1u << lane) - 1u))] = (uint16_t)(lane << 9);
-    if (lane < 8) list[cnt + lane] = 0;
+    const int mine = __popc(m & ((1u << lane) - 1u));
+    if (((m >> lane) & 1u) && bounds_ok(mine < WLIST_ENTRIES, status, 25)) list[mine] = (uint16_t)(lane << 9);
+    if (lane < 8 && bounds_ok(cnt + lane < WLIST_ENTRIES, status, 25)) list[cnt + lane] = 0;
     return cnt;
 }
 
@@ -352,7 +407,7 @@ __device__ __forceinline__ void load_patterns(const PackedParams &p, int tm, int
         const int mb = tm * RB + i, nb = tn * 4 + i;
 #pragma unroll
         for (int w = 0; w < W; ++w) ra[i][w] = rb[i][w] = 0u;
-        if (valid && i < RB && mb < p.a_rows) {
+        if (valid && i < RB && mb < p.a_rows && bounds_ok(kb0 >= 0 && kb0 + KPL <= p.nKB, p.status, 21)) {
             const uint8_t *src = p.a_pat + (size_t)mb * p.nKB + kb0;
             if (KPL == 16) {
                 const uint4 v = *reinterpret_cast<const uint4 *>(src);
@@ -361,7 +416,7 @@ __device__ __forceinline__ void load_patterns(const PackedParams &p, int tm, int
                 ra[i][0] = *reinterpret_cast<const unsigned *>(src);
             }
         }
-        if (valid && nb < p.b_rows) {
+        if (valid && nb < p.b_rows && bounds_ok(kb0 >= 0 && kb0 + KPL <= p.nKB, p.status, 21)) {
             const uint8_t *src = p.b_pat + (size_t)nb * p.nKB + kb0;
             if (KPL == 16) {
                 const uint4 v = *reinterpret_cast<const uint4 *>(src);
@@ -396,7 +451,7 @@ __device__ __forceinline__ unsigned tile_live(unsigned aw, unsigned bw)
 
 // Appends the listed rows of one K block at position q; returns the new position.
 __device__ __forceinline__ int append_rows(uint16_t *krow, uint8_t *rmask, int q, int kb, unsigned rows,
-                                           unsigned aw, unsigned bw)
+                                           unsigned aw, unsigned bw, int cap, int *status)
 {
     while (rows) {
         const int kk = __ffs(rows) - 1;
@@ -404,8 +459,10 @@ __device__ __forceinline__ int append_rows(uint16_t *krow, uint8_t *rmask, int q
         const unsigned as = aw >> kk, bs = bw >> kk;
         const unsigned abits = (as & 1u) | ((as >> 7) & 2u) | ((as >> 14) & 4u) | ((as >> 21) & 8u);
         const unsigned bbits = (bs & 1u) | ((bs >> 7) & 2u) | ((bs >> 14) & 4u) | ((bs >> 21) & 8u);
-        krow[q] = (uint16_t)(kb * BK + kk);
-        rmask[q] = (uint8_t)(abits | (bbits << 4));
+        if (bounds_ok(q < cap, status, 20)) {
+            krow[q] = (uint16_t)(kb * BK + kk);
+            rmask[q] = (uint8_t)(abits | (bbits << 4));
+        }
         ++q;
     }
     return q;
@@ -477,7 +534,7 @@ __device__ __forceinline__ int tile_list(const PackedParams &p, int tm, int tn, 
         const int incl = warp_inclusive_scan(c, lane);
         int q = pos + incl - c;
 #pragma unroll
-        for (int j = 0; j < KPL; ++j) q = append_rows(krow, rmask, q, kb0 + j, rows[j], aw[j], bw[j]);
+        for (int j = 0; j < KPL; ++j) q = append_rows(krow, rmask, q, kb0 + j, rows[j], aw[j], bw[j], p.cap, p.status);
         pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
     }
     return pos;
@@ -510,7 +567,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full0 + 8 * s, 1);
+            mbar_init(full0 + 8 * s, FULL_ARRIVALS);
             mbar_init(empty0 + 8 * s, P_CONSUMER_WARPS);
         }
         for (int b = 0; b < 2; ++b) {
@@ -601,14 +658,14 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     const unsigned rows = live == 0u ? 0u : (__popc(live) > whole_above ? 0xFFu : live);
                     const int c = __popc(rows);
                     const int incl = warp_inclusive_scan(c, lane);
-                    append_rows(krow, rmask, pos + incl - c, kb, rows, aw, bw);
+                    append_rows(krow, rmask, pos + incl - c, kb, rows, aw, bw, p.cap, p.status);
                     pos += __shfl_sync(0xFFFFFFFFu, incl, 31);
                 }
             }
             // rows past the end of the last stage read as dead
             if (!run_code) {
                 const int q = pos + lane;
-                if (q < ((pos + 31) & ~31)) {
+                if (q < ((pos + 31) & ~31) && bounds_ok(q < p.cap, p.status, 22)) {
                     krow[q] = 0;
                     rmask[q] = 0;
                 }
@@ -658,11 +715,14 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     if (!ok) break;
                     const uint32_t full = full0 + 8 * slot;
                     if (q == 0 && lane == 0) {
+                        if (ESMM_ROW_COPY == 1) fence_proxy_async();   // the slot may last have been written by plain copies
                         mbar_arrive_expect_tx(full, (uint32_t)ROWS_PER_STAGE * STAGE_ROW_BYTES);
                         const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
                         const int kb0 = r0 >> lc;
                         tma_load_3d(s0, &maps.a_run[lc], a_x, kk0, panel * p.nKB + kb0, full);
                         tma_load_3d(s0 + STAGE_HALF_BYTES, &maps.b_run[lc], b_col0, kk0, kb0, full);
+                    } else if (FULL_ARRIVALS > 1 && lane == 0) {
+                        mbar_arrive(full);
                     }
                     if (q == 0) {
                         issued_bits |= 1u << slot;
@@ -678,7 +738,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             for (int r0 = 0; r0 < n && !run_code; r0 += ROWS_PER_STAGE) {
                 const int cnt = min(ROWS_PER_STAGE, n - r0);
                 const bool valid = lane < cnt;
-                const int k = valid ? (int)krow[r0 + lane] : -1;
+                const int k = valid && bounds_ok(r0 + lane < p.cap, p.status, 27) ? (int)krow[r0 + lane] : -1;
                 // a uniform run?  rows = k offsets kk0 .. kk0 + c - 1 of 32 / c consecutive K blocks
                 const int k_first = __shfl_sync(0xFFFFFFFFu, k, 0);
                 const int kb0 = k_first >> 3, kk0 = k_first & 7;
@@ -705,13 +765,13 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                 ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
-                if (q == 0 || __any_sync(0xFFFFFFFFu, box8 || row1)) {
+                {
                     const uint32_t full = full0 + 8 * slot;
-                    if (q == 0 && lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * STAGE_ROW_BYTES);
-                    __syncwarp();
                     const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
                     const uint32_t sa = s0 + lane * A_ROW;
                     const uint32_t sb = s0 + STAGE_HALF_BYTES + lane * ROW_BYTES;
+                    // (with cp.async rows the slot may last have been written through the generic proxy)
+                    if (ESMM_ROW_COPY == 1 && (run >= 0 || box8)) fence_proxy_async();
                     if (run >= 0) {
                         if (q == 0 && lane == 0) {
                             tma_load_3d(sa, &maps.a_run[run], a_x, kk0, panel * p.nKB + kb0, full);
@@ -720,10 +780,44 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     } else if (box8) {
                         tma_load_2d(sa, &maps.a_kb, a_x, a_row0 + k, full);
                         tma_load_2d(sb, &maps.b_kb, b_col0, k, full);
-                    } else if (row1) {
-                        tma_load_2d(sa, &maps.a_row, a_x, a_row0 + k, full);
-                        tma_load_2d(sb, &maps.b_row, b_col0, k, full);
                     }
+#if ESMM_ROW_COPY == 1
+                    // Single rows: the whole warp copies each of its rows, 16 bytes per lane; their completion is
+                    // tied to the stage's barrier below.
+                    unsigned rows_left = __ballot_sync(0xFFFFFFFFu, row1);
+                    const bool any_rows = rows_left != 0u;
+                    const bool col_ok = b_col0 + lane * 4 < p.N;
+                    while (rows_left) {
+                        const int r = __ffs((int)rows_left) - 1;
+                        rows_left &= rows_left - 1u;
+                        const int kr = __shfl_sync(0xFFFFFFFFu, k, r);
+                        if (lane * 16 < A_ROW)
+                            cp_async_16(s0 + r * A_ROW + lane * 16,
+                                        p.a_packed + ((size_t)(a_row0 + kr) * TILE_M + a_x + lane * 4), 16);
+                        const bool b_ok = col_ok && kr < p.K;   // outside B: zero fill, as the tensor copy does
+                        cp_async_16(s0 + STAGE_HALF_BYTES + r * ROW_BYTES + lane * 16,
+                                    b_ok ? p.B + ((size_t)kr * p.N + b_col0 + lane * 4) : p.B, b_ok ? 16 : 0);
+                    }
+                    if (any_rows) cp_async_mbar_arrive(full);   // every lane: its copies count towards this phase
+                    __syncwarp();
+                    if (lane == 0) {
+                        // bytes that arrive by tensor copy: whole-stage runs and 8-row boxes (of all producers)
+                        const uint32_t tma_rows = run >= 0 ? (uint32_t)ROWS_PER_STAGE : (uint32_t)__popc(cover);
+                        if (q == 0) mbar_arrive_expect_tx(full, tma_rows * STAGE_ROW_BYTES);
+                        else mbar_arrive(full);
+                    }
+#else
+                    if (row1) {
+                        if (ESMM_ROW_COPY == 2 && b_col0 + TILE_N <= p.N && k < p.K) {
+                            bulk_copy_1d(sa, p.a_packed + ((size_t)(a_row0 + k) * TILE_M + a_x), A_ROW, full);
+                            bulk_copy_1d(sb, p.B + ((size_t)k * p.N + b_col0), ROW_BYTES, full);
+                        } else {
+                            tma_load_2d(sa, &maps.a_row, a_x, a_row0 + k, full);
+                            tma_load_2d(sb, &maps.b_row, b_col0, k, full);
+                        }
+                    }
+                    if (q == 0 && lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * STAGE_ROW_BYTES);
+#endif
                     issued_bits |= 1u << slot;
                     parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
                 }
@@ -737,6 +831,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             __syncwarp();
             if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
         }
+        if (ESMM_ROW_COPY == 1) asm volatile("cp.async.wait_all;" ::: "memory");   // this thread's plain copies have landed
         if (!ok && lane == 0) {
             // leave only after the copies already issued have landed (bounded)
             for (int s = 0; s < p.stages; ++s) {
@@ -782,27 +877,40 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             // joint masks of a stage: bit r = row r is live for (top | bottom) block x my columns.  The
             // masks of the next stage are formed under the multiply-adds of the current one (the list's
             // buffer is padded by one stage, so reading one stage past the end is harmless).
-            unsigned rm = run_tile ? 0xFFu : rmask[lane];
+            unsigned rm = run_tile ? 0xFFu : rmask[lane];   // (cap >= 64: the first stage is always inside the list)
+            bool stage_ready = false;   // the stage's full barrier was already seen complete (dense_rows' look ahead)
             for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
-                const unsigned colb = (rm >> b_shift) & 1u;
-                const unsigned jt = __ballot_sync(0xFFFFFFFFu, ((rm >> t_shift) & colb) != 0u);
-                const unsigned jb = WMB == 2 ? __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u) : jt;
-                if (!run_tile) rm = rmask[r0 + ROWS_PER_STAGE + lane];
+                unsigned jt = 0xFFFFFFFFu, jb = 0xFFFFFFFFu;   // a run tile: every row live for every block
+                if (!run_tile) {
+                    const unsigned colb = (rm >> b_shift) & 1u;
+                    jt = __ballot_sync(0xFFFFFFFFu, ((rm >> t_shift) & colb) != 0u);
+                    jb = WMB == 2 ? __ballot_sync(0xFFFFFFFFu, ((rm >> (t_shift + 1)) & colb) != 0u) : jt;
+                    rm = bounds_ok(r0 + ROWS_PER_STAGE + lane < p.cap, p.status, 23) ? rmask[r0 + ROWS_PER_STAGE + lane] : 0u;
+                }
                 const bool dense = (jt & jb) == 0xFFFFFFFFu && !p.force_listed;
                 // in the 64-row tiling a row feeds 16 two-wide FMAs, as in the half modes: lists there too
                 int cnt_t = 0, cnt_b = 0;
                 if (WMB == 1 ? !dense : jt != jb) {
-                    cnt_t = build_list(wlist_t, jt, lane);
-                    if (WMB == 2) cnt_b = build_list(wlist_b, jb, lane);
+                    cnt_t = build_list(wlist_t, jt, lane, p.status);
+                    if (WMB == 2) cnt_b = build_list(wlist_b, jb, lane, p.status);
                     __syncwarp();
                 }
-                ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
+                if (!stage_ready) ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
                 if (!ok) break;
+                if (!bounds_ok(slot >= 0 && slot < p.stages && L.stage_off + (uint32_t)(slot + 1) * PSTAGE_BYTES <= L.krow_off,
+                               p.status, 24)) {
+                    ok = false;   // a stage outside the ring: leave through the time-out path rather than read it
+                    break;
+                }
+                stage_ready = false;
                 const char *sA = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + a_thr;
                 const char *sB = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + b_thr;
                 if (warp == 0 && it == 0) ESMM_STAMP(10 + r0 / ROWS_PER_STAGE);
                 if (dense) {
-                    dense_rows<WMB>(acc, sA, sB);
+                    const int nslot = slot + 1 == p.stages ? 0 : slot + 1;
+                    // (the look ahead stays inside the tile: the next tile's first stage is awaited normally)
+                    stage_ready = dense_rows<WMB>(acc, sA, sB, full0 + 8 * nslot, nslot == 0 ? phase ^ 1 : phase) &&
+                                  r0 + ROWS_PER_STAGE < n;
                 } else if (WMB == 1) {
                     listed_rows<MODE_TOP, 1>(acc, sA, sB, wlist_t, cnt_t);
                 } else if (jt == jb) {
@@ -841,8 +949,11 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     }
                     if (row < p.M) {
                         float *c = p.C + (size_t)row * p.N + col0;
-                        if (col0 < p.N) *reinterpret_cast<float4 *>(c) = make_float4(v[0], v[1], v[2], v[3]);
-                        if (col0 + 16 < p.N) *reinterpret_cast<float4 *>(c + 16) = make_float4(v[4], v[5], v[6], v[7]);
+                        const size_t c_floats = (size_t)p.M * p.N, off = (size_t)row * p.N + col0;
+                        if (col0 < p.N && bounds_ok(off + 4 <= c_floats, p.status, 26))
+                            *reinterpret_cast<float4 *>(c) = make_float4(v[0], v[1], v[2], v[3]);
+                        if (col0 + 16 < p.N && bounds_ok(off + 20 <= c_floats, p.status, 26))
+                            *reinterpret_cast<float4 *>(c + 16) = make_float4(v[4], v[5], v[6], v[7]);
                     }
                 }
             }
@@ -917,6 +1028,8 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
         p.vec_patterns = forced_vec;
     p.a_pat = d_a_pat;
     p.b_pat = d_b_pat;
+    p.a_packed = d_a_packed;
+    p.B = d_B;
     p.C = d_C;
 
     int stages = tuning_get("STAGES", P_MAX_STAGES);

@@ -22,6 +22,7 @@
 // fast ones.  The only waits are cp.async.wait_group and __syncthreads with a trip count common to all
 // threads: no flag or barrier that another agent has to signal, nothing that can wait forever.
 #include <cstring>
+#include <type_traits>
 
 #include "esmm_gemm_shared.cuh"
 
@@ -31,8 +32,6 @@ constexpr int SK_COLS = 32;                     // columns of a strip = one B pa
 constexpr int SK_ROWS = 32;                     // rows of C handled (M <= 32)
 constexpr int SK_STAGE_ROWS = 32;               // k per stage
 constexpr int SK_ROW_BYTES = 128;               // one k of either operand in shared memory
-constexpr int SK_HALF = SK_STAGE_ROWS * SK_ROW_BYTES;   // 4096: A rows, then B rows
-constexpr int SK_STAGE_BYTES = 2 * SK_HALF;     // 8192
 constexpr int SK_STAGES = 6;
 constexpr int SK_WARPS = 4;                      // one per SM sub-partition
 constexpr int SK_THREADS = SK_WARPS * 32;
@@ -89,36 +88,64 @@ __device__ __forceinline__ int sk_scan(int v, int lane)
     return v;
 }
 
+// ROWS = 32: rows 0-31 of the first panel (any M <= 32).  ROWS = 16 (M <= 16): only rows 0-15 are fetched and
+// multiplied - half the shared-memory traffic of A and half the multiply-adds.
+template <int ROWS>
 __global__ void __launch_bounds__(SK_THREADS)
 esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
 {
+    constexpr int A_ROW_BYTES = ROWS * 4;                           // one k of A in shared memory
+    constexpr int A_CHUNKS = A_ROW_BYTES / 16;                      // 16-byte pieces per A row
+    constexpr int A_HALF = SK_STAGE_ROWS * A_ROW_BYTES;             // A rows, then B rows
+    constexpr int STAGE_BYTES = A_HALF + SK_STAGE_ROWS * SK_ROW_BYTES;
+    constexpr int BATCH = 4;                                        // rows per register set of operands
     extern __shared__ __align__(1024) char smem[];
     // layout: ring | krow (u16 x cap) | warp sums
-    uint16_t *krow = reinterpret_cast<uint16_t *>(smem + SK_STAGES * SK_STAGE_BYTES);
-    volatile int *wsum = reinterpret_cast<volatile int *>(smem + SK_STAGES * SK_STAGE_BYTES + ((p.cap * 2 + 15) & ~15));
+    uint16_t *krow = reinterpret_cast<uint16_t *>(smem + SK_STAGES * STAGE_BYTES);
+    volatile int *wsum = reinterpret_cast<volatile int *>(smem + SK_STAGES * STAGE_BYTES + ((p.cap * 2 + 15) & ~15));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int strip = blockIdx.x;
     SK_STAMP(0);
 
     // ---------------- the strip's list of live k ----------------
-    // Thread t owns the K blocks t * per .. t * per + per - 1 (consecutive threads, ascending k): count,
-    // prefix over the CTA, write.
+    // Thread t owns the K blocks t * per .. t * per + per - 1 (consecutive threads, ascending k; per a multiple
+    // of 4 so that a thread's pattern bytes are whole 32-bit words where the arrays allow): count, prefix over
+    // the CTA, write.
     {
+        constexpr int MAX_WORDS = SK_MAX_KP / BK / SK_THREADS / 4;   // 4 words of 4 K blocks per thread at most
         const uint8_t *bp = p.b_pat + (size_t)strip * p.nKB;
-        const int per = (p.nKB + SK_THREADS - 1) / SK_THREADS;
+        const int per = ((p.nKB + SK_THREADS - 1) / SK_THREADS + 3) & ~3;
         const int kb_lo = min((int)threadIdx.x * per, p.nKB), kb_hi = min(kb_lo + per, p.nKB);
+        const bool words = (p.nKB & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.a_pat) | reinterpret_cast<uintptr_t>(bp)) & 3) == 0;
+        unsigned live[MAX_WORDS];
         int c = 0;
-        for (int kb = kb_lo; kb < kb_hi; ++kb) c += __popc((unsigned)(p.a_pat[kb] & bp[kb]));
+#pragma unroll
+        for (int w = 0; w < MAX_WORDS; ++w) {
+            const int kb = kb_lo + 4 * w;
+            unsigned v = 0u;
+            if (kb < kb_hi) {
+                if (words) {
+                    v = *reinterpret_cast<const unsigned *>(p.a_pat + kb) & *reinterpret_cast<const unsigned *>(bp + kb);
+                } else {
+                    for (int j = 0; j < 4 && kb + j < kb_hi; ++j) v |= (unsigned)(p.a_pat[kb + j] & bp[kb + j]) << (8 * j);
+                }
+            }
+            live[w] = v;
+            c += __popc(v);
+        }
         const int incl = sk_scan(c, lane);
         if (lane == 31) wsum[warp] = incl;
         __syncthreads();
         int q = incl - c;
         for (int w = 0; w < warp; ++w) q += wsum[w];
-        for (int kb = kb_lo; kb < kb_hi; ++kb) {
-            unsigned live = (unsigned)(p.a_pat[kb] & bp[kb]);
-            while (live) {
-                krow[q++] = (uint16_t)(kb * BK + __ffs((int)live) - 1);
-                live &= live - 1u;
+#pragma unroll
+        for (int w = 0; w < MAX_WORDS; ++w) {
+            unsigned v = live[w];
+            while (v) {
+                const int bit = __ffs((int)v) - 1;                   // bit 8 j + kk: K block kb_lo + 4 w + j, offset kk
+                if (bounds_ok(q < p.cap, p.status, 30)) krow[q] = (uint16_t)((kb_lo + 4 * w) * BK + bit);   // checked build: site 30
+                ++q;
+                v &= v - 1u;
             }
         }
         __syncthreads();
@@ -129,7 +156,7 @@ esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
     const int num_stages = (n + SK_STAGE_ROWS - 1) / SK_STAGE_ROWS;
     SK_STAMP(1);
 
-    // ---------------- copies: every thread moves 4 of a stage's 512 sixteen-byte pieces ----------------
+    // ---------------- copies: every thread moves up to 4 of a stage's sixteen-byte pieces ----------------
     // (Rows of 128 bytes are too short for the tensor copy engine, which spends about as long on a row of
     // 128 bytes as on one of 512: measured, one row per ~17 cycles per SM.)
     const int col0 = strip * SK_COLS, chunk = threadIdx.x & 7, sub = threadIdx.x >> 3;   // sub: 0 .. 15
@@ -137,15 +164,17 @@ esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
     auto issue = [&](int stage) {
         if (stage < num_stages) {
             const int r0 = stage * SK_STAGE_ROWS, cnt = min(SK_STAGE_ROWS, n - r0);
-            const uint32_t sa = smem_u32(smem) + (uint32_t)(stage % SK_STAGES) * SK_STAGE_BYTES + (uint32_t)chunk * 16;
+            const uint32_t s0 = smem_u32(smem) + (uint32_t)(stage % SK_STAGES) * STAGE_BYTES + (uint32_t)chunk * 16;
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
+            for (int i = 0; i < SK_STAGE_ROWS / 16; ++i) {
                 const int r = i * 16 + sub;
-                if (r < cnt) {
+                if (r < cnt && bounds_ok(r0 + r < p.cap, p.status, 31)) {
                     const int k = krow[r0 + r];
-                    cp_async_16(sa + r * SK_ROW_BYTES, p.a_packed + (size_t)k * TILE_M + chunk * 4, 16);
+                    if (!bounds_ok(k >= 0 && k < p.kp, p.status, 32)) continue;   // site 32: a k outside the packed panel / B
+                    if (chunk < A_CHUNKS)
+                        cp_async_16(s0 + r * A_ROW_BYTES, p.a_packed + (size_t)k * TILE_M + chunk * 4, 16);
                     const bool b_ok = col_ok && k < p.K;   // outside B: zero fill
-                    cp_async_16(sa + SK_HALF + r * SK_ROW_BYTES, b_ok ? p.B + (size_t)k * p.N + col0 + chunk * 4 : p.B,
+                    cp_async_16(s0 + A_HALF + r * SK_ROW_BYTES, b_ok ? p.B + (size_t)k * p.N + col0 + chunk * 4 : p.B,
                                 b_ok ? 16 : 0);
                 }
             }
@@ -153,15 +182,49 @@ esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
         cp_async_commit();   // one group per stage, empty past the end: the wait below counts groups
     };
 
-    // ---------------- 32 rows x 8 columns per warp, 4 x 2 per thread ----------------
+    // ---------------- per warp ROWS rows x 8 columns; per thread (ROWS / 8) rows x 2 columns ----------------
     // every 4 consecutive lanes touch 2 row groups x 2 column pairs (few distinct bytes per load)
-    const int rg = ((lane >> 1) & 3) | ((lane >> 4) << 2);       // group of 4 rows
+    const int rg = ((lane >> 1) & 3) | ((lane >> 4) << 2);       // group of ROWS / 8 consecutive rows
     const int cp = (lane & 1) | (((lane >> 3) & 1) << 1);        // pair of columns within the warp's 8
-    const char *tA = smem + rg * 16;
-    const char *tB = smem + SK_HALF + warp * 32 + cp * 8;
+    const uint32_t tA = smem_u32(smem) + rg * (ROWS / 2);
+    const uint32_t tB = smem_u32(smem) + A_HALF + warp * 32 + cp * 8;
     // rows 2p, 2p+1 x the column pair: diag[p] = (c[2p][0], c[2p+1][1]), anti[p] = (c[2p][1], c[2p+1][0])
-    float2 diag[2], anti[2];
-    diag[0] = diag[1] = anti[0] = anti[1] = make_float2(0.0f, 0.0f);
+    constexpr int RP = ROWS / 16;                                 // row pairs per thread
+    float2 diag[RP], anti[RP];
+#pragma unroll
+    for (int i = 0; i < RP; ++i) diag[i] = anti[i] = make_float2(0.0f, 0.0f);
+
+    // Operands of BATCH consecutive rows of a stage.  The loop below loads the next batch before it multiplies
+    // the current one (two register sets, ping-pong), so that a load has a whole batch of multiply-adds to land
+    // under; the loads are volatile so that they stay where they are written.
+    struct Ops {
+        float2 a[BATCH][RP], b[BATCH];
+    };
+    auto load_rows = [&](Ops &o, uint32_t sA, uint32_t sB, int r) {
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const uint32_t pa = sA + (uint32_t)((r + i) * A_ROW_BYTES), pb = sB + (uint32_t)((r + i) * SK_ROW_BYTES);
+            if (RP == 2)
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(o.a[i][0].x), "=f"(o.a[i][0].y), "=f"(o.a[i][RP - 1].x), "=f"(o.a[i][RP - 1].y) : "r"(pa));
+            else
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(o.a[i][0].x), "=f"(o.a[i][0].y) : "r"(pa));
+            asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(o.b[i].x), "=f"(o.b[i].y) : "r"(pb));
+        }
+    };
+    auto fma_rows = [&](const Ops &o, int count) {
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            if (i < count) {
+                const float2 bs = make_float2(o.b[i].y, o.b[i].x);
+#pragma unroll
+                for (int pr = 0; pr < RP; ++pr) {
+                    diag[pr] = __ffma2_rn(o.a[i][pr], o.b[i], diag[pr]);
+                    anti[pr] = __ffma2_rn(o.a[i][pr], bs, anti[pr]);
+                }
+            }
+        }
+    };
 
 #pragma unroll
     for (int s = 0; s < SK_STAGES - 1; ++s) issue(s);
@@ -171,22 +234,25 @@ esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
         issue(s + SK_STAGES - 1);               // into the slot of stage s - 1
         if (warp == 0) SK_STAMP(10 + s);
         const int cnt = min(SK_STAGE_ROWS, n - s * SK_STAGE_ROWS);
-        const char *sA = tA + (size_t)(s % SK_STAGES) * SK_STAGE_BYTES;
-        const char *sB = tB + (size_t)(s % SK_STAGES) * SK_STAGE_BYTES;
-        auto row = [&](int r) {
-            const float4 a = *reinterpret_cast<const float4 *>(sA + r * SK_ROW_BYTES);
-            const float2 b = *reinterpret_cast<const float2 *>(sB + r * SK_ROW_BYTES);
-            const float2 a01 = make_float2(a.x, a.y), a23 = make_float2(a.z, a.w), bs = make_float2(b.y, b.x);
-            diag[0] = __ffma2_rn(a01, b, diag[0]);
-            anti[0] = __ffma2_rn(a01, bs, anti[0]);
-            diag[1] = __ffma2_rn(a23, b, diag[1]);
-            anti[1] = __ffma2_rn(a23, bs, anti[1]);
-        };
+        const uint32_t sA = tA + (uint32_t)(s % SK_STAGES) * STAGE_BYTES;
+        const uint32_t sB = tB + (uint32_t)(s % SK_STAGES) * STAGE_BYTES;
+        // (a batch loaded past the stage's last row reads the next slot or the row list: in bounds, never multiplied)
+        Ops x, y;
+        load_rows(x, sA, sB, 0);
         if (cnt == SK_STAGE_ROWS) {
-#pragma unroll 16
-            for (int r = 0; r < SK_STAGE_ROWS; ++r) row(r);
+#pragma unroll 1
+            for (int r = 0; r < SK_STAGE_ROWS; r += 2 * BATCH) {
+                load_rows(y, sA, sB, r + BATCH);
+                fma_rows(x, BATCH);
+                load_rows(x, sA, sB, r + 2 * BATCH);
+                fma_rows(y, BATCH);
+            }
         } else {
-            for (int r = 0; r < cnt; ++r) row(r);
+#pragma unroll 1
+            for (int r = 0; r < cnt; r += BATCH) {
+                fma_rows(x, min(BATCH, cnt - r));
+                load_rows(x, sA, sB, r + BATCH);
+            }
         }
         if (warp == 0) SK_STAMP(200 + s);
     }
@@ -196,12 +262,217 @@ esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
     // C is overwritten (beta = 0); un-scramble the 2 x 2 blocks into rows
     const int col = strip * SK_COLS + warp * 8 + cp * 2;
 #pragma unroll
-    for (int pr = 0; pr < 2; ++pr)
+    for (int pr = 0; pr < RP; ++pr)
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-            const int r = rg * 4 + 2 * pr + e;
+            const int r = rg * (ROWS / 8) + 2 * pr + e;
             const float2 v = e == 0 ? make_float2(diag[pr].x, anti[pr].x) : make_float2(anti[pr].y, diag[pr].y);
-            if (r < p.M && col < p.N) *reinterpret_cast<float2 *>(p.C + (size_t)r * p.N + col) = v;
+            if (r < p.M && col < p.N && bounds_ok((size_t)r * p.N + col + 2 <= (size_t)p.M * p.N, p.status, 33))
+                *reinterpret_cast<float2 *>(p.C + (size_t)r * p.N + col) = v;
+        }
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// Second form: warp-private pipelines.  A strip is shared by TWO warps, 16 columns each, and the two never meet
+// after the strip's list of live k has been built: every warp fetches what it needs itself - per live k the 64 or
+// 128 bytes of packed A and the 64 bytes of its half of B's row - into a ring of its own, waits only for its own
+// copies (cp.async.wait_group + __syncwarp) and multiplies.  There is no barrier in the main loop and no stage
+// that waits for the slowest of several warps; the price is that A travels from L2 twice.  A thread holds
+// (ROWS / 8) rows x 4 columns; operands of four rows are loaded one batch ahead of the multiply-adds.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int ST_WARPS = 2;
+constexpr int ST_THREADS = ST_WARPS * 32;
+constexpr int ST_WCOLS = SK_COLS / ST_WARPS;     // 16 columns per warp
+constexpr int ST_B_ROW_BYTES = ST_WCOLS * 4;     // 64
+constexpr int ST_STAGE_ROWS = 32;
+constexpr int ST_STAGES = 6;
+
+template <int ROWS>
+__global__ void __launch_bounds__(ST_THREADS)
+esmm_joint_sgemm_strip_kernel(const SkinnyParams p)
+{
+    constexpr int A_ROW_BYTES = ROWS * 4;
+    constexpr int A_CHUNKS = A_ROW_BYTES / 16;                       // 16-byte pieces per row of A: 4 or 8
+    constexpr int A_HALF = ST_STAGE_ROWS * A_ROW_BYTES;
+    constexpr int STAGE_BYTES = A_HALF + ST_STAGE_ROWS * ST_B_ROW_BYTES;
+    constexpr int RING_BYTES = ST_STAGES * STAGE_BYTES;              // per warp
+    constexpr int RP = ROWS / 16;                                    // row pairs per thread
+    constexpr int BATCH = 4;
+    extern __shared__ __align__(1024) char smem[];
+    // layout: ring of warp 0 | ring of warp 1 | krow (u16 x cap) | warp sums
+    uint16_t *krow = reinterpret_cast<uint16_t *>(smem + ST_WARPS * RING_BYTES);
+    volatile int *wsum = reinterpret_cast<volatile int *>(smem + ST_WARPS * RING_BYTES + ((p.cap * 2 + 15) & ~15));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int strip = blockIdx.x;
+    SK_STAMP(0);
+
+    // ---------------- the strip's list of live k (both warps together, once) ----------------
+    {
+        constexpr int MAX_WORDS = SK_MAX_KP / BK / ST_THREADS / 4;   // words of 4 K blocks per thread at most (8)
+        const uint8_t *bp = p.b_pat + (size_t)strip * p.nKB;
+        const int per = ((p.nKB + ST_THREADS - 1) / ST_THREADS + 3) & ~3;
+        const int kb_lo = min((int)threadIdx.x * per, p.nKB), kb_hi = min(kb_lo + per, p.nKB);
+        const bool words = (p.nKB & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.a_pat) | reinterpret_cast<uintptr_t>(bp)) & 3) == 0;
+        unsigned live[MAX_WORDS];
+        int c = 0;
+#pragma unroll
+        for (int w = 0; w < MAX_WORDS; ++w) {
+            const int kb = kb_lo + 4 * w;
+            unsigned v = 0u;
+            if (kb < kb_hi) {
+                if (words) {
+                    v = *reinterpret_cast<const unsigned *>(p.a_pat + kb) & *reinterpret_cast<const unsigned *>(bp + kb);
+                } else {
+                    for (int j = 0; j < 4 && kb + j < kb_hi; ++j) v |= (unsigned)(p.a_pat[kb + j] & bp[kb + j]) << (8 * j);
+                }
+            }
+            live[w] = v;
+            c += __popc(v);
+        }
+        const int incl = sk_scan(c, lane);
+        if (lane == 31) wsum[warp] = incl;
+        __syncthreads();
+        int q = incl - c;
+        for (int w = 0; w < warp; ++w) q += wsum[w];
+#pragma unroll
+        for (int w = 0; w < MAX_WORDS; ++w) {
+            unsigned v = live[w];
+            while (v) {
+                const int bit = __ffs((int)v) - 1;                   // bit 8 j + kk: K block kb_lo + 4 w + j, offset kk
+                if (bounds_ok(q < p.cap, p.status, 30)) krow[q] = (uint16_t)((kb_lo + 4 * w) * BK + bit);
+                ++q;
+                v &= v - 1u;
+            }
+        }
+        __syncthreads();   // the last time the two warps wait for each other
+    }
+    int n = 0;
+#pragma unroll
+    for (int w = 0; w < ST_WARPS; ++w) n += wsum[w];
+    const int num_stages = (n + ST_STAGE_ROWS - 1) / ST_STAGE_ROWS;
+    SK_STAMP(1);
+
+    // ---------------- this warp's copies: lane = (row of a group of 8, 16-byte piece) ----------------
+    const uint32_t ring = smem_u32(smem) + (uint32_t)warp * RING_BYTES;
+    const int wcol0 = strip * SK_COLS + warp * ST_WCOLS;
+    const int piece = lane & 3, prow = lane >> 2;                    // B: 4 pieces per row, 8 rows per pass
+    const bool bcol_ok = wcol0 + piece * 4 < p.N;
+    auto issue = [&](int stage) {
+        if (stage < num_stages) {
+            const int r0 = stage * ST_STAGE_ROWS, cnt = min(ST_STAGE_ROWS, n - r0);
+            const uint32_t s0 = ring + (uint32_t)(stage % ST_STAGES) * STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < ST_STAGE_ROWS / 8; ++i) {
+                const int r = i * 8 + prow;
+                if (r < cnt && bounds_ok(r0 + r < p.cap, p.status, 31)) {
+                    const int k = krow[r0 + r];
+                    if (!bounds_ok(k >= 0 && k < p.kp, p.status, 32)) continue;
+                    const float *a_src = p.a_packed + (size_t)k * TILE_M + piece * 4;
+#pragma unroll
+                    for (int h = 0; h < A_CHUNKS / 4; ++h)             // 4 (or 2 x 4) pieces of this row of A
+                        cp_async_16(s0 + r * A_ROW_BYTES + (h * 4 + piece) * 16, a_src + h * 16, 16);
+                    const bool b_ok = bcol_ok && k < p.K;              // outside B: zero fill
+                    cp_async_16(s0 + A_HALF + r * ST_B_ROW_BYTES + piece * 16,
+                                b_ok ? p.B + (size_t)k * p.N + wcol0 + piece * 4 : p.B, b_ok ? 16 : 0);
+                }
+            }
+        }
+        cp_async_commit();   // one group per stage, empty past the end: the wait below counts groups
+    };
+
+    // ---------------- (ROWS / 8) rows x 4 columns per thread ----------------
+    // every 4 consecutive lanes touch 2 row groups x 2 column quads (few distinct bytes per load)
+    const int rg = (lane >> 1) & 7;                              // group of ROWS / 8 consecutive rows
+    const int cq = (lane & 1) | ((lane >> 4) << 1);              // quad of columns within the warp's 16
+    const uint32_t tA = ring + rg * (ROWS / 2);
+    const uint32_t tB = ring + A_HALF + cq * 16;
+    // block (pr, j): rows 2 pr, 2 pr + 1 of the thread's rows x columns 2 j, 2 j + 1 of its quad:
+    // diag = (c[r0][c0], c[r1][c1]), anti = (c[r0][c1], c[r1][c0])
+    float2 diag[RP][2], anti[RP][2];
+#pragma unroll
+    for (int i = 0; i < RP; ++i)
+#pragma unroll
+        for (int j = 0; j < 2; ++j) diag[i][j] = anti[i][j] = make_float2(0.0f, 0.0f);
+
+    struct Ops {
+        float2 a[BATCH][RP];
+        float4 b[BATCH];
+    };
+    auto load_rows = [&](Ops &o, uint32_t sA, uint32_t sB, int r) {
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            const uint32_t pa = sA + (uint32_t)((r + i) * A_ROW_BYTES), pb = sB + (uint32_t)((r + i) * ST_B_ROW_BYTES);
+            if (RP == 2)
+                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                             : "=f"(o.a[i][0].x), "=f"(o.a[i][0].y), "=f"(o.a[i][RP - 1].x), "=f"(o.a[i][RP - 1].y) : "r"(pa));
+            else
+                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(o.a[i][0].x), "=f"(o.a[i][0].y) : "r"(pa));
+            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
+                         : "=f"(o.b[i].x), "=f"(o.b[i].y), "=f"(o.b[i].z), "=f"(o.b[i].w) : "r"(pb));
+        }
+    };
+    auto fma_rows = [&](const Ops &o, int count) {
+#pragma unroll
+        for (int i = 0; i < BATCH; ++i) {
+            if (i < count) {
+                const float2 b01 = make_float2(o.b[i].x, o.b[i].y), b10 = make_float2(o.b[i].y, o.b[i].x);
+                const float2 b23 = make_float2(o.b[i].z, o.b[i].w), b32 = make_float2(o.b[i].w, o.b[i].z);
+#pragma unroll
+                for (int pr = 0; pr < RP; ++pr) {
+                    diag[pr][0] = __ffma2_rn(o.a[i][pr], b01, diag[pr][0]);
+                    anti[pr][0] = __ffma2_rn(o.a[i][pr], b10, anti[pr][0]);
+                    diag[pr][1] = __ffma2_rn(o.a[i][pr], b23, diag[pr][1]);
+                    anti[pr][1] = __ffma2_rn(o.a[i][pr], b32, anti[pr][1]);
+                }
+            }
+        }
+    };
+
+#pragma unroll
+    for (int s = 0; s < ST_STAGES - 1; ++s) issue(s);
+    for (int s = 0; s < num_stages; ++s) {
+        cp_async_wait_group<ST_STAGES - 2>();   // this lane's pieces of stage s have landed ...
+        __syncwarp();                           // ... every lane's have, and every lane is done with stage s - 1
+        issue(s + ST_STAGES - 1);               // into the slot of stage s - 1
+        if (warp == 0) SK_STAMP(10 + s);
+        const int cnt = min(ST_STAGE_ROWS, n - s * ST_STAGE_ROWS);
+        const uint32_t sA = tA + (uint32_t)(s % ST_STAGES) * STAGE_BYTES;
+        const uint32_t sB = tB + (uint32_t)(s % ST_STAGES) * STAGE_BYTES;
+        // (a batch loaded past the stage's last row reads the next slot, the other warp's ring or the row list: in
+        // bounds, never multiplied)
+        Ops x, y;
+        load_rows(x, sA, sB, 0);
+        if (cnt == ST_STAGE_ROWS) {
+#pragma unroll 1
+            for (int r = 0; r < ST_STAGE_ROWS; r += 2 * BATCH) {
+                load_rows(y, sA, sB, r + BATCH);
+                fma_rows(x, BATCH);
+                load_rows(x, sA, sB, r + 2 * BATCH);
+                fma_rows(y, BATCH);
+            }
+        } else {
+#pragma unroll 1
+            for (int r = 0; r < cnt; r += BATCH) {
+                fma_rows(x, min(BATCH, cnt - r));
+                load_rows(x, sA, sB, r + BATCH);
+            }
+        }
+        if (warp == 0) SK_STAMP(200 + s);
+    }
+    cp_async_wait_group<0>();   // nothing of this thread is in flight when it leaves
+    SK_STAMP(5);
+
+    // C is overwritten (beta = 0); un-scramble the 2 x 2 blocks into rows of 4 columns
+    const int col = wcol0 + cq * 4;
+#pragma unroll
+    for (int pr = 0; pr < RP; ++pr)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int r = rg * (ROWS / 8) + 2 * pr + e;
+            const float4 v = e == 0 ? make_float4(diag[pr][0].x, anti[pr][0].x, diag[pr][1].x, anti[pr][1].x)
+                                    : make_float4(anti[pr][0].y, diag[pr][0].y, anti[pr][1].y, diag[pr][1].y);
+            if (r < p.M && col < p.N && bounds_ok((size_t)r * p.N + col + 4 <= (size_t)p.M * p.N, p.status, 33))
+                *reinterpret_cast<float4 *>(p.C + (size_t)r * p.N + col) = v;
         }
 }
 
@@ -237,11 +508,35 @@ int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const fl
     p.C = d_C;
     p.status = device_status_ptr();
     if (!p.status) return ESMM_ERR_CUDA;
-    // ring, row list, one int per warp
-    const size_t smem = (size_t)SK_STAGES * SK_STAGE_BYTES + ((p.cap * 2 + 15) & ~15) + (SK_WARPS * 4 + 15) / 16 * 16;
-    ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_skinny_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem));
-    esmm_joint_sgemm_skinny_kernel<<<ceil_div(N, SK_COLS), SK_THREADS, smem, stream>>>(p);
+    const bool rows16 = M <= 16 && tuning_get("SKINNY_ROWS", 0) != 32;
+    if (tuning_get("SKINNY_SHARED", 1) == 0) {   // (the warp-private form is opt-in until it has been measured)
+        // warp-private pipelines: two rings, row list, one int per warp
+        const size_t ring = (size_t)ST_STAGES * ST_STAGE_ROWS * ((rows16 ? 16 : 32) * 4 + ST_B_ROW_BYTES);
+        const size_t smem = ST_WARPS * ring + ((p.cap * 2 + 15) & ~15) + 16;
+        if (rows16) {
+            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_strip_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem));
+            esmm_joint_sgemm_strip_kernel<16><<<ceil_div(N, SK_COLS), ST_THREADS, smem, stream>>>(p);
+        } else {
+            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_strip_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                               (int)smem));
+            esmm_joint_sgemm_strip_kernel<32><<<ceil_div(N, SK_COLS), ST_THREADS, smem, stream>>>(p);
+        }
+        ESMM_CUDA_TRY(cudaGetLastError());
+        return ESMM_OK;
+    }
+    // one ring per CTA: ring, row list, one int per warp
+    const size_t stage_bytes = (size_t)SK_STAGE_ROWS * ((rows16 ? 16 : 32) * 4 + SK_ROW_BYTES);
+    const size_t smem = (size_t)SK_STAGES * stage_bytes + ((p.cap * 2 + 15) & ~15) + (SK_WARPS * 4 + 15) / 16 * 16;
+    if (rows16) {
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_skinny_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem));
+        esmm_joint_sgemm_skinny_kernel<16><<<ceil_div(N, SK_COLS), SK_THREADS, smem, stream>>>(p);
+    } else {
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_skinny_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)smem));
+        esmm_joint_sgemm_skinny_kernel<32><<<ceil_div(N, SK_COLS), SK_THREADS, smem, stream>>>(p);
+    }
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;
 }

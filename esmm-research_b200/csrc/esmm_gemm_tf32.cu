@@ -125,17 +125,6 @@ __device__ __forceinline__ void umma_kblock(uint32_t d, uint32_t ah, uint32_t al
     umma_tf32<PAIR, IDESC>(d, ah + 2u * j, bh + 2u * j, 1u);
 }
 
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
-{
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(done)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return done != 0;
-}
-
 // All live K blocks of a group (live: 4-bit mask, not 0); the dense case is unrolled with constant offsets.
 // A wait on a data barrier costs the issuing thread about 170 cycles even when the data is there, more than
 // two MMAs take, and the tensor pipe runs dry meanwhile.  So the next group's barrier is polled (one
@@ -422,7 +411,8 @@ esmm_joint_sgemm_tf32x3_kernel(const __grid_constant__ Tf32Maps maps, const Tf32
                     for (int j = 0; j < T_GROUP_KB; ++j) live |= ((au[j] & bu[j]) != 0u ? 1u : 0u) << j;
                 }
                 const unsigned m = __ballot_sync(0xFFFFFFFFu, live != 0u);
-                if (live) list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
+                if (live && bounds_ok(pos + __popc(m & ((1u << lane) - 1u)) < p.cap, p.status, 50))   // checked build: site 50
+                    list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
                 pos += __popc(m);
             }
             if (lane == 0) nlive[buf] = pos;
@@ -764,7 +754,8 @@ esmm_joint_sgemm_tf32x3_pair_kernel(const __grid_constant__ Tf32PairMaps maps, c
                     }
                 }
                 const unsigned m = __ballot_sync(0xFFFFFFFFu, live != 0u);
-                if (live) list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
+                if (live && bounds_ok(pos + __popc(m & ((1u << lane) - 1u)) < p.cap, p.status, 50))   // checked build: site 50
+                    list[pos + __popc(m & ((1u << lane) - 1u))] = (uint16_t)(g | (live << 12));
                 pos += __popc(m);
             }
             if (lane == 0) {

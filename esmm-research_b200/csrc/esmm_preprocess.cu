@@ -28,8 +28,10 @@ __device__ __forceinline__ unsigned nz4(const float4 &v)
 // Needs K % 4 == 0 and a 16-byte aligned A.
 __global__ void __launch_bounds__(PRE_THREADS)
 esmm_preprocess_a_patterns_kernel(const float *__restrict__ A, int M, int K, int tile_m, int nMB,
-                                  int nKB, int k_chunks, uint8_t *__restrict__ out)
+                                  int nKB, int k_chunks, uint8_t *__restrict__ out, int *status)
 {
+    // checked build, sites 10 (loads of A) and 11 (pattern stores)
+    const size_t a_floats = (size_t)M * K, out_bytes = (size_t)nMB * nKB;
     const int lane = threadIdx.x & 31;
     const long warps_total = (long)gridDim.x * (PRE_THREADS / 32);
     const long tasks = (long)nMB * k_chunks;
@@ -47,16 +49,22 @@ esmm_preprocess_a_patterns_kernel(const float *__restrict__ A, int M, int K, int
             for (; r + 8 <= rows; r += 8) {
                 float4 v[8];
 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    v[u] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)(r + u) * K));
+                for (int u = 0; u < 8; ++u) {
+                    v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (bounds_ok((size_t)(row0 + r + u) * K + col + 4 <= a_floats, status, 10))
+                        v[u] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)(r + u) * K));
+                }
 #pragma unroll
                 for (int u = 0; u < 8; ++u) nib |= nz4(v[u]);
             }
-            for (; r < rows; ++r) nib |= nz4(__ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K)));
+            for (; r < rows; ++r)
+                if (bounds_ok((size_t)(row0 + r) * K + col + 4 <= a_floats, status, 10))
+                    nib |= nz4(__ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K)));
         }
         const unsigned other = __shfl_xor_sync(0xFFFFFFFFu, nib, 1);
         const int kb = kc * 16 + (lane >> 1);
-        if (!(lane & 1) && kb < nKB) out[(size_t)mb * nKB + kb] = (uint8_t)(nib | (other << 4));
+        if (!(lane & 1) && kb < nKB && bounds_ok((size_t)mb * nKB + kb < out_bytes, status, 11))
+            out[(size_t)mb * nKB + kb] = (uint8_t)(nib | (other << 4));
     }
 }
 
@@ -72,8 +80,11 @@ constexpr int PACK_SMEM_PER_WARP = 128 * 32 * 4;  // 16 KB
 
 __global__ void __launch_bounds__(PACK_WARPS * 32)
 esmm_preprocess_a_pack_kernel(const float *__restrict__ A, int M, int K, int nMB, int nKB, int k_chunks,
-                              uint8_t *__restrict__ out, float *__restrict__ packed)
+                              uint8_t *__restrict__ out, float *__restrict__ packed, int *status)
 {
+    // checked build, sites 10 (loads of A), 11 (pattern stores), 12 (stores into the packed copy), 13 (the warp's tile)
+    const size_t a_floats = (size_t)M * K, out_bytes = (size_t)nMB * nKB;
+    const size_t packed_floats = (size_t)((M + 127) / 128) * nKB * BK * 128;
     extern __shared__ __align__(16) float pack_smem[];
     float *tile = pack_smem + (threadIdx.x >> 5) * (PACK_SMEM_PER_WARP / 4);
     const int lane = threadIdx.x & 31;
@@ -93,7 +104,8 @@ esmm_preprocess_a_pack_kernel(const float *__restrict__ A, int M, int K, int nMB
 #pragma unroll
         for (int r = 0; r < 32; ++r) {
             v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (col_ok && row0 + r < M) v[r] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K));
+            if (col_ok && row0 + r < M && bounds_ok((size_t)(row0 + r) * K + col + 4 <= a_floats, status, 10))
+                v[r] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K));
         }
 #pragma unroll
         for (int r = 0; r < 32; ++r) nib |= nz4(v[r]);
@@ -107,6 +119,7 @@ esmm_preprocess_a_pack_kernel(const float *__restrict__ A, int M, int K, int nMB
         for (int r = 0; r < 32; ++r) {
             // element (r, c) lives at c * 32 + ((r + (c >> 2)) & 31); here c >> 2 == lane
             const int pos = (r + lane) & 31;
+            if (!bounds_ok((lane * 4 + 3) * 32 + pos < PACK_SMEM_PER_WARP / 4, status, 13)) continue;
             if (nib & 1u) tile[(lane * 4 + 0) * 32 + pos] = v[r].x;
             if (nib & 2u) tile[(lane * 4 + 1) * 32 + pos] = v[r].y;
             if (nib & 4u) tile[(lane * 4 + 2) * 32 + pos] = v[r].z;
@@ -114,13 +127,16 @@ esmm_preprocess_a_pack_kernel(const float *__restrict__ A, int M, int K, int nMB
         }
         const unsigned other = __shfl_xor_sync(0xFFFFFFFFu, nib, 1);
         const int kb_lane = kc * 16 + (lane >> 1);
-        if (!(lane & 1) && kb_lane < nKB) out[(size_t)mb * nKB + kb_lane] = (uint8_t)(nib | (other << 4));
+        if (!(lane & 1) && kb_lane < nKB && bounds_ok((size_t)mb * nKB + kb_lane < out_bytes, status, 11))
+            out[(size_t)mb * nKB + kb_lane] = (uint8_t)(nib | (other << 4));
         __syncwarp();
-        float *dst = packed + (size_t)(mb >> 2) * nKB * BK * 128 + (mb & 3) * 32 + lane;
+        const size_t dst0 = (size_t)(mb >> 2) * nKB * BK * 128 + (mb & 3) * 32 + lane;
+        float *dst = packed + dst0;
 #pragma unroll 8
         for (int c = 0; c < 128; ++c) {
             const int k = kc * 128 + c;  // global k = kb * 8 + kk
-            if (((liveq[c & 3] >> (c >> 2)) & 1u) && k < nKB * BK)
+            if (((liveq[c & 3] >> (c >> 2)) & 1u) && k < nKB * BK &&
+                bounds_ok(dst0 + (size_t)k * 128 < packed_floats, status, 12))
                 dst[(size_t)k * 128] = tile[c * 32 + ((lane + (c >> 2)) & 31)];
         }
         __syncwarp();
@@ -136,8 +152,11 @@ constexpr int PACK64_SMEM_PER_WARP = 64 * 32 * 4;  // 8 KB
 
 __global__ void __launch_bounds__(PACK_WARPS * 32)
 esmm_preprocess_a_pack64_kernel(const float *__restrict__ A, int M, int K, int nMB, int nKB, int k_chunks,
-                                uint8_t *__restrict__ out, float *__restrict__ packed)
+                                uint8_t *__restrict__ out, float *__restrict__ packed, int *status)
 {
+    // checked build, sites 10 (loads of A), 11 (pattern stores), 12 (stores into the packed copy), 13 (the warp's tile)
+    const size_t a_floats = (size_t)M * K, out_bytes = (size_t)nMB * nKB;
+    const size_t packed_floats = (size_t)((M + 127) / 128) * nKB * BK * 128;
     extern __shared__ __align__(16) float pack_smem[];
     float *tile = pack_smem + (threadIdx.x >> 5) * (PACK64_SMEM_PER_WARP / 4);
     const int lane = threadIdx.x & 31;
@@ -156,7 +175,8 @@ esmm_preprocess_a_pack64_kernel(const float *__restrict__ A, int M, int K, int n
         for (int i = 0; i < 16; ++i) {
             const int r = 2 * i + h;
             v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (col_ok && row0 + r < M) v[i] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K));
+            if (col_ok && row0 + r < M && bounds_ok((size_t)(row0 + r) * K + col + 4 <= a_floats, status, 10))
+                v[i] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)r * K));
         }
         unsigned nib = 0;
 #pragma unroll
@@ -171,6 +191,7 @@ esmm_preprocess_a_pack64_kernel(const float *__restrict__ A, int M, int K, int n
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
             const int pos = (2 * i + h + 2 * cl) & 31;
+            if (!bounds_ok((cl * 4 + 3) * 32 + pos < PACK64_SMEM_PER_WARP / 4, status, 13)) continue;
             if (nib & 1u) tile[(cl * 4 + 0) * 32 + pos] = v[i].x;
             if (nib & 2u) tile[(cl * 4 + 1) * 32 + pos] = v[i].y;
             if (nib & 4u) tile[(cl * 4 + 2) * 32 + pos] = v[i].z;
@@ -178,13 +199,16 @@ esmm_preprocess_a_pack64_kernel(const float *__restrict__ A, int M, int K, int n
         }
         const unsigned other = __shfl_xor_sync(0xFFFFFFFFu, nib, 1);
         const int kb_lane = kc * 8 + (cl >> 1);
-        if (h == 0 && !(cl & 1) && kb_lane < nKB) out[(size_t)mb * nKB + kb_lane] = (uint8_t)(nib | (other << 4));
+        if (h == 0 && !(cl & 1) && kb_lane < nKB && bounds_ok((size_t)mb * nKB + kb_lane < out_bytes, status, 11))
+            out[(size_t)mb * nKB + kb_lane] = (uint8_t)(nib | (other << 4));
         __syncwarp();
-        float *dst = packed + (size_t)(mb >> 2) * nKB * BK * 128 + (mb & 3) * 32 + lane;
+        const size_t dst0 = (size_t)(mb >> 2) * nKB * BK * 128 + (mb & 3) * 32 + lane;
+        float *dst = packed + dst0;
 #pragma unroll 8
         for (int c = 0; c < 64; ++c) {
             const int k = kc * 64 + c;  // global k = kb * 8 + kk
-            if (((liveq[c & 3] >> (c >> 2)) & 1u) && k < nKB * BK)
+            if (((liveq[c & 3] >> (c >> 2)) & 1u) && k < nKB * BK &&
+                bounds_ok(dst0 + (size_t)k * 128 < packed_floats, status, 12))
                 dst[(size_t)k * 128] = tile[c * 32 + ((lane + 2 * (c >> 2)) & 31)];
         }
         __syncwarp();
@@ -195,7 +219,7 @@ esmm_preprocess_a_pack64_kernel(const float *__restrict__ A, int M, int K, int n
 // alignment conditions do not hold.
 __global__ void esmm_preprocess_a_patterns_generic_kernel(const float *__restrict__ A, int M, int K,
                                                           int tile_m, int nMB, int nKB,
-                                                          uint8_t *__restrict__ out)
+                                                          uint8_t *__restrict__ out, int *status)
 {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)nMB * nKB) return;
@@ -204,7 +228,7 @@ __global__ void esmm_preprocess_a_patterns_generic_kernel(const float *__restric
     for (int r = mb * tile_m; r < min(M, (mb + 1) * tile_m); ++r)
         for (int k = 0; k < BK; ++k) {
             const int c = kb * BK + k;
-            if (c < K) pat |= nz(A[(size_t)r * K + c]) << k;
+            if (c < K && bounds_ok((size_t)r * K + c < (size_t)M * K, status, 10)) pat |= nz(A[(size_t)r * K + c]) << k;
         }
     out[idx] = (uint8_t)pat;
 }
@@ -215,8 +239,10 @@ __global__ void esmm_preprocess_a_patterns_generic_kernel(const float *__restric
 // bytes of the 4 K blocks.  Needs N % 4 == 0 and a 16-byte aligned B.
 __global__ void __launch_bounds__(PRE_THREADS)
 esmm_preprocess_b_patterns_kernel(const float *__restrict__ B, int K, int N, int nNB, int nKB,
-                                  int n_strips, int k_groups, uint8_t *__restrict__ out)
+                                  int n_strips, int k_groups, uint8_t *__restrict__ out, int *status)
 {
+    // checked build, sites 14 (loads of B) and 15 (pattern stores)
+    const size_t b_floats = (size_t)K * N, out_bytes = (size_t)nNB * nKB;
     const int lane = threadIdx.x & 31;
     const long warps_total = (long)gridDim.x * (PRE_THREADS / 32);
     const long tasks = (long)n_strips * k_groups;
@@ -235,7 +261,8 @@ esmm_preprocess_b_patterns_kernel(const float *__restrict__ B, int K, int N, int
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (col_ok && k0 + u < K) v[u] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)(k0 + u) * N));
+                if (col_ok && k0 + u < K && bounds_ok((size_t)(k0 + u) * N + col + 4 <= b_floats, status, 14))
+                    v[u] = __ldg(reinterpret_cast<const float4 *>(src + (size_t)(k0 + u) * N));
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -249,10 +276,11 @@ esmm_preprocess_b_patterns_kernel(const float *__restrict__ B, int K, int N, int
             if (nb < nNB) {
                 uint8_t *dst = out + (size_t)nb * nKB + kg * 4;
                 if (kg * 4 + 4 <= nKB && (nKB & 3) == 0) {
-                    *reinterpret_cast<uint32_t *>(dst) = word;
+                    if (bounds_ok((size_t)nb * nKB + kg * 4 + 4 <= out_bytes, status, 15)) *reinterpret_cast<uint32_t *>(dst) = word;
                 } else {
                     for (int g = 0; g < 4; ++g)
-                        if (kg * 4 + g < nKB) dst[g] = (uint8_t)(word >> (8 * g));
+                        if (kg * 4 + g < nKB && bounds_ok((size_t)nb * nKB + kg * 4 + g < out_bytes, status, 15))
+                            dst[g] = (uint8_t)(word >> (8 * g));
                 }
             }
         }
@@ -260,7 +288,7 @@ esmm_preprocess_b_patterns_kernel(const float *__restrict__ B, int K, int N, int
 }
 
 __global__ void esmm_preprocess_b_patterns_generic_kernel(const float *__restrict__ B, int K, int N,
-                                                          int nNB, int nKB, uint8_t *__restrict__ out)
+                                                          int nNB, int nKB, uint8_t *__restrict__ out, int *status)
 {
     const long idx = (long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long)nNB * nKB) return;
@@ -269,7 +297,8 @@ __global__ void esmm_preprocess_b_patterns_generic_kernel(const float *__restric
     for (int k = 0; k < BK; ++k) {
         const int r = kb * BK + k;
         if (r >= K) break;
-        for (int c = nb * PAT_N; c < min(N, (nb + 1) * PAT_N); ++c) pat |= nz(B[(size_t)r * N + c]) << k;
+        for (int c = nb * PAT_N; c < min(N, (nb + 1) * PAT_N); ++c)
+            if (bounds_ok((size_t)r * N + c < (size_t)K * N, status, 14)) pat |= nz(B[(size_t)r * N + c]) << k;
     }
     out[idx] = (uint8_t)pat;
 }
@@ -287,6 +316,7 @@ int preprocess_a_launch(const float *d_A, int M, int K, int tile_m, uint8_t *d_o
     if (!d_A || !d_out) return ESMM_ERR_NULL;
     if (M <= 0 || K <= 0 || tile_m <= 0) return ESMM_ERR_SHAPE;
     const int nMB = ceil_div(M, tile_m), nKB = ceil_div(K, BK);
+    int *status = kCheckedBuild ? device_status_ptr() : nullptr;   // only the checked build's kernels write it
     if ((K & 3) == 0 && ((uintptr_t)d_A & 15) == 0) {
         const int k_chunks = ceil_div(K, 128);
         const long tasks = (long)nMB * k_chunks;
@@ -296,11 +326,11 @@ int preprocess_a_launch(const float *d_A, int M, int K, int tile_m, uint8_t *d_o
         const long cap = (long)sms * 16 * 4;
         if (blocks > cap) blocks = cap;
         esmm_preprocess_a_patterns_kernel<<<(unsigned)blocks, PRE_THREADS, 0, stream>>>(
-            d_A, M, K, tile_m, nMB, nKB, k_chunks, d_out);
+            d_A, M, K, tile_m, nMB, nKB, k_chunks, d_out, status);
     } else {
         const long total = (long)nMB * nKB;
         esmm_preprocess_a_patterns_generic_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-            d_A, M, K, tile_m, nMB, nKB, d_out);
+            d_A, M, K, tile_m, nMB, nKB, d_out, status);
     }
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;
@@ -315,6 +345,7 @@ int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, flo
     const int nMB = ceil_div(M, 32), nKB = ceil_div(K, BK);
     const int sms = sm_count();
     if (sms <= 0) return record_cuda_error_text("no CUDA device");
+    int *status = kCheckedBuild ? device_status_ptr() : nullptr;
     if (tuning_get("PACK", 64) == 64) {
         const int k_chunks = ceil_div(K, 64);
         const long tasks = (long)nMB * k_chunks;
@@ -331,7 +362,7 @@ int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, flo
         const long cap = (long)sms * 6 * 8;
         if (blocks > cap) blocks = cap;
         esmm_preprocess_a_pack64_kernel<<<(unsigned)blocks, PACK_WARPS * 32, smem, stream>>>(
-            d_A, M, K, nMB, nKB, k_chunks, d_out, d_packed);
+            d_A, M, K, nMB, nKB, k_chunks, d_out, d_packed, status);
         ESMM_CUDA_TRY(cudaGetLastError());
         return ESMM_OK;
     }
@@ -350,7 +381,7 @@ int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, flo
     const long cap = (long)sms * 3 * 8;
     if (blocks > cap) blocks = cap;
     esmm_preprocess_a_pack_kernel<<<(unsigned)blocks, PACK_WARPS * 32, smem, stream>>>(
-        d_A, M, K, nMB, nKB, k_chunks, d_out, d_packed);
+        d_A, M, K, nMB, nKB, k_chunks, d_out, d_packed, status);
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;
 }
@@ -360,6 +391,7 @@ int preprocess_b_launch(const float *d_B, int K, int N, uint8_t *d_out, cudaStre
     if (!d_B || !d_out) return ESMM_ERR_NULL;
     if (K <= 0 || N <= 0) return ESMM_ERR_SHAPE;
     const int nNB = ceil_div(N, PAT_N), nKB = ceil_div(K, BK);
+    int *status = kCheckedBuild ? device_status_ptr() : nullptr;
     if ((N & 3) == 0 && ((uintptr_t)d_B & 15) == 0 && ((uintptr_t)d_out & 3) == 0) {
         const int n_strips = ceil_div(N, 128), k_groups = ceil_div(nKB, 4);
         const long tasks = (long)n_strips * k_groups;
@@ -369,11 +401,11 @@ int preprocess_b_launch(const float *d_B, int K, int N, uint8_t *d_out, cudaStre
         const long cap = (long)sms * 16 * 4;
         if (blocks > cap) blocks = cap;
         esmm_preprocess_b_patterns_kernel<<<(unsigned)blocks, PRE_THREADS, 0, stream>>>(
-            d_B, K, N, nNB, nKB, n_strips, k_groups, d_out);
+            d_B, K, N, nNB, nKB, n_strips, k_groups, d_out, status);
     } else {
         const long total = (long)nNB * nKB;
         esmm_preprocess_b_patterns_generic_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(
-            d_B, K, N, nNB, nKB, d_out);
+            d_B, K, N, nNB, nKB, d_out, status);
     }
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;

@@ -41,7 +41,8 @@ typedef enum esmm_status {
     ESMM_ERR_UNSUPPORTED = 7, /* kernel id or granularity this library does not provide */
     ESMM_ERR_VERIFY = 8,      /* verification against the reference result failed */
     ESMM_ERR_TOO_LARGE = 9,   /* K exceeds what the kernel's shared-memory masks can hold */
-    ESMM_ERR_MISMATCH = 10    /* cached pattern file does not match the requested shape */
+    ESMM_ERR_MISMATCH = 10,   /* cached pattern file does not match the requested shape */
+    ESMM_ERR_BOUNDS = 11      /* checked build only: a kernel computed an index outside its buffer (access skipped) */
 } esmm_status;
 
 const char *esmm_strerror(int status);
@@ -188,6 +189,20 @@ int esmm_sgemm_joint_static(int M, int N, int K, const float *d_A, const float *
 /* Synchronises `stream`, returns and clears the device status word:
  * ESMM_OK, ESMM_ERR_TIMEOUT (a bounded wait expired) or ESMM_ERR_CUDA. */
 int esmm_device_status(void *stream);
+
+/*
+ * The checked build (libesmm_b200_checked.so, same ABI, compiled with -DESMM_CHECKED) stands in for a
+ * memory sanitizer: its kernels test every shared- and global-memory index they compute and, instead of
+ * trapping, record ESMM_ERR_BOUNDS plus the site in the device status word and skip the access;
+ * esmm_device_status() then returns ESMM_ERR_BOUNDS and esmm_last_cuda_error() names the site.  The
+ * reference has only `#ifdef DEBUG` synchronisations (src/preprocessors/a_preprocessor_hybrid.cu:115-120).
+ *   esmm_checked_build            1 in the checked build, 0 in the product build.
+ *   esmm_selftest_bounds_report   launches one thread that reports a failed check WITHOUT making any
+ *                                 access: the next esmm_device_status() returns ESMM_ERR_BOUNDS in the checked
+ *                                 build and ESMM_OK in the product build.
+ */
+int esmm_checked_build(void);
+int esmm_selftest_bounds_report(void *stream);
 
 /*
  * Failure-path self test: launches one CTA that waits (bounded, `budget_us` microseconds, at most

@@ -51,7 +51,7 @@ def test_argument_validation_needs_no_device(pkg):
     assert L.esmm_run_kernel_pattern(14, 128, 128, 128, ok_ptr, ok_ptr, ok_ptr, 0, 0, 1, 0, 0, None, b"1111", None,
                                      None) == pkg.ERR_SHAPE
     assert L.esmm_interleave_shards(ok_ptr, ok_ptr, 8, 12, 2, 0) == pkg.ERR_SHAPE
-    for st in range(11):
+    for st in range(12):
         assert L.esmm_strerror(st)
 
 
