@@ -503,6 +503,51 @@ def run_ours(args) -> None:
             e2e_step()
         assert torch.equal(dA, c["A"])       # the replica assembled from the ranks' slices is A
         barrier()
+
+        # where the end-to-end step's time goes: each phase of a step alone (all ranks at once, nothing overlapped),
+        # device-timed on its own stream, max over ranks
+        def phase_ms(fn, stream):
+            barrier()
+            a, b = ev(), ev()
+            a.record(stream)
+            fn()
+            b.record(stream)
+            barrier()
+            return sharding.max_over_ranks(a.elapsed_time(b), dist, dev)
+
+        def only_h2d():
+            with torch.cuda.stream(s_up):
+                for i in range(n_chunks):
+                    r0 = i * rows_c + rank * rows_s
+                    dA[r0:r0 + rows_s].copy_(hA[i], non_blocking=True)
+
+        def only_allgather():
+            with torch.cuda.stream(s_up):
+                for i in range(n_chunks):
+                    rows = dA[i * rows_c:(i + 1) * rows_c]
+                    dist.all_gather_into_tensor(rows.view(-1), rows[rank * rows_s:(rank + 1) * rows_s].view(-1))
+
+        def only_compute():
+            for i in range(n_chunks):
+                rows = slice(i * rows_c, (i + 1) * rows_c)
+                pkg.sgemm_joint(rows_c, Nl, K, dA[rows].data_ptr(), c["B"].data_ptr(), Cd[rows].data_ptr(),
+                                c["bp"].data_ptr(), ws_c[i].data_ptr(), stream=s_run.cuda_stream)
+
+        def only_d2h():
+            with torch.cuda.stream(s_down):
+                hC.copy_(Cd, non_blocking=True)
+
+        breakdown = {
+            "h2d_ms": phase_ms(only_h2d, s_up), "allgather_ms": phase_ms(only_allgather, s_up),
+            "compute_ms": phase_ms(only_compute, s_run), "d2h_ms": phase_ms(only_d2h, s_down),
+            "h2d_bytes_per_rank": int(4 * M * K // world), "allgather_bytes_received_per_rank": int(4 * M * K * (world - 1) // world),
+            "d2h_bytes_per_rank": int(4 * M * Nl),
+            "note": "each phase alone, all ranks at once, max over ranks; the pipelined step overlaps them chunk by chunk",
+        }
+        breakdown["h2d_gbs_per_rank"] = breakdown["h2d_bytes_per_rank"] / (breakdown["h2d_ms"] * 1e-3) / 1e9
+        breakdown["d2h_gbs_per_rank"] = breakdown["d2h_bytes_per_rank"] / (breakdown["d2h_ms"] * 1e-3) / 1e9
+        breakdown["host_link_gbs_all_ranks"] = world * (breakdown["h2d_bytes_per_rank"] + breakdown["d2h_bytes_per_rank"]) / \
+            ((breakdown["h2d_ms"] + breakdown["d2h_ms"]) * 1e-3) / 1e9
         e2e_steps = max(1, min(args.steps, 10))
         t0 = time.perf_counter()
         for _ in range(e2e_steps):
@@ -512,7 +557,7 @@ def run_ours(args) -> None:
         pkg.device_status()
         e2e = {"value": flops_dense * e2e_steps / dt / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(4 * M * K), "d2h_bytes_per_step": int(4 * M * N),
-               "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps, "chunks": n_chunks,
+               "ms_per_step": dt / e2e_steps * 1e3, "steps": e2e_steps, "chunks": n_chunks, "breakdown": breakdown,
                "note": "whole job per step, in row chunks on three streams: every rank copies 1 / world of the chunk's "
                        "rows of A from pinned host memory, all-gather over NVLink, packing + GEMM on the rank's column "
                        "shard, the chunk of C back to pinned host memory; B and its patterns resident"}

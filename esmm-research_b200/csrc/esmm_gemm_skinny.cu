@@ -9,20 +9,28 @@
 //   * one CTA per 32-column strip of C (N / 32 CTAs, several resident per SM).  A strip is exactly one
 //     pattern block of B, so its live k are a_pat[0][kb] & b_pat[strip][kb]: every listed row is live
 //     for the whole CTA, there are no per-warp masks and no index lists in the inner loop;
-//   * all threads first build the strip's list of live k; then stages of 32 rows travel through a ring
-//     as 16-byte asynchronous copies (cp.async, one commit group per stage), every thread moving 4 of a
-//     stage's 512 pieces: per row 128 bytes of packed A (rows 0-31 of the first panel) and 128 of B;
-//   * four warps, one per SM sub-partition, hold 32 rows x 8 columns each, 4 rows x 2 columns per thread:
-//     per k a 16-byte and an 8-byte load and 4 two-wide FMAs (fma.rn.f32x2, 2 x 2 blocks as in the packed
-//     kernel).
+//   * all threads first build the strip's list of live k (pattern bytes read as 32-bit words); then stages of
+//     32 rows travel through a ring as 16-byte asynchronous copies (cp.async, one commit group per stage): per
+//     row 128 bytes of B and 128 bytes of packed A (rows 0-31 of the first panel), or only 64 bytes of A (rows
+//     0-15) when M <= 16 - the 16-row variant moves and multiplies half as much of A;
+//   * four warps, one per SM sub-partition, hold ROWS rows x 8 columns each, (ROWS / 8) rows x 2 columns per
+//     thread, as 2 x 2 blocks of two-wide FMAs (fma.rn.f32x2) like the packed kernel.  The operands of four rows
+//     are loaded (volatile, so that they stay put) one batch ahead of the multiply-adds that use them, two
+//     register sets in ping-pong: without that the compiler sank every load to its first use and a row cost a
+//     shared-memory round trip (36 cycles per row and warp measured; 26 with the batches).
 //
-// Variants measured on M = 16, N = 11008, K = 4096 (819 live k per strip): a tensor-copy producer warp
-// with two computing warps, a cp.async producer warp with four, one warp per strip with 8 x 4 outputs per
-// thread - all between 33 and 45 us against 55 us for the tiled kernel; this form is the simplest of the
-// fast ones.  The only waits are cp.async.wait_group and __syncthreads with a trip count common to all
-// threads: no flag or barrier that another agent has to signal, nothing that can wait forever.
+// Measured on M = 16, N = 11008, K = 4096 (819 live k per strip, 344 CTAs on 148 SMs), kernel alone, back to back:
+// 24.8 us (35.5 us before the 16-row variant and the batched loads; tiled kernel 49 us; cuBLAS 110 us).  What is
+// left: an SM holds 2 or 3 strips, i.e. 8-12 warps, and every asynchronous-copy or shared-load instruction costs its
+// warp tens of cycles of issue whatever its width (a warp-wide 16-byte cp.async: about 26 cycles, measured), so the
+// row rate is set by the number of such instructions, not by bytes.  Variants measured and dropped: a tensor-copy
+// producer warp with two computing warps, a cp.async producer warp with four, one warp per strip with 8 x 4 outputs per
+// thread (33-45 us, before batching); two warps per strip, 16 columns and (ROWS / 8) x 4 outputs per thread each, with
+// private rings and no barrier in the main loop (28.2 us at M = 16, 49.3 us at M = 32: twice the copy instructions per
+// warp) or on one shared ring (28.9 / 37.4 us).
+// The only waits are cp.async.wait_group and __syncthreads with a trip count common to all threads: no flag or
+// barrier that another agent has to signal, nothing that can wait forever.
 #include <cstring>
-#include <type_traits>
 
 #include "esmm_gemm_shared.cuh"
 
@@ -272,210 +280,6 @@ esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
         }
 }
 
-// ---------------------------------------------------------------------------------------------------------------
-// Second form: warp-private pipelines.  A strip is shared by TWO warps, 16 columns each, and the two never meet
-// after the strip's list of live k has been built: every warp fetches what it needs itself - per live k the 64 or
-// 128 bytes of packed A and the 64 bytes of its half of B's row - into a ring of its own, waits only for its own
-// copies (cp.async.wait_group + __syncwarp) and multiplies.  There is no barrier in the main loop and no stage
-// that waits for the slowest of several warps; the price is that A travels from L2 twice.  A thread holds
-// (ROWS / 8) rows x 4 columns; operands of four rows are loaded one batch ahead of the multiply-adds.
-// ---------------------------------------------------------------------------------------------------------------
-constexpr int ST_WARPS = 2;
-constexpr int ST_THREADS = ST_WARPS * 32;
-constexpr int ST_WCOLS = SK_COLS / ST_WARPS;     // 16 columns per warp
-constexpr int ST_B_ROW_BYTES = ST_WCOLS * 4;     // 64
-constexpr int ST_STAGE_ROWS = 32;
-constexpr int ST_STAGES = 6;
-
-template <int ROWS>
-__global__ void __launch_bounds__(ST_THREADS)
-esmm_joint_sgemm_strip_kernel(const SkinnyParams p)
-{
-    constexpr int A_ROW_BYTES = ROWS * 4;
-    constexpr int A_CHUNKS = A_ROW_BYTES / 16;                       // 16-byte pieces per row of A: 4 or 8
-    constexpr int A_HALF = ST_STAGE_ROWS * A_ROW_BYTES;
-    constexpr int STAGE_BYTES = A_HALF + ST_STAGE_ROWS * ST_B_ROW_BYTES;
-    constexpr int RING_BYTES = ST_STAGES * STAGE_BYTES;              // per warp
-    constexpr int RP = ROWS / 16;                                    // row pairs per thread
-    constexpr int BATCH = 4;
-    extern __shared__ __align__(1024) char smem[];
-    // layout: ring of warp 0 | ring of warp 1 | krow (u16 x cap) | warp sums
-    uint16_t *krow = reinterpret_cast<uint16_t *>(smem + ST_WARPS * RING_BYTES);
-    volatile int *wsum = reinterpret_cast<volatile int *>(smem + ST_WARPS * RING_BYTES + ((p.cap * 2 + 15) & ~15));
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int strip = blockIdx.x;
-    SK_STAMP(0);
-
-    // ---------------- the strip's list of live k (both warps together, once) ----------------
-    {
-        constexpr int MAX_WORDS = SK_MAX_KP / BK / ST_THREADS / 4;   // words of 4 K blocks per thread at most (8)
-        const uint8_t *bp = p.b_pat + (size_t)strip * p.nKB;
-        const int per = ((p.nKB + ST_THREADS - 1) / ST_THREADS + 3) & ~3;
-        const int kb_lo = min((int)threadIdx.x * per, p.nKB), kb_hi = min(kb_lo + per, p.nKB);
-        const bool words = (p.nKB & 3) == 0 && ((reinterpret_cast<uintptr_t>(p.a_pat) | reinterpret_cast<uintptr_t>(bp)) & 3) == 0;
-        unsigned live[MAX_WORDS];
-        int c = 0;
-#pragma unroll
-        for (int w = 0; w < MAX_WORDS; ++w) {
-            const int kb = kb_lo + 4 * w;
-            unsigned v = 0u;
-            if (kb < kb_hi) {
-                if (words) {
-                    v = *reinterpret_cast<const unsigned *>(p.a_pat + kb) & *reinterpret_cast<const unsigned *>(bp + kb);
-                } else {
-                    for (int j = 0; j < 4 && kb + j < kb_hi; ++j) v |= (unsigned)(p.a_pat[kb + j] & bp[kb + j]) << (8 * j);
-                }
-            }
-            live[w] = v;
-            c += __popc(v);
-        }
-        const int incl = sk_scan(c, lane);
-        if (lane == 31) wsum[warp] = incl;
-        __syncthreads();
-        int q = incl - c;
-        for (int w = 0; w < warp; ++w) q += wsum[w];
-#pragma unroll
-        for (int w = 0; w < MAX_WORDS; ++w) {
-            unsigned v = live[w];
-            while (v) {
-                const int bit = __ffs((int)v) - 1;                   // bit 8 j + kk: K block kb_lo + 4 w + j, offset kk
-                if (bounds_ok(q < p.cap, p.status, 30)) krow[q] = (uint16_t)((kb_lo + 4 * w) * BK + bit);
-                ++q;
-                v &= v - 1u;
-            }
-        }
-        __syncthreads();   // the last time the two warps wait for each other
-    }
-    int n = 0;
-#pragma unroll
-    for (int w = 0; w < ST_WARPS; ++w) n += wsum[w];
-    const int num_stages = (n + ST_STAGE_ROWS - 1) / ST_STAGE_ROWS;
-    SK_STAMP(1);
-
-    // ---------------- this warp's copies: lane = (row of a group of 8, 16-byte piece) ----------------
-    const uint32_t ring = smem_u32(smem) + (uint32_t)warp * RING_BYTES;
-    const int wcol0 = strip * SK_COLS + warp * ST_WCOLS;
-    const int piece = lane & 3, prow = lane >> 2;                    // B: 4 pieces per row, 8 rows per pass
-    const bool bcol_ok = wcol0 + piece * 4 < p.N;
-    auto issue = [&](int stage) {
-        if (stage < num_stages) {
-            const int r0 = stage * ST_STAGE_ROWS, cnt = min(ST_STAGE_ROWS, n - r0);
-            const uint32_t s0 = ring + (uint32_t)(stage % ST_STAGES) * STAGE_BYTES;
-#pragma unroll
-            for (int i = 0; i < ST_STAGE_ROWS / 8; ++i) {
-                const int r = i * 8 + prow;
-                if (r < cnt && bounds_ok(r0 + r < p.cap, p.status, 31)) {
-                    const int k = krow[r0 + r];
-                    if (!bounds_ok(k >= 0 && k < p.kp, p.status, 32)) continue;
-                    const float *a_src = p.a_packed + (size_t)k * TILE_M + piece * 4;
-#pragma unroll
-                    for (int h = 0; h < A_CHUNKS / 4; ++h)             // 4 (or 2 x 4) pieces of this row of A
-                        cp_async_16(s0 + r * A_ROW_BYTES + (h * 4 + piece) * 16, a_src + h * 16, 16);
-                    const bool b_ok = bcol_ok && k < p.K;              // outside B: zero fill
-                    cp_async_16(s0 + A_HALF + r * ST_B_ROW_BYTES + piece * 16,
-                                b_ok ? p.B + (size_t)k * p.N + wcol0 + piece * 4 : p.B, b_ok ? 16 : 0);
-                }
-            }
-        }
-        cp_async_commit();   // one group per stage, empty past the end: the wait below counts groups
-    };
-
-    // ---------------- (ROWS / 8) rows x 4 columns per thread ----------------
-    // every 4 consecutive lanes touch 2 row groups x 2 column quads (few distinct bytes per load)
-    const int rg = (lane >> 1) & 7;                              // group of ROWS / 8 consecutive rows
-    const int cq = (lane & 1) | ((lane >> 4) << 1);              // quad of columns within the warp's 16
-    const uint32_t tA = ring + rg * (ROWS / 2);
-    const uint32_t tB = ring + A_HALF + cq * 16;
-    // block (pr, j): rows 2 pr, 2 pr + 1 of the thread's rows x columns 2 j, 2 j + 1 of its quad:
-    // diag = (c[r0][c0], c[r1][c1]), anti = (c[r0][c1], c[r1][c0])
-    float2 diag[RP][2], anti[RP][2];
-#pragma unroll
-    for (int i = 0; i < RP; ++i)
-#pragma unroll
-        for (int j = 0; j < 2; ++j) diag[i][j] = anti[i][j] = make_float2(0.0f, 0.0f);
-
-    struct Ops {
-        float2 a[BATCH][RP];
-        float4 b[BATCH];
-    };
-    auto load_rows = [&](Ops &o, uint32_t sA, uint32_t sB, int r) {
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) {
-            const uint32_t pa = sA + (uint32_t)((r + i) * A_ROW_BYTES), pb = sB + (uint32_t)((r + i) * ST_B_ROW_BYTES);
-            if (RP == 2)
-                asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                             : "=f"(o.a[i][0].x), "=f"(o.a[i][0].y), "=f"(o.a[i][RP - 1].x), "=f"(o.a[i][RP - 1].y) : "r"(pa));
-            else
-                asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(o.a[i][0].x), "=f"(o.a[i][0].y) : "r"(pa));
-            asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];"
-                         : "=f"(o.b[i].x), "=f"(o.b[i].y), "=f"(o.b[i].z), "=f"(o.b[i].w) : "r"(pb));
-        }
-    };
-    auto fma_rows = [&](const Ops &o, int count) {
-#pragma unroll
-        for (int i = 0; i < BATCH; ++i) {
-            if (i < count) {
-                const float2 b01 = make_float2(o.b[i].x, o.b[i].y), b10 = make_float2(o.b[i].y, o.b[i].x);
-                const float2 b23 = make_float2(o.b[i].z, o.b[i].w), b32 = make_float2(o.b[i].w, o.b[i].z);
-#pragma unroll
-                for (int pr = 0; pr < RP; ++pr) {
-                    diag[pr][0] = __ffma2_rn(o.a[i][pr], b01, diag[pr][0]);
-                    anti[pr][0] = __ffma2_rn(o.a[i][pr], b10, anti[pr][0]);
-                    diag[pr][1] = __ffma2_rn(o.a[i][pr], b23, diag[pr][1]);
-                    anti[pr][1] = __ffma2_rn(o.a[i][pr], b32, anti[pr][1]);
-                }
-            }
-        }
-    };
-
-#pragma unroll
-    for (int s = 0; s < ST_STAGES - 1; ++s) issue(s);
-    for (int s = 0; s < num_stages; ++s) {
-        cp_async_wait_group<ST_STAGES - 2>();   // this lane's pieces of stage s have landed ...
-        __syncwarp();                           // ... every lane's have, and every lane is done with stage s - 1
-        issue(s + ST_STAGES - 1);               // into the slot of stage s - 1
-        if (warp == 0) SK_STAMP(10 + s);
-        const int cnt = min(ST_STAGE_ROWS, n - s * ST_STAGE_ROWS);
-        const uint32_t sA = tA + (uint32_t)(s % ST_STAGES) * STAGE_BYTES;
-        const uint32_t sB = tB + (uint32_t)(s % ST_STAGES) * STAGE_BYTES;
-        // (a batch loaded past the stage's last row reads the next slot, the other warp's ring or the row list: in
-        // bounds, never multiplied)
-        Ops x, y;
-        load_rows(x, sA, sB, 0);
-        if (cnt == ST_STAGE_ROWS) {
-#pragma unroll 1
-            for (int r = 0; r < ST_STAGE_ROWS; r += 2 * BATCH) {
-                load_rows(y, sA, sB, r + BATCH);
-                fma_rows(x, BATCH);
-                load_rows(x, sA, sB, r + 2 * BATCH);
-                fma_rows(y, BATCH);
-            }
-        } else {
-#pragma unroll 1
-            for (int r = 0; r < cnt; r += BATCH) {
-                fma_rows(x, min(BATCH, cnt - r));
-                load_rows(x, sA, sB, r + BATCH);
-            }
-        }
-        if (warp == 0) SK_STAMP(200 + s);
-    }
-    cp_async_wait_group<0>();   // nothing of this thread is in flight when it leaves
-    SK_STAMP(5);
-
-    // C is overwritten (beta = 0); un-scramble the 2 x 2 blocks into rows of 4 columns
-    const int col = wcol0 + cq * 4;
-#pragma unroll
-    for (int pr = 0; pr < RP; ++pr)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int r = rg * (ROWS / 8) + 2 * pr + e;
-            const float4 v = e == 0 ? make_float4(diag[pr][0].x, anti[pr][0].x, diag[pr][1].x, anti[pr][1].x)
-                                    : make_float4(anti[pr][0].y, diag[pr][0].y, anti[pr][1].y, diag[pr][1].y);
-            if (r < p.M && col < p.N && bounds_ok((size_t)r * p.N + col + 4 <= (size_t)p.M * p.N, p.status, 33))
-                *reinterpret_cast<float4 *>(p.C + (size_t)r * p.N + col) = v;
-        }
-}
-
 #ifdef ESMM_TRACE
 extern "C" int esmm_sk_trace_read(unsigned long long *host, int n)
 {
@@ -509,23 +313,7 @@ int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const fl
     p.status = device_status_ptr();
     if (!p.status) return ESMM_ERR_CUDA;
     const bool rows16 = M <= 16 && tuning_get("SKINNY_ROWS", 0) != 32;
-    if (tuning_get("SKINNY_SHARED", 1) == 0) {   // (the warp-private form is opt-in until it has been measured)
-        // warp-private pipelines: two rings, row list, one int per warp
-        const size_t ring = (size_t)ST_STAGES * ST_STAGE_ROWS * ((rows16 ? 16 : 32) * 4 + ST_B_ROW_BYTES);
-        const size_t smem = ST_WARPS * ring + ((p.cap * 2 + 15) & ~15) + 16;
-        if (rows16) {
-            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_strip_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)smem));
-            esmm_joint_sgemm_strip_kernel<16><<<ceil_div(N, SK_COLS), ST_THREADS, smem, stream>>>(p);
-        } else {
-            ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_strip_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               (int)smem));
-            esmm_joint_sgemm_strip_kernel<32><<<ceil_div(N, SK_COLS), ST_THREADS, smem, stream>>>(p);
-        }
-        ESMM_CUDA_TRY(cudaGetLastError());
-        return ESMM_OK;
-    }
-    // one ring per CTA: ring, row list, one int per warp
+    // ring, row list, one int per warp
     const size_t stage_bytes = (size_t)SK_STAGE_ROWS * ((rows16 ? 16 : 32) * 4 + SK_ROW_BYTES);
     const size_t smem = (size_t)SK_STAGES * stage_bytes + ((p.cap * 2 + 15) & ~15) + (SK_WARPS * 4 + 15) / 16 * 16;
     if (rows16) {

@@ -255,15 +255,18 @@ def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, tuning, rows):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
-@pytest.mark.parametrize("skinny", [1, 0])
-def test_gemm_few_rows(cuda, pkg, oracle_mod, tuning, skinny):
-    """M <= 32 (one pattern block of A) and N >= 128 runs the strip kernel (one CTA per 32 columns); the same
-    inputs with that kernel switched off go through the tiled kernel.  Same bits as the oracle either way."""
-    if not skinny:
+@pytest.mark.parametrize("form", ["strip", "strip32", "tiled"])
+def test_gemm_few_rows(cuda, pkg, oracle_mod, tuning, form):
+    """M <= 32 (one pattern block of A) and N >= 128 runs the strip kernel (one CTA per 32 columns), which has a
+    16-row variant for M <= 16 (`strip32` forces the 32-row one); the same inputs with that kernel switched off go
+    through the tiled kernel.  Same bits as the oracle every way."""
+    if form == "tiled":
         tuning("NO_SKINNY", 1)
+    if form.endswith("32"):
+        tuning("SKINNY_ROWS", 32)
     for M, N, K, pa, pb in [(16, 256, 256, 0.5, 0.5), (32, 1408, 1024, 0.4, 0.6), (1, 128, 64, 1.0, 1.0),
                             (31, 132, 8 * 37, 0.7, 0.3), (8, 512, 4096, 0.2, 0.9), (32, 160, 76, 0.8, 0.8),
-                            (24, 256, 2048, 0.0, 0.5)]:
+                            (24, 256, 2048, 0.0, 0.5), (16, 11008, 4096, 0.4, 0.5), (9, 140, 16384, 0.3, 0.3)]:
         A, B = workloads.tile_random(M, N, K, pa, pb, seed=M + N + K, gran_a=32, gran_b=32)
         check_all_paths(cuda, pkg, oracle_mod, A, B)
     for pat in (0xFF, 0x0F, 0x81):
