@@ -56,19 +56,19 @@ constexpr int ROWS_PER_STAGE = 32;
 constexpr int STAGE_HALF_BYTES = ROWS_PER_STAGE * ROW_BYTES;   // 16384: A rows, then B rows
 constexpr int PSTAGE_BYTES = 2 * STAGE_HALF_BYTES;             // 32768
 constexpr int P_CONSUMER_WARPS = 8;
-// Issuing a tensor copy costs the issuing warp about 70 cycles per active lane, whatever the box size,
-// and different warps issue in parallel (measured: 32, 64 and 128 single-row copies from 1, 2 and 4
-// warps all land within the same 2200 cycles).  A stage fetched row by row is 64 copies, so the rows
-// of a stage are spread over several producer warps.
-// Three of them: with the 8 consumer warps and the mask warp that is 12 warps, 3 per SM sub-partition,
-// which leaves each thread up to 168 registers (a 13th warp would cap them at 128).
-#ifndef ESMM_TMA_WARPS
-#define ESMM_TMA_WARPS 3
-#endif
-constexpr int P_TMA_WARPS = ESMM_TMA_WARPS;                    // 1 .. 3
+// Issuing a copy costs the issuing warp about 50 cycles per copy, whatever the mechanism (2-D tensor copy of one row
+// or of an 8-row box, untiled bulk copy, or a warp-wide 16-byte cp.async per row: 3300 cycles for the 64 copies of a
+// row-by-row stage from one warp, 1270 from three, 970 from four - measured), and different warps issue in parallel.
+// So the rows of a stage are shared out among several producer warps.
+//   3 producer warps: 8 consumer + 3 producer + 1 mask warp = 12 warps, 3 per SM sub-partition, every thread with
+//     the 168 registers a 384-thread CTA allows (the consumers need about 150).  The default.
+//   7 producer warps: 16 warps.  A 512-thread CTA starts with 128 registers per thread; the two warp groups of
+//     consumers raise their allowance and the two warp groups of producers / mask warp lower theirs (setmaxnreg),
+//     so that row-by-row stages are posted about twice as fast.  Measured at 4096^3: independent 32-granular
+//     patterns at 0.2 / 0.2 0.429 -> 0.335 ms and 64-granular 0.207 -> 0.189 ms, but dense and uniform patterns 1.4%
+//     slower and block-pruned operands 7-8% slower (seven warps take the same per-stage decisions and wait on the
+//     same barriers).  Opt-in: esmm_tuning_set("PRODUCER_WARPS", 7).
 constexpr int P_TMA_WARP = P_CONSUMER_WARPS;                   // first producer warp
-constexpr int P_MASK_WARP = P_CONSUMER_WARPS + P_TMA_WARPS;
-constexpr int P_THREADS = (P_CONSUMER_WARPS + P_TMA_WARPS + 1) * 32;
 constexpr int P_MAX_STAGES = 6;
 
 // Optional timeline for tuning (build with -DESMM_TRACE): CTA 0 stamps %globaltimer at a few points
@@ -139,7 +139,7 @@ __device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar)
 #endif
 // arrivals a stage's full barrier expects: the byte count posted by producer 0, plus - when rows come by
 // cp.async - one arrival per other producer warp after it has tied its copies to the barrier
-constexpr int FULL_ARRIVALS = ESMM_ROW_COPY == 1 ? P_TMA_WARPS : 1;
+
 
 __device__ __forceinline__ void bulk_copy_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
 {
@@ -540,10 +540,15 @@ __device__ __forceinline__ int tile_list(const PackedParams &p, int tm, int tn, 
     return pos;
 }
 
-template <int WMB>
-__global__ void __launch_bounds__(P_THREADS, 1)
+template <int WMB, int NPW>
+__global__ void __launch_bounds__((P_CONSUMER_WARPS + NPW + 1) * 32, 1)
 esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const PackedParams p)
 {
+    static_assert(NPW == 3 || NPW == 7, "consumers, producers and the mask warp fill whole warp groups");
+    constexpr int P_TMA_WARPS = NPW;
+    constexpr int P_MASK_WARP = P_CONSUMER_WARPS + NPW;
+    constexpr bool P_REBALANCE_REGS = NPW == 7;
+    constexpr int FULL_ARRIVALS = ESMM_ROW_COPY == 1 ? NPW : 1;
     constexpr int TM_ROWS = 64 * WMB;                  // rows of a tile of C: 128 or 64
     constexpr int RB = 2 * WMB;                        // 32-row blocks per tile
     constexpr int A_ROW = TM_ROWS * 4;                 // bytes of one k of the A tile in shared memory
@@ -583,7 +588,10 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
     bool ok = true;
     if (warp == 0) ESMM_STAMP(0);
 
+    // (16-warp form: registers move from the producer / mask warp groups to the consumer warp groups; 8 x 32 x 184 +
+    // 8 x 32 x 64 = 63488 of the 65536 the CTA starts with.  Each instruction heads its own side's code.)
     if (warp == P_MASK_WARP) {
+        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         // ---------------- mask warp: the tile's list of live k rows ----------------
         int it = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
@@ -679,6 +687,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             if (it == 0) ESMM_STAMP(1);
         }
     } else if (warp >= P_TMA_WARP) {
+        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
         // ---------------- producer warps: one lane per row of the stage ----------------
         // All of them walk the row list and take the same decisions; producer q issues the copies of
         // rows 32 q / P .. of each stage, producer 0 also the stage's byte count and whole-stage boxes.
@@ -842,6 +851,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             }
         }
     } else {
+        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
         // ---------------- consumer warps: 32 WMB rows x 32 columns of the tile each ----------------
         const int wm = warp >> 2, wn = warp & 3;              // 2 x 4 warps
         const int lm = (lane >> 1) & 7;                       // group of 4 rows within a 32-row block
@@ -1076,15 +1086,17 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     int grid = tuning_get("GRID", sms);
     if (grid > p.num_tiles) grid = p.num_tiles;
     if (grid < 1) grid = 1;
-    if (tile_rows == 64) {
-        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<1>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total));
-        esmm_joint_sgemm_packed_kernel<1><<<grid, P_THREADS, L.total, stream>>>(maps, p);
-    } else {
-        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<2>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total));
-        esmm_joint_sgemm_packed_kernel<2><<<grid, P_THREADS, L.total, stream>>>(maps, p);
-    }
+    const bool wide = tuning_get("PRODUCER_WARPS", 3) == 7;
+    auto launch = [&](auto kernel, int threads) -> int {
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total));
+        kernel<<<grid, threads, L.total, stream>>>(maps, p);
+        return ESMM_OK;
+    };
+    const int threads = (P_CONSUMER_WARPS + (wide ? 7 : 3) + 1) * 32;
+    int lst;
+    if (tile_rows == 64) lst = wide ? launch(esmm_joint_sgemm_packed_kernel<1, 7>, threads) : launch(esmm_joint_sgemm_packed_kernel<1, 3>, threads);
+    else lst = wide ? launch(esmm_joint_sgemm_packed_kernel<2, 7>, threads) : launch(esmm_joint_sgemm_packed_kernel<2, 3>, threads);
+    if (lst != ESMM_OK) return lst;
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;
 }

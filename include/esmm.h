@@ -219,7 +219,7 @@ int esmm_selftest_bounded_wait(unsigned budget_us, void *stream);
  * environment cannot change what the library does.  No counterpart in the reference, whose tile
  * shapes are compile-time template constants (include/runners.cuh:830-838).
  * Names: TILE_M (64 | 128), STAGES, BROW_BITS, ROW_DENSITY, FORCE_LISTED, NO_RUN_TILES, VEC_PATTERNS
- * (0 | 4 | 16), NO_SKINNY, SKINNY_ROWS (32), GRID, PACK (64 | 128), SWIZZLE, TF32_PAIR (0 | 128 | 256), TF32_SPLIT_LAST,
+ * (0 | 4 | 16), NO_SKINNY, SKINNY_ROWS (32), PRODUCER_WARPS (3 | 7), GRID, PACK (64 | 128), SWIZZLE, TF32_PAIR (0 | 128 | 256), TF32_SPLIT_LAST,
  * TF32_DIRECT_STORES.  esmm_tuning_set returns ESMM_ERR_UNSUPPORTED for any other name;
  * esmm_tuning_reset returns every hook to "unset" (the library's own choice).
  */
@@ -358,7 +358,7 @@ void esmm_print_usage(const char *program_name, int additive);
  *                             what is there.
  *   esmm_multi_fill           device-side generator instead of an upload (esmm_fill_normal): the same A on every
  *                             device (seed), B's block on rank g from seed + 1 + g.
- *   esmm_multi_run            `runs` times esmm_sgemm_joint on every device, the devices' loops started together;
+ *   esmm_multi_run            one untimed call, then `runs` times esmm_sgemm_joint on every device, the devices' loops started together;
  *                             ms_per_gpu[g] = that device's CUDA-event time per run, *ms_max the slowest (the
  *                             whole-box time).  A bounded device wait that gave up returns ESMM_ERR_TIMEOUT.
  *   esmm_multi_download       the blocks of C into a host M x N matrix, device by device, no collective.

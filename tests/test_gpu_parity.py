@@ -255,6 +255,26 @@ def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, tuning, rows):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
+@pytest.mark.parametrize("rows", [128, 64])
+def test_gemm_seven_producer_warps(cuda, pkg, oracle_mod, tuning, rows):
+    """The 16-warp form of the tiled kernel (7 producer warps, registers moved between warp groups with setmaxnreg;
+    esmm_tuning_set("PRODUCER_WARPS", 7)): run tiles, row-by-row stages, 8-row boxes, ragged edges, both tile
+    heights - the same bits as the oracle as with the default 12 warps."""
+    tuning("PRODUCER_WARPS", 7)
+    tuning("TILE_M", int(rows))
+    for pat in (0xFF, 0x0F, 0x01):
+        A, B = workloads.uniform_pattern(256, 384, 512, pat, seed=pat)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    for M, N, K, pa, pb, ga in [(512, 512, 1024, 0.2, 0.2, 32), (384, 256, 2048, 0.5, 0.5, 64), (257, 260, 1000, 0.4, 0.4, 32),
+                                (100, 132, 8 * 37, 0.3, 0.7, 32), (256, 512, 8192 + 128, 0.3, 0.5, 32)]:
+        A, B = workloads.tile_random(M, N, K, pa, pb, seed=M + K, gran_a=ga, gran_b=32)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.block_random(384, 512, 1024, 0.3, 0.4, seed=9)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.llm_mlp(256, 1408, 1024, seed=4)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
 @pytest.mark.parametrize("form", ["strip", "strip32", "tiled"])
 def test_gemm_few_rows(cuda, pkg, oracle_mod, tuning, form):
     """M <= 32 (one pattern block of A) and N >= 128 runs the strip kernel (one CTA per 32 columns), which has a
