@@ -207,20 +207,13 @@ struct Acc {
     float2 diag[4][4], anti[4][4];
 };
 
-#ifndef ESMM_ANTI_SCALAR
-#define ESMM_ANTI_SCALAR 0
-#endif
-// One 2 x 2 block: the diagonal pair as one two-wide FMA; the anti-diagonal pair either as a second two-wide FMA on
-// the swapped column pair or (ESMM_ANTI_SCALAR) as two scalar FMAs, which need no swapped pair.
+// One 2 x 2 block: the diagonal pair and the anti-diagonal pair, one two-wide FMA each (the second on the swapped column
+// pair).  (The anti-diagonal pair as two scalar FMAs instead - no swapped operands, 48 instead of 32 multiply-add
+// instructions per row - was measured 23 % slower on the dense path.)
 __device__ __forceinline__ void fma_block(float2 &diag, float2 &anti, float2 ar, float bx, float by)
 {
     diag = __ffma2_rn(ar, make_float2(bx, by), diag);
-#if ESMM_ANTI_SCALAR
-    anti.x = fmaf(ar.x, by, anti.x);
-    anti.y = fmaf(ar.y, bx, anti.y);
-#else
     anti = __ffma2_rn(ar, make_float2(by, bx), anti);
-#endif
 }
 
 __device__ __forceinline__ void fma_pair_row(Acc &c, int p, float2 ar, const KFrag &f)
@@ -247,17 +240,14 @@ __device__ __forceinline__ void fma_bottom(Acc &c, const KFrag &f)
 // loop trip (measured: 4 rows 1 % slower than 8, 16 rows 1.6 % faster, 32 no better than 16),
 // so that the compiler can issue the loads of a row under the multiply-adds of the row before.
 template <int WMB>
-__device__ __forceinline__ bool dense_rows(Acc &acc, const char *sA, const char *sB, uint32_t next_full, uint32_t next_parity)
+__device__ __forceinline__ void dense_rows(Acc &acc, const char *sA, const char *sB)
 {
     constexpr int A_ROW = 256 * WMB;   // bytes of one k of the A tile
-    // (A rolling prefetch across the loop's back edge was measured slower than this form.)
+    // (Measured and dropped: a rolling prefetch across the loop's back edge; a non-blocking look at the next stage's
+    // barrier under the last multiply-adds of this one, so that the wait at the stage change is skipped - no gain.)
 #ifndef ESMM_DENSE_UNROLL
 #define ESMM_DENSE_UNROLL 16
 #endif
-#ifndef ESMM_POLL_NEXT
-#define ESMM_POLL_NEXT 0
-#endif
-    bool next_ready = false;
 #pragma unroll 1
     for (int r0 = 0; r0 < ROWS_PER_STAGE; r0 += ESMM_DENSE_UNROLL) {
 #pragma unroll
@@ -266,11 +256,7 @@ __device__ __forceinline__ bool dense_rows(Acc &acc, const char *sA, const char 
             fma_top(acc, f);
             if (WMB == 2) fma_bottom(acc, f);
         }
-        // has the next stage landed already?  One non-blocking look while the multiply-adds above are still in the
-        // pipe: the wait at the stage change is then skipped.
-        if (ESMM_POLL_NEXT && r0 + ESMM_DENSE_UNROLL >= ROWS_PER_STAGE) next_ready = mbar_test_wait(next_full, next_parity);
     }
-    return next_ready;
 }
 
 // ---- stages that are not all-live ------------------------------------------------------------------
@@ -888,7 +874,6 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             // masks of the next stage are formed under the multiply-adds of the current one (the list's
             // buffer is padded by one stage, so reading one stage past the end is harmless).
             unsigned rm = run_tile ? 0xFFu : rmask[lane];   // (cap >= 64: the first stage is always inside the list)
-            bool stage_ready = false;   // the stage's full barrier was already seen complete (dense_rows' look ahead)
             for (int r0 = 0; r0 < n; r0 += ROWS_PER_STAGE) {
                 unsigned jt = 0xFFFFFFFFu, jb = 0xFFFFFFFFu;   // a run tile: every row live for every block
                 if (!run_tile) {
@@ -905,22 +890,18 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     if (WMB == 2) cnt_b = build_list(wlist_b, jb, lane, p.status);
                     __syncwarp();
                 }
-                if (!stage_ready) ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
+                ok = mbar_wait(full0 + 8 * slot, phase, abort_flag);
                 if (!ok) break;
                 if (!bounds_ok(slot >= 0 && slot < p.stages && L.stage_off + (uint32_t)(slot + 1) * PSTAGE_BYTES <= L.krow_off,
                                p.status, 24)) {
                     ok = false;   // a stage outside the ring: leave through the time-out path rather than read it
                     break;
                 }
-                stage_ready = false;
                 const char *sA = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + a_thr;
                 const char *sB = smem + L.stage_off + (size_t)slot * PSTAGE_BYTES + b_thr;
                 if (warp == 0 && it == 0) ESMM_STAMP(10 + r0 / ROWS_PER_STAGE);
                 if (dense) {
-                    const int nslot = slot + 1 == p.stages ? 0 : slot + 1;
-                    // (the look ahead stays inside the tile: the next tile's first stage is awaited normally)
-                    stage_ready = dense_rows<WMB>(acc, sA, sB, full0 + 8 * nslot, nslot == 0 ? phase ^ 1 : phase) &&
-                                  r0 + ROWS_PER_STAGE < n;
+                    dense_rows<WMB>(acc, sA, sB);
                 } else if (WMB == 1) {
                     listed_rows<MODE_TOP, 1>(acc, sA, sB, wlist_t, cnt_t);
                 } else if (jt == jb) {
