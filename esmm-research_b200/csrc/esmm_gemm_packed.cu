@@ -93,6 +93,7 @@ struct PackedParams {
     int a_rows;      // rows of the A pattern array (ceil(M / 32))
     int b_rows;      // rows of the B pattern array (ceil(N / 32))
     int tiles_m, tiles_n, num_tiles;
+    int group_m;     // tile rows per raster group
     int stages;
     int brow_bits;   // K blocks with more live k than this are fetched whole
     int row_density; // ... on tiles with at most this many live k per K block on average; denser tiles
@@ -585,7 +586,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             ok = mbar_wait(lempty0 + 8 * buf, ((it >> 1) & 1) ^ 1, abort_flag);
             if (!ok) break;
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m);
             uint16_t *krow = reinterpret_cast<uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
             uint8_t *rmask = reinterpret_cast<uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
             // A first pass over the tile's pattern bytes decides the listing policy.
@@ -691,7 +692,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
             if (!ok) break;
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m);
             const uint16_t *krow = reinterpret_cast<const uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
             const int n = nrows[buf];
             const int run_code = runinfo[buf];
@@ -855,7 +856,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
             if (!ok) break;
             int tm, tn;
-            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn);
+            tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m);
             const uint8_t *rmask = reinterpret_cast<const uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
             const int n = nrows[buf];
             const bool run_tile = runinfo[buf] != 0;
@@ -1003,6 +1004,8 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     if (forced_rows == 64 || forced_rows == TILE_M) tile_rows = forced_rows;
     p.tiles_m = ceil_div(M, tile_rows);
     p.num_tiles = p.tiles_m * p.tiles_n;
+    p.group_m = tuning_get("GROUP_M", GROUP_M);
+    if (p.group_m < 1) p.group_m = 1;
     p.brow_bits = tuning_get("BROW_BITS", 6);
     if (p.brow_bits < 0) p.brow_bits = 0;
     if (p.brow_bits > 8) p.brow_bits = 8;

@@ -14,14 +14,15 @@ constexpr int GROUP_M = 8;         // tile rows per raster group
 constexpr int SMEM_LIMIT = 232448; // 227 KB per CTA on sm_100
 
 #ifdef __CUDACC__
-// Tiles are walked in groups of GROUP_M tile rows, column by column inside a group, so that
-// the CTAs running at the same time share a compact set of A row panels and B column panels in L2.
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int &tm, int &tn)
+// Tiles are walked in groups of `group_m` tile rows (GROUP_M unless the launch says otherwise), column by column
+// inside a group, so that the CTAs running at the same time share a compact set of A row panels and B column panels
+// in L2.  A pass over a group touches the group's A panels and all of B, and B comes from DRAM again for every group.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int &tm, int &tn, int group_m = GROUP_M)
 {
-    const int per_group = GROUP_M * tiles_n;
+    const int per_group = group_m * tiles_n;
     const int group = tile / per_group;
-    const int first_m = group * GROUP_M;
-    const int gsize = min(tiles_m - first_m, GROUP_M);
+    const int first_m = group * group_m;
+    const int gsize = min(tiles_m - first_m, group_m);
     const int r = tile - group * per_group;
     tm = first_m + r % gsize;
     tn = r / gsize;
