@@ -52,6 +52,11 @@ class ClockSampler(threading.Thread):
     def __init__(self, index: int, uuid: str | None = None):
         super().__init__(daemon=True)
         self.index, self.uuid, self.stop_flag, self.rows, self.source = index, uuid, threading.Event(), [], "nvml"
+        try:                                  # initialised here, outside the timed region (it takes tens of ms)
+            self.nv, self.handle = self._nvml_handle()
+            self.max_mhz = self.nv.nvmlDeviceGetMaxClockInfo(self.handle, self.nv.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = self.handle = None
 
     def _nvml_handle(self):
         import pynvml
@@ -65,8 +70,9 @@ class ClockSampler(threading.Thread):
 
     def run(self):
         try:
-            nv, h = self._nvml_handle()
-            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            if self.nv is None:
+                raise RuntimeError("no NVML")
+            nv, h, mx = self.nv, self.handle, self.max_mhz
             while not self.stop_flag.is_set():
                 sm = nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)
                 mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
