@@ -16,6 +16,7 @@ import numpy as np
 _HERE = os.path.dirname(os.path.abspath(__file__))
 _LIB_PATH = os.path.join(_HERE, "liboracle.so")
 _REF_PATH = os.path.join(_HERE, "_ref", "libesmm_ref.so")
+SWAPPED_EXE = os.path.join(_HERE, "_ref", "exec_swapped")   # the reference driver.cu built against this repository
 
 _f32p = np.ctypeslib.ndpointer(dtype=np.float32, flags="C_CONTIGUOUS")
 _f64p = np.ctypeslib.ndpointer(dtype=np.float64, flags="C_CONTIGUOUS")
@@ -42,6 +43,13 @@ def build(force: bool = False) -> None:
     if have_ref_tree():
         if force or not os.path.exists(_REF_PATH) or os.path.getmtime(_REF_PATH) < os.path.getmtime(shim):
             subprocess.check_call(["make", "-C", _HERE, "ref", f"REF_ROOT={ref_root()}"])
+        # the reference's own driver against this repository's headers and library (run by a GPU test)
+        lib = os.path.join(os.path.dirname(_HERE), "esmm-research_b200", "libesmm_b200.so")
+        inc = [os.path.join(os.path.dirname(_HERE), "include", h) for h in ("utils.cuh", "runners.cuh", "esmm.h")]
+        if os.path.exists(lib):
+            newest = max(os.path.getmtime(f) for f in inc + [lib])
+            if force or not os.path.exists(SWAPPED_EXE) or os.path.getmtime(SWAPPED_EXE) < newest:
+                subprocess.check_call(["make", "-C", _HERE, "swapped", f"REF_ROOT={ref_root()}"])
 
 
 _lib = None

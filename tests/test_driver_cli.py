@@ -135,3 +135,27 @@ def test_gpus_flag_on_one_gpu(pkg, cuda):
     assert "1 GPUs, column shards of 512" in out and "Kernel 29" in out and "PASSED" in out
     line = json.loads([l for l in out.splitlines() if l.startswith("{")][0])
     assert line["gpus"] == 1 and line["passed"] is True and len(line["ms_per_gpu"]) == 1 and 0 <= line["cpu_rel_inf"] <= 1e-4
+
+
+@pytest.mark.gpu
+def test_reference_driver_runs_against_this_library(pkg, cuda, oracle_mod):
+    """The reference's OWN driver.cu, byte for byte, built against this repository's include/ and libesmm_b200
+    (oracle/_ref/exec_swapped, made by oracle/Makefile where the reference tree is at hand): its main(), its generators
+    by name, its cuBLAS reference, its switch over the kernel ids and its PASSED / FAILED lines - with this library
+    underneath.  The header swap at run time, not only at compile time."""
+    exe = oracle_mod.SWAPPED_EXE
+    if not os.path.exists(exe):
+        pytest.skip("oracle/_ref/exec_swapped not built (needs the reference tree at build time)")
+
+    def run_ref(*args):
+        p = subprocess.run([exe, *args], capture_output=True, text=True, timeout=600)
+        return p.returncode, p.stdout + p.stderr
+    rc, out = run_ref("29,15", "2", "--blockwise", "--pattern", "11110000", "--size", "512", "--skip-stats")
+    assert rc == 0, out
+    assert "Kernel 29 (ESMM A+B Optimized V3 (K26 + templated smem + float2 A-loads)): PASSED" in out
+    assert "Kernel 15 (cuBLAS): PASSED" in out and "Summary: 2/2 kernels passed" in out
+    assert "=== Skip Stats: K29 ===" in out and out.count("Kernel time:") == 2
+    rc, out = run_ref("all", "1", "--size", "256", "--pattern", "11110000")
+    assert rc == 0 and "Summary: 12/12 kernels passed" in out, out          # every id of the reference's switch
+    rc, out = run_ref("20-30", "1", "--size", "256", "--random", "--no-check", "--verbose")
+    assert rc == 0 and "Sparsity mode: RANDOM (unstructured)" in out and "Summary: 8/8 kernels completed (no verification)" in out
