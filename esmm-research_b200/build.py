@@ -1,5 +1,5 @@
-"""Builds libesmm_b200.so (the C-ABI library), libesmm_b200_checked.so (the same sources with every computed
-shared- and global-memory index bounds-checked), exec_b200 (the driver CLI) and cusparse_bench in-tree with
+"""Builds libesmm_b200.so (the C-ABI library), libesmm_b200_checked.so (the same sources with their shape- and data-dependent
+shared- and global-memory indices bounds-checked), exec_b200 (the driver CLI) and cusparse_bench in-tree with
 nvcc for sm_100a.  Usage: `python build.py [--force] [--verbose]`."""
 from __future__ import annotations
 

@@ -33,9 +33,9 @@ int *device_status_ptr();  // device address, valid after the first call on the 
 
 #ifdef __CUDACC__
 // ---------------------------------------------------------------------------
-// Checked build (-DESMM_CHECKED; libesmm_b200_checked.so): the index of every access to shared or
-// global memory that the kernels compute themselves (everything but the copy engine's boxes, which
-// the tensor maps bound in hardware) is tested first.  A failed test records ESMM_ERR_BOUNDS and
+// Checked build (-DESMM_CHECKED; libesmm_b200_checked.so): indices into shared or global memory that
+// depend on the problem's shape or data (not the copy engine's boxes, which the tensor maps bound in
+// hardware, nor offsets that are constants of the thread) are tested before the access.  A failed test records ESMM_ERR_BOUNDS and
 // the number of the site in the device status word - the first failure wins - and the access is
 // skipped: no trap, no fault, the context stays usable and esmm_device_status() reports it.  In the
 // product build bounds_ok() is the constant true and the tests compile away.

@@ -192,8 +192,9 @@ int esmm_device_status(void *stream);
 
 /*
  * The checked build (libesmm_b200_checked.so, same ABI, compiled with -DESMM_CHECKED) stands in for a
- * memory sanitizer: its kernels test every shared- and global-memory index they compute and, instead of
- * trapping, record ESMM_ERR_BOUNDS plus the site in the device status word and skip the access;
+ * memory sanitizer: its kernels test the shared- and global-memory indices that depend on the problem's shape
+ * or data (list and mask positions, ring slots, pattern loads, loads of A and B in the preprocessors, every store
+ * to a caller's buffer) and, instead of trapping, record ESMM_ERR_BOUNDS plus the site in the device status word and skip the access;
  * esmm_device_status() then returns ESMM_ERR_BOUNDS and esmm_last_cuda_error() names the site.  The
  * reference has only `#ifdef DEBUG` synchronisations (src/preprocessors/a_preprocessor_hybrid.cu:115-120).
  *   esmm_checked_build            1 in the checked build, 0 in the product build.
