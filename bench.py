@@ -254,6 +254,18 @@ def other_config_rows(pkg, torch, dev, time_each):
     for M4 in (2048, 16):
         hA, hB = workloads.llm_mlp(M4, 11008, 4096, seed=40 + M4)
         measure(f"c4 M={M4} K=4096 N=11008 (LLM MLP)", torch.from_numpy(hA).to(dev), torch.from_numpy(hB).to(dev))
+    # The reference's own headline inputs (README: `exec 29,15 10 --blockwise --pattern P --size 4096`): an independent
+    # random 8-bit pattern per 32 x 8 tile of A and 8 x 32 tile of B, bit density popcount(P) / 8, values {0..4} +
+    # 0.01 {0..4} with a random sign, seeds 12345 / 12346 - drawn by the library's restatement of the driver's rand()
+    # generators (bit for bit the reference's matrices).
+    hA = np.zeros((S, S), np.float32)
+    hB = np.zeros((S, S), np.float32)
+    for pattern in ("11110000", "11000000", "10000000"):
+        sparsity = 100.0 - pattern.count("1") / 8.0 * 100.0
+        pkg.check(L.esmm_randomize_matrix_a_blocklevel(hA.ctypes.data, S, S, 8, 32, sparsity, 12345), "generator A")
+        pkg.check(L.esmm_randomize_matrix_b_blocklevel(hB.ctypes.data, S, S, 8, 32, sparsity, 12346), "generator B")
+        measure(f"reference README inputs: --blockwise --pattern {pattern} --size {S}", torch.from_numpy(hA).to(dev),
+                torch.from_numpy(hB).to(dev))
     pkg.device_status()
     return rows
 
