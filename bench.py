@@ -369,7 +369,7 @@ def run_ours(args) -> None:
     pkg.device_status()
     shard_check = None
     if dist is not None and not args.no_check:
-        # every rank checks its own shard (untimed); the line reports the all-ranks verdict
+        # every rank checks its own shard (untimed); the line reports the result over all ranks
         mine = check_shard_against_oracle(pkg, torch, cases[0]["A"], cases[0]["B"], Cd)
         flags = torch.tensor([1 if mine["passed"] else 0, 1 if mine["bit_identical"] else 0], dtype=torch.int32, device=dev)
         dist.all_reduce(flags, op=dist.ReduceOp.MIN)
