@@ -147,6 +147,23 @@ __device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, 
     }
 }
 
+// The same wait for a warp with nothing to do until the barrier completes and no hurry afterwards: it sleeps
+// between polls, so that it takes next to no issue slots from the warps that work.
+__device__ __forceinline__ bool mbar_wait_idle(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+{
+    const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+    while (true) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (global_timer_ns() - t0 > WAIT_BUDGET_NS) {
+            *abort_flag = 1;
+            return false;
+        }
+        __nanosleep(2000);
+    }
+}
+
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
 {
     return mbar_wait_budget(bar, parity, abort_flag, WAIT_BUDGET_NS);

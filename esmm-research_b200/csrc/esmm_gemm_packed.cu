@@ -46,6 +46,7 @@
 // Every wait is bounded; a wait that expires raises the device status word and the CTA
 // leaves after waiting (bounded again) for its copies in flight.
 #include <cstring>
+#include <mutex>
 
 #include "esmm_gemm_shared.cuh"
 
@@ -102,54 +103,23 @@ struct PackedParams {
     int force_listed;  // tuning aid: take the index-list path even for all-live stages
     int no_run_tiles;  // tuning aid: build the row list even for tiles that need none
     int vec_patterns;  // K blocks per lane and load in the mask warp: 16, 4 (alignment permitting) or 0 = bytes
+    int adaptive;      // 16-warp form: the CTA's first tile decides whether 3 or all 7 producer warps copy
+    int *form_hint;    // host-mapped word, or null: CTA 0 notes whether its first tile wanted 7 producers
     const uint8_t *a_pat;
     const uint8_t *b_pat;
-    const float *a_packed;   // the operands themselves, for the producers' plain row copies
-    const float *B;
     float *C;
     int *status;
 };
 
-// Tensor maps of one launch.  *_row / *_kb: 2-D, 1 and 8 rows of 128 columns.  *_run[i]: 3-D
+// Tensor maps of one launch.  *_box[i]: 2-D, 1 << i rows (1, 2, 4, 8) of 128 columns.  *_run[i]: 3-D
 // (column, k % 8, k / 8) boxes of 128 x c x 32/c with c = 1 << i.
 struct PackedMaps {
-    CUtensorMap a_row, a_kb, a_run[4];
-    CUtensorMap b_row, b_kb, b_run[4];
+    CUtensorMap a_box[4], a_run[4];
+    CUtensorMap b_box[4], b_run[4];
 };
 
-// 16-byte asynchronous copy global -> shared by the executing thread; src_bytes = 0 writes zeros instead
-__device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, int src_bytes)
-{
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
-}
-
-// Ties the completion of all cp.async copies the executing thread has issued so far to the barrier's current
-// phase: the pending count goes up by one now and down by one when the copies have landed.
-__device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar)
-{
-    asm volatile("cp.async.mbarrier.arrive.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-// How the producers fetch single rows (rows that are neither part of a whole-stage run nor of an 8-row box):
-//   0  one 2-D tensor copy per row and operand, one lane per row
-//   1  the whole warp copies each row with 16-byte cp.async, completion tied to the stage's barrier
-//   2  one untiled bulk copy (cp.async.bulk) per row and operand, one lane per row; rows that would leave the
-//      matrix (ragged last tile of columns, padding rows of K) take the tensor copy, which fills with zeros
-#ifndef ESMM_ROW_COPY
-#define ESMM_ROW_COPY 0
-#endif
-// arrivals a stage's full barrier expects: the byte count posted by producer 0, plus - when rows come by
-// cp.async - one arrival per other producer warp after it has tied its copies to the barrier
-
-
-__device__ __forceinline__ void bulk_copy_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar)
-{
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
-                 "l"(src), "r"(bytes), "r"(bar)
-                 : "memory");
-}
-
 constexpr int RUN_TILE = 0x100;
+constexpr int RUNS_LIKELY = 0x200;   // a listed tile whose stages may be whole runs of K blocks: the producers look for them
 
 struct PackedSmem {
     uint32_t stage_off, krow_off, krow_stride, rmask_off, rmask_stride, wlist_off, bar_off, misc_off, total;
@@ -172,7 +142,7 @@ __host__ __device__ inline PackedSmem packed_smem_layout(int stages, int cap)
     o += P_CONSUMER_WARPS * 2 * 96;  // two lists of WLIST_BYTES per warp
     L.bar_off = o;    // full[P_MAX_STAGES], empty[P_MAX_STAGES], list_full[2], list_empty[2]
     o += (2 * P_MAX_STAGES + 4) * 8;
-    L.misc_off = o;   // nrows[2], abort, -, runinfo[2]
+    L.misc_off = o;   // nrows[2], abort, n_producers, runinfo[2]
     o += 32;
     L.total = o;
     return L;
@@ -466,7 +436,7 @@ __device__ __forceinline__ int warp_inclusive_scan(int v, int lane)
 }
 
 // First pass of the mask warp over a tile's pattern bytes: the live byte of its first K block, whether all
-// K blocks share it, and the number of live k.
+// K blocks share it, the number of live k, and how many of those lie in K blocks with at most brow_bits live k.
 // whether the live k of a K block are live for each of the tile's RB row blocks and 4 column blocks
 template <int RB>
 __device__ __forceinline__ bool blocks_cover(unsigned aw, unsigned bw, unsigned live)
@@ -477,7 +447,7 @@ __device__ __forceinline__ bool blocks_cover(unsigned aw, unsigned bw, unsigned 
 
 template <int RB, int KPL>
 __device__ __forceinline__ void tile_scan(const PackedParams &p, int tm, int tn, int lane, unsigned &live_first,
-                                          bool &uniform, bool &full, int &live_total)
+                                          bool &uniform, bool &full, int &live_total, int &live_small)
 {
     for (int c0 = 0; c0 < p.nKB; c0 += 32 * KPL) {
         const int kb0 = c0 + KPL * lane;
@@ -485,17 +455,19 @@ __device__ __forceinline__ void tile_scan(const PackedParams &p, int tm, int tn,
         load_patterns<RB, KPL>(p, tm, tn, kb0, kb0 < p.nKB, aw, bw);
         if (c0 == 0) live_first = __shfl_sync(0xFFFFFFFFu, tile_live(aw[0], bw[0]), 0);
         bool same = true, cover = true;
-        int cnt = 0;
+        int cnt = 0, small = 0;
 #pragma unroll
         for (int j = 0; j < KPL; ++j) {
             const unsigned live = tile_live(aw[j], bw[j]);
             same = same && live == live_first;
             cover = cover && blocks_cover<RB>(aw[j], bw[j], live);
             cnt += __popc(live);
+            small += __popc(live) <= p.brow_bits ? __popc(live) : 0;
         }
         uniform = uniform && __all_sync(0xFFFFFFFFu, kb0 >= p.nKB || same);
         full = full && __all_sync(0xFFFFFFFFu, kb0 >= p.nKB || cover);
         live_total += __reduce_add_sync(0xFFFFFFFFu, cnt);
+        live_small += __reduce_add_sync(0xFFFFFFFFu, small);
     }
 }
 
@@ -527,6 +499,25 @@ __device__ __forceinline__ int tile_list(const PackedParams &p, int tm, int tn, 
     return pos;
 }
 
+#ifndef ESMM_CONS_REGS
+#define ESMM_CONS_REGS 160
+#define ESMM_PROD_REGS 96
+#endif
+
+// Sum over a tile's listed rows of the number of consumer warps (of 8) the row is live for.  (A call rather than
+// inline code: it runs once per CTA, and the kernel's register allocation stays that of the code without it.)
+template <int WMB>
+__device__ __noinline__ int listed_warp_rows(const uint8_t *rmask, int n, int lane)
+{
+    int warp_rows = 0;
+    for (int r = lane; r < n; r += 32) {
+        const unsigned m = rmask[r], a = m & 15u, b = m >> 4;
+        const int na = WMB == 2 ? ((a & 3u) != 0u) + ((a & 12u) != 0u) : __popc(a & 3u);
+        warp_rows += na * __popc(b);
+    }
+    return __reduce_add_sync(0xFFFFFFFFu, warp_rows);
+}
+
 template <int WMB, int NPW>
 __global__ void __launch_bounds__((P_CONSUMER_WARPS + NPW + 1) * 32, 1)
 esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const PackedParams p)
@@ -535,7 +526,6 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
     constexpr int P_TMA_WARPS = NPW;
     constexpr int P_MASK_WARP = P_CONSUMER_WARPS + NPW;
     constexpr bool P_REBALANCE_REGS = NPW == 7;
-    constexpr int FULL_ARRIVALS = ESMM_ROW_COPY == 1 ? NPW : 1;
     constexpr int TM_ROWS = 64 * WMB;                  // rows of a tile of C: 128 or 64
     constexpr int RB = 2 * WMB;                        // 32-row blocks per tile
     constexpr int A_ROW = TM_ROWS * 4;                 // bytes of one k of the A tile in shared memory
@@ -552,6 +542,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
     const uint32_t lempty0 = smem_u32(bars + 2 * P_MAX_STAGES + 2);
     volatile int *nrows = reinterpret_cast<volatile int *>(smem + L.misc_off);
     volatile int *abort_flag = nrows + 2;
+    volatile int *n_producers = nrows + 3;   // 16-warp form: producer warps that copy (set with the first tile's list)
     // per list buffer: 0, or RUN_TILE | log2(c) | kk0 << 4 for a tile whose every K block has the same c = 1, 2,
     // 4 or 8 consecutive live k (kk0 .. kk0 + c - 1), live for all of the tile's row and column blocks.  Such
     // a tile needs no row list: stage s is the 3-D box of K blocks 32 s / c .. and every stage is all-live.
@@ -559,7 +550,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; ++s) {
-            mbar_init(full0 + 8 * s, FULL_ARRIVALS);
+            mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, P_CONSUMER_WARPS);
         }
         for (int b = 0; b < 2; ++b) {
@@ -578,7 +569,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
     // (16-warp form: registers move from the producer / mask warp groups to the consumer warp groups; 8 x 32 x 184 +
     // 8 x 32 x 64 = 63488 of the 65536 the CTA starts with.  Each instruction heads its own side's code.)
     if (warp == P_MASK_WARP) {
-        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ESMM_PROD_REGS));
         // ---------------- mask warp: the tile's list of live k rows ----------------
         int it = 0;
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
@@ -592,11 +583,11 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             // A first pass over the tile's pattern bytes decides the listing policy.
             unsigned live_first = 0;
             bool uniform = true, full = true;
-            int live_total = 0;
+            int live_total = 0, live_small = 0;
             if (p.vec_patterns == 16) {
-                tile_scan<RB, 16>(p, tm, tn, lane, live_first, uniform, full, live_total);
+                tile_scan<RB, 16>(p, tm, tn, lane, live_first, uniform, full, live_total, live_small);
             } else if (p.vec_patterns == 4) {
-                tile_scan<RB, 4>(p, tm, tn, lane, live_first, uniform, full, live_total);
+                tile_scan<RB, 4>(p, tm, tn, lane, live_first, uniform, full, live_total, live_small);
             } else {
                 for (int kb0 = 0; kb0 < p.nKB; kb0 += 32) {
                     const int kb = kb0 + lane;
@@ -614,6 +605,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     uniform = uniform && __all_sync(0xFFFFFFFFu, kb >= p.nKB || live == live_first);
                     full = false;   // the byte-wise path keeps the general listing
                     live_total += __reduce_add_sync(0xFFFFFFFFu, __popc(live));
+                    live_small += __reduce_add_sync(0xFFFFFFFFu, __popc(live) <= p.brow_bits ? __popc(live) : 0);
                 }
             }
             // uniform tile: list live k only.  Otherwise single rows cost a copy each, which pays
@@ -665,16 +657,35 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     rmask[q] = 0;
                 }
             }
+            // a tile of mostly single rows: no stage of it is a run of whole K blocks, bar a rare coincidence
+            const bool sparse_rows = !run_code && !uniform && whole_above == p.brow_bits && 2 * live_small >= pos;
+            if (it == 0 && (NPW == 7 || (blockIdx.x == 0 && p.form_hint != nullptr))) {
+                // 16-warp form: how many producer warps copy.  A row-by-row stage costs its producers the same 64
+                // copies whatever the patterns, and its consumers one pass per row that is live for their own
+                // 64 (32) rows x 32 columns.  Where the CTA's first tile is mostly such rows and a consumer warp
+                // works on 12 of a stage's 32 rows or fewer, three producers cannot keep up and all seven copy;
+                // otherwise three do and four stay idle.
+                bool wants7 = false;
+                if (sparse_rows) {
+                    __syncwarp();
+                    wants7 = listed_warp_rows<WMB>(rmask, min(pos, p.cap), lane) <= 3 * pos;
+                }
+                if (lane == 0) {
+                    *n_producers = !p.adaptive || wants7 ? 7 : 3;
+                    // (either form computes the same C; the note only steers the shape of the next launch)
+                    if (blockIdx.x == 0 && p.form_hint != nullptr) *p.form_hint = wants7 ? 1 : 0;
+                }
+            }
             if (lane == 0) {
                 nrows[buf] = pos;
-                runinfo[buf] = run_code;
+                runinfo[buf] = run_code | (sparse_rows ? 0 : RUNS_LIKELY);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(lfull0 + 8 * buf);
             if (it == 0) ESMM_STAMP(1);
         }
     } else if (warp >= P_TMA_WARP) {
-        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ESMM_PROD_REGS));
         // ---------------- producer warps: one lane per row of the stage ----------------
         // All of them walk the row list and take the same decisions; producer q issues the copies of
         // rows 32 q / P .. of each stage, producer 0 also the stage's byte count and whole-stage boxes.
@@ -682,20 +693,30 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
         // count then goes negative for a moment, which it is allowed to, and the phase cannot complete
         // before producer 0's arrival.)
         const int q = warp - P_TMA_WARP;
-        if (q == 0 && lane < 12) tma_prefetch_descriptor(&maps.a_row + lane);
+        if (q == 0 && lane < 16) tma_prefetch_descriptor(&maps.a_box[0] + lane);
         int slot = 0;
         uint32_t phase = 0;
         uint32_t issued_bits = 0, parity_bits = 0;  // per slot: ever issued / parity of last issue
         int it = 0;
+        int copying = P_TMA_WARPS;   // producer warps that share the copies out
         for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
             const int buf = it & 1;
-            ok = mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
+            ok = NPW == 7 && q >= copying ? mbar_wait_idle(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag)
+                                          : mbar_wait(lfull0 + 8 * buf, (it >> 1) & 1, abort_flag);
             if (!ok) break;
+            if (NPW == 7 && it == 0) copying = *n_producers;
+            if (NPW == 7 && q >= copying) {
+                // an idle producer: it only hands the list buffer back, once per tile
+                __syncwarp();
+                if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
+                continue;
+            }
             int tm, tn;
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m);
             const uint16_t *krow = reinterpret_cast<const uint16_t *>(smem + L.krow_off + buf * L.krow_stride);
             const int n = nrows[buf];
-            const int run_code = runinfo[buf];
+            const int run_code = runinfo[buf] & (RUN_TILE | 0xFF);
+            const bool look_for_runs = (runinfo[buf] & RUNS_LIKELY) != 0 && p.b_runs_ok;
             // packed A is stored in panels of 128 rows: a 64-row tile is the left or right half of one
             const int panel = WMB == 2 ? tm : tm >> 1;
             const int a_x = WMB == 2 ? 0 : (tm & 1) * TM_ROWS;
@@ -711,14 +732,11 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     if (!ok) break;
                     const uint32_t full = full0 + 8 * slot;
                     if (q == 0 && lane == 0) {
-                        if (ESMM_ROW_COPY == 1) fence_proxy_async();   // the slot may last have been written by plain copies
                         mbar_arrive_expect_tx(full, (uint32_t)ROWS_PER_STAGE * STAGE_ROW_BYTES);
                         const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
                         const int kb0 = r0 >> lc;
                         tma_load_3d(s0, &maps.a_run[lc], a_x, kk0, panel * p.nKB + kb0, full);
                         tma_load_3d(s0 + STAGE_HALF_BYTES, &maps.b_run[lc], b_col0, kk0, kb0, full);
-                    } else if (FULL_ARRIVALS > 1 && lane == 0) {
-                        mbar_arrive(full);
                     }
                     if (q == 0) {
                         issued_bits |= 1u << slot;
@@ -731,15 +749,22 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                     }
                 }
             }
+            // (the k of a stage's rows are read one stage ahead, under the copies of the stage before)
+            int k_next = !run_code && lane < n && bounds_ok(lane < p.cap, p.status, 27) ? (int)krow[lane] : -1;
             for (int r0 = 0; r0 < n && !run_code; r0 += ROWS_PER_STAGE) {
                 const int cnt = min(ROWS_PER_STAGE, n - r0);
                 const bool valid = lane < cnt;
-                const int k = valid && bounds_ok(r0 + lane < p.cap, p.status, 27) ? (int)krow[r0 + lane] : -1;
+                if (it == 0 && q == 0 && r0 < 80 * ROWS_PER_STAGE) ESMM_STAMP(700 + 4 * (r0 / ROWS_PER_STAGE));
+                const int k = k_next;
+                {
+                    const int rn = r0 + ROWS_PER_STAGE + lane;
+                    k_next = rn < n && bounds_ok(rn < p.cap, p.status, 27) ? (int)krow[rn] : -1;
+                }
                 // a uniform run?  rows = k offsets kk0 .. kk0 + c - 1 of 32 / c consecutive K blocks
                 const int k_first = __shfl_sync(0xFFFFFFFFu, k, 0);
                 const int kb0 = k_first >> 3, kk0 = k_first & 7;
                 int run = -1;  // log2(c)
-                if (cnt == ROWS_PER_STAGE && p.b_runs_ok) {
+                if (cnt == ROWS_PER_STAGE && look_for_runs) {
 #pragma unroll
                     for (int lc = 3; lc >= 0; --lc) {
                         const int c = 1 << lc;
@@ -747,77 +772,50 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
                         if (run < 0 && kk0 + c <= BK && __all_sync(0xFFFFFFFFu, k == expect)) run = lc;
                     }
                 }
-                // otherwise: rows lane .. lane + 7 are the 8 k of one K block?  (the list is ascending)
-                const int k7 = __shfl_down_sync(0xFFFFFFFFu, k, 7);
-                const bool lead8 = valid && (k & 7) == 0 && lane + 7 < cnt && k7 == k + 7;
-                const unsigned lead_mask = __ballot_sync(0xFFFFFFFFu, lead8);
-                unsigned cover = lead_mask | (lead_mask << 1);
-                cover |= cover << 2;
-                cover |= cover << 4;                                  // rows fetched by some 8-row box
-                // my share of the stage: the rows (or leading rows of 8-row boxes) in my lane group
-                const bool mine = ((lane * P_TMA_WARPS) >> 5) == q;
-                const bool box8 = run < 0 && lead8 && mine;
-                const bool row1 = run < 0 && !lead8 && valid && !((cover >> lane) & 1u) && mine;
+                // otherwise: the list is ascending, and rows with consecutive k are consecutive rows of packed A and of
+                // B alike, so a run of L such rows is fetched in boxes of 8, 4, 2 and 1 rows (L = 8 a + 4 b + 2 c +
+                // d, largest first): fewer copies for the same bytes.  The lane at a box's first row issues it.
+                const int k_prev = __shfl_up_sync(0xFFFFFFFFu, k, 1);
+                const unsigned starts = __ballot_sync(0xFFFFFFFFu, valid && (lane == 0 || k != k_prev + 1));
+                int box_log = -1;   // log2 of the height of the box this lane issues
+                if (valid && run < 0) {
+                    const int first = 31 - __clz((int)(starts & (0xFFFFFFFFu >> (31 - lane))));   // my run's first lane
+                    const unsigned later = lane == 31 ? 0u : (starts >> (first + 1)) << (first + 1);
+                    const int len = (later ? __ffs((int)later) - 1 : cnt) - first;
+                    const int o = lane - first;
+                    const int full8 = len & ~7;
+                    if (o < full8) box_log = (o & 7) == 0 ? 3 : -1;
+                    else if ((len & 4) && o == full8) box_log = 2;
+                    else if ((len & 2) && o == full8 + (len & 4)) box_log = 1;
+                    else if ((len & 1) && o == len - 1) box_log = 0;
+                }
+                // my share of the stage: the boxes that start in my lane group
+                if (((lane * copying) >> 5) != q) box_log = -1;
+                if (it == 0 && q == 0 && r0 < 80 * ROWS_PER_STAGE) ESMM_STAMP(701 + 4 * (r0 / ROWS_PER_STAGE));
                 ok = mbar_wait(empty0 + 8 * slot, phase ^ 1, abort_flag);
                 ok = __all_sync(0xFFFFFFFFu, ok);
                 if (!ok) break;
+                if (it == 0 && q == 0 && r0 < 80 * ROWS_PER_STAGE) ESMM_STAMP(702 + 4 * (r0 / ROWS_PER_STAGE));
                 {
                     const uint32_t full = full0 + 8 * slot;
                     const uint32_t s0 = smem_u32(smem + L.stage_off) + (uint32_t)slot * PSTAGE_BYTES;
                     const uint32_t sa = s0 + lane * A_ROW;
                     const uint32_t sb = s0 + STAGE_HALF_BYTES + lane * ROW_BYTES;
-                    // (with cp.async rows the slot may last have been written through the generic proxy)
-                    if (ESMM_ROW_COPY == 1 && (run >= 0 || box8)) fence_proxy_async();
                     if (run >= 0) {
                         if (q == 0 && lane == 0) {
                             tma_load_3d(sa, &maps.a_run[run], a_x, kk0, panel * p.nKB + kb0, full);
                             tma_load_3d(sb, &maps.b_run[run], b_col0, kk0, kb0, full);
                         }
-                    } else if (box8) {
-                        tma_load_2d(sa, &maps.a_kb, a_x, a_row0 + k, full);
-                        tma_load_2d(sb, &maps.b_kb, b_col0, k, full);
-                    }
-#if ESMM_ROW_COPY == 1
-                    // Single rows: the whole warp copies each of its rows, 16 bytes per lane; their completion is
-                    // tied to the stage's barrier below.
-                    unsigned rows_left = __ballot_sync(0xFFFFFFFFu, row1);
-                    const bool any_rows = rows_left != 0u;
-                    const bool col_ok = b_col0 + lane * 4 < p.N;
-                    while (rows_left) {
-                        const int r = __ffs((int)rows_left) - 1;
-                        rows_left &= rows_left - 1u;
-                        const int kr = __shfl_sync(0xFFFFFFFFu, k, r);
-                        if (lane * 16 < A_ROW)
-                            cp_async_16(s0 + r * A_ROW + lane * 16,
-                                        p.a_packed + ((size_t)(a_row0 + kr) * TILE_M + a_x + lane * 4), 16);
-                        const bool b_ok = col_ok && kr < p.K;   // outside B: zero fill, as the tensor copy does
-                        cp_async_16(s0 + STAGE_HALF_BYTES + r * ROW_BYTES + lane * 16,
-                                    b_ok ? p.B + ((size_t)kr * p.N + b_col0 + lane * 4) : p.B, b_ok ? 16 : 0);
-                    }
-                    if (any_rows) cp_async_mbar_arrive(full);   // every lane: its copies count towards this phase
-                    __syncwarp();
-                    if (lane == 0) {
-                        // bytes that arrive by tensor copy: whole-stage runs and 8-row boxes (of all producers)
-                        const uint32_t tma_rows = run >= 0 ? (uint32_t)ROWS_PER_STAGE : (uint32_t)__popc(cover);
-                        if (q == 0) mbar_arrive_expect_tx(full, tma_rows * STAGE_ROW_BYTES);
-                        else mbar_arrive(full);
-                    }
-#else
-                    if (row1) {
-                        if (ESMM_ROW_COPY == 2 && b_col0 + TILE_N <= p.N && k < p.K) {
-                            bulk_copy_1d(sa, p.a_packed + ((size_t)(a_row0 + k) * TILE_M + a_x), A_ROW, full);
-                            bulk_copy_1d(sb, p.B + ((size_t)k * p.N + b_col0), ROW_BYTES, full);
-                        } else {
-                            tma_load_2d(sa, &maps.a_row, a_x, a_row0 + k, full);
-                            tma_load_2d(sb, &maps.b_row, b_col0, k, full);
-                        }
+                    } else if (box_log >= 0) {
+                        tma_load_2d(sa, &maps.a_box[box_log], a_x, a_row0 + k, full);
+                        tma_load_2d(sb, &maps.b_box[box_log], b_col0, k, full);
                     }
                     if (q == 0 && lane == 0) mbar_arrive_expect_tx(full, (uint32_t)cnt * STAGE_ROW_BYTES);
-#endif
                     issued_bits |= 1u << slot;
                     parity_bits = (parity_bits & ~(1u << slot)) | (phase << slot);
                 }
                 if (it == 0 && q == 0) ESMM_STAMP(400 + r0 / ROWS_PER_STAGE);
+                if (it == 0 && q == 0 && r0 < 80 * ROWS_PER_STAGE) ESMM_STAMP(703 + 4 * (r0 / ROWS_PER_STAGE));
                 if (++slot == p.stages) {
                     slot = 0;
                     phase ^= 1;
@@ -827,7 +825,6 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             __syncwarp();
             if (lane == 0) mbar_arrive(lempty0 + 8 * buf);
         }
-        if (ESMM_ROW_COPY == 1) asm volatile("cp.async.wait_all;" ::: "memory");   // this thread's plain copies have landed
         if (!ok && lane == 0) {
             // leave only after the copies already issued have landed (bounded)
             for (int s = 0; s < p.stages; ++s) {
@@ -838,7 +835,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             }
         }
     } else {
-        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
+        if (P_REBALANCE_REGS) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(ESMM_CONS_REGS));
         // ---------------- consumer warps: 32 WMB rows x 32 columns of the tile each ----------------
         const int wm = warp >> 2, wn = warp & 3;              // 2 x 4 warps
         const int lm = (lane >> 1) & 7;                       // group of 4 rows within a 32-row block
@@ -859,7 +856,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
             tile_coords(tile, p.tiles_m, p.tiles_n, tm, tn, p.group_m);
             const uint8_t *rmask = reinterpret_cast<const uint8_t *>(smem + L.rmask_off + buf * L.rmask_stride);
             const int n = nrows[buf];
-            const bool run_tile = runinfo[buf] != 0;
+            const bool run_tile = (runinfo[buf] & RUN_TILE) != 0;
             if (warp == 0) ESMM_STAMP(600 + 4 * it);
 
             Acc acc;
@@ -969,8 +966,45 @@ bool gemm_ab_skinny_applies(int M, int N, int K);
 int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                           const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream);
 
+// The launch shape follows the operands: the 16-warp form pays on tiles of scattered single rows and costs about
+// half a percent elsewhere, and which kind the operands are is known on the device only.  So CTA 0 of every
+// launch notes what its first tile would have wanted in a word of host-mapped memory (one per device, set up at
+// the first launch), and the next launch on that device reads the word, without waiting for anything: repeated
+// products of like operands - what a benchmark loop or a layer with fixed weights issues - get the right
+// shape from the second call on, and a stale or missing note only costs that difference.  The results are
+// bit-identical in both shapes.  esmm_tuning_set("PRODUCER_WARPS", 3 | 7 | 0) pins the shape instead.
+static int *form_hint_word()
+{
+    static std::mutex mu;
+    static int *words[64] = {nullptr};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!words[dev]) {
+        void *h = nullptr;
+        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+            (void)cudaGetLastError();   // no note then: the 12-warp form is launched
+            return nullptr;
+        }
+        memset(h, 0, 64);
+        words[dev] = static_cast<int *>(h);
+    }
+    return words[dev];
+}
+
+int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                               const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream, bool follow_hint);
+
 int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                           const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream)
+{
+    return gemm_ab_packed_launch_form(M, N, K, d_a_packed, d_B, d_C, d_a_pat, d_b_pat, stream, true);
+}
+
+// follow_hint = false: the 12-warp form unless PRODUCER_WARPS says otherwise, and no host-mapped word (for the
+// entry point that may not allocate).
+int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                               const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream, bool follow_hint)
 {
     if (!d_a_packed || !d_B || !d_C || !d_a_pat || !d_b_pat) return ESMM_ERR_NULL;
     if (M <= 0 || N <= 0 || K <= 0 || (K & 3) || (N & 3)) return ESMM_ERR_SHAPE;
@@ -1022,8 +1056,6 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
         p.vec_patterns = forced_vec;
     p.a_pat = d_a_pat;
     p.b_pat = d_b_pat;
-    p.a_packed = d_a_packed;
-    p.B = d_B;
     p.C = d_C;
 
     int stages = tuning_get("STAGES", P_MAX_STAGES);
@@ -1045,14 +1077,13 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     p.b_runs_ok = (K % BK) == 0;
     PackedMaps maps;
     const uint64_t a_rows_total = (uint64_t)panels * p.kp;
-    int st = make_map_2d(&maps.a_row, d_a_packed, TILE_M, a_rows_total, tile_rows, 1, CU_TENSOR_MAP_SWIZZLE_NONE,
+    int st = 0;
+    for (int i = 0; i < 4 && !st; ++i) {
+        st = make_map_2d(&maps.a_box[i], d_a_packed, TILE_M, a_rows_total, tile_rows, 1u << i, CU_TENSOR_MAP_SWIZZLE_NONE,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-    if (!st) st = make_map_2d(&maps.a_kb, d_a_packed, TILE_M, a_rows_total, tile_rows, BK, CU_TENSOR_MAP_SWIZZLE_NONE,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-    if (!st) st = make_map_2d(&maps.b_row, d_B, (uint64_t)N, (uint64_t)K, TILE_N, 1, CU_TENSOR_MAP_SWIZZLE_NONE,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
-    if (!st) st = make_map_2d(&maps.b_kb, d_B, (uint64_t)N, (uint64_t)K, TILE_N, BK, CU_TENSOR_MAP_SWIZZLE_NONE,
-                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+        if (!st) st = make_map_2d(&maps.b_box[i], d_B, (uint64_t)N, (uint64_t)K, TILE_N, 1u << i, CU_TENSOR_MAP_SWIZZLE_NONE,
+                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+    }
     for (int i = 0; i < 4 && !st; ++i) {
         const uint32_t c = 1u << i;
         st = make_map_3d(&maps.a_run[i], d_a_packed, TILE_M, BK, (uint64_t)panels * p.nKB, (uint64_t)TILE_M * 4,
@@ -1062,7 +1093,7 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
                 st = make_map_3d(&maps.b_run[i], d_B, (uint64_t)N, BK, (uint64_t)p.nKB, (uint64_t)N * 4,
                                  (uint64_t)N * 4 * BK, TILE_N, c, ROWS_PER_STAGE / c);
             else
-                maps.b_run[i] = maps.b_row;  // never used
+                maps.b_run[i] = maps.b_box[0];  // never used
         }
     }
     if (st) return st;
@@ -1070,7 +1101,26 @@ int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const fl
     int grid = tuning_get("GRID", sms);
     if (grid > p.num_tiles) grid = p.num_tiles;
     if (grid < 1) grid = 1;
-    const bool wide = tuning_get("PRODUCER_WARPS", 3) == 7;
+    // 3 = 12 warps; 7 = 16 warps, 7 producers copying; 0 = 16 warps, 3 or 7 copying as each CTA's first tile says;
+    // not set = 3 or 0 as the last launch on this device noted
+    int producer_warps = tuning_get("PRODUCER_WARPS", -1);
+    if (producer_warps != 3 && producer_warps != 7 && producer_warps != 0) {
+        producer_warps = 3;
+        if (follow_hint) {
+            int *word = form_hint_word();
+            if (word) {
+                void *dev_word = nullptr;
+                if (cudaHostGetDevicePointer(&dev_word, word, 0) == cudaSuccess) {
+                    p.form_hint = static_cast<int *>(dev_word);
+                    if (*static_cast<volatile int *>(word) != 0) producer_warps = 0;
+                } else {
+                    (void)cudaGetLastError();
+                }
+            }
+        }
+    }
+    const bool wide = producer_warps != 3;
+    p.adaptive = producer_warps == 0;
     auto launch = [&](auto kernel, int threads) -> int {
         ESMM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total));
         kernel<<<grid, threads, L.total, stream>>>(maps, p);

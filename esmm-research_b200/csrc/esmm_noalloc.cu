@@ -22,8 +22,8 @@
 
 namespace esmm {
 
-int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
-                          const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream);
+int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
+                               const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream, bool follow_hint);
 int preprocess_a_pack_launch(const float *d_A, int M, int K, uint8_t *d_out, float *d_packed,
                              cudaStream_t stream);
 
@@ -83,5 +83,5 @@ extern "C" int esmm_sgemm_joint_static(int M, int N, int K, const float *d_A, co
     float *a_packed = reinterpret_cast<float *>(scratch + esmm::STATIC_PATTERN_BYTES);
     st = esmm::preprocess_a_pack_launch(d_A, M, K, a_pat, a_packed, (cudaStream_t)stream);
     if (st != ESMM_OK) return st;
-    return esmm::gemm_ab_packed_launch(M, N, K, a_packed, d_B, d_C, a_pat, d_b_pat, (cudaStream_t)stream);
+    return esmm::gemm_ab_packed_launch_form(M, N, K, a_packed, d_B, d_C, a_pat, d_b_pat, (cudaStream_t)stream, false);
 }

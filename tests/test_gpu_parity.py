@@ -255,12 +255,14 @@ def test_gemm_both_tile_heights(cuda, pkg, oracle_mod, tuning, rows):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
+@pytest.mark.parametrize("producers", [7, 0, 3])
 @pytest.mark.parametrize("rows", [128, 64])
-def test_gemm_seven_producer_warps(cuda, pkg, oracle_mod, tuning, rows):
-    """The 16-warp form of the tiled kernel (7 producer warps, registers moved between warp groups with setmaxnreg;
-    esmm_tuning_set("PRODUCER_WARPS", 7)): run tiles, row-by-row stages, 8-row boxes, ragged edges, both tile
-    heights - the same bits as the oracle as with the default 12 warps."""
-    tuning("PRODUCER_WARPS", 7)
+def test_gemm_producer_warp_forms(cuda, pkg, oracle_mod, tuning, rows, producers):
+    """The launch shapes of the tiled kernel, each pinned with esmm_tuning_set("PRODUCER_WARPS", v): 7 = the 16-warp
+    form (registers moved between warp groups with setmaxnreg) with all 7 producer warps copying, 0 = the same form
+    where each CTA's first tile decides between 3 and 7, 3 = the 12-warp form.  Run tiles, row-by-row stages, boxes
+    of 1 / 2 / 4 / 8 consecutive rows, ragged edges, both tile heights - the same bits as the oracle in every shape."""
+    tuning("PRODUCER_WARPS", int(producers))
     tuning("TILE_M", int(rows))
     for pat in (0xFF, 0x0F, 0x01):
         A, B = workloads.uniform_pattern(256, 384, 512, pat, seed=pat)
@@ -273,6 +275,32 @@ def test_gemm_seven_producer_warps(cuda, pkg, oracle_mod, tuning, rows):
     check_all_paths(cuda, pkg, oracle_mod, A, B)
     A, B = workloads.llm_mlp(256, 1408, 1024, seed=4)
     check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
+@pytest.mark.parametrize("producers", [3, 0])
+def test_gemm_boxes_of_consecutive_rows(cuda, pkg, oracle_mod, tuning, producers):
+    """Listed rows with consecutive k are fetched in boxes of 8, 4, 2 and 1 rows.  Uniform patterns whose live k form
+    runs of every length from 1 to 14 (0xE7: k 5, 6, 7 of one K block and 0, 1, 2 of the next are one run of 6), with
+    K such that runs straddle stage boundaries and the last stage is ragged; both launch shapes."""
+    tuning("PRODUCER_WARPS", int(producers))
+    for pat in (0xE7, 0x7E, 0xDB, 0xFE, 0x7F, 0xBF, 0x55, 0x33, 0xF1, 0x9F):
+        for M, N, K in ((256, 384, 512), (130, 132, 8 * 37)):
+            A, B = workloads.uniform_pattern(M, N, K, pat, seed=pat)
+            check_all_paths(cuda, pkg, oracle_mod, A, B)
+    A, B = workloads.all_byte_values(M=256, N=256, seed=16)
+    check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
+def test_gemm_launch_shape_follows_last_call(cuda, pkg, oracle_mod):
+    """With PRODUCER_WARPS not pinned, CTA 0 of every launch notes (in a host-mapped word) whether its first tile was
+    one of scattered single rows, and the next launch on the device takes the 16-warp form if so.  Alternating
+    operands of both kinds, twice each, goes through every transition (12 -> 16 warps, 16 -> 16, 16 -> 12, 12 -> 12);
+    every product has the oracle's bits whatever shape it ran in."""
+    sparse = workloads.tile_random(512, 512, 2048, 0.2, 0.2, seed=77, gran_a=32, gran_b=32)
+    dense = workloads.uniform_pattern(256, 384, 512, 0x0F, seed=78)
+    blocks = workloads.block_random(384, 512, 1024, 0.3, 0.4, seed=79)
+    for A, B in (dense, sparse, sparse, dense, dense, blocks, sparse, blocks):
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
 @pytest.mark.parametrize("form", ["strip", "strip32", "tiled"])
