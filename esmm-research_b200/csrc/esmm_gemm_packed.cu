@@ -973,27 +973,66 @@ int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const fl
 // products of like operands - what a benchmark loop or a layer with fixed weights issues - get the right
 // shape from the second call on, and a stale or missing note only costs that difference.  The results are
 // bit-identical in both shapes.  esmm_tuning_set("PRODUCER_WARPS", 3 | 7 | 0) pins the shape instead.
-static int *form_hint_word()
+struct FormHint {
+    volatile int *host = nullptr;   // what the host reads
+    int *device = nullptr;          // the same word as the kernels address it
+};
+
+static FormHint form_hint_word(int dev)
 {
     static std::mutex mu;
-    static int *words[64] = {nullptr};
-    int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    static FormHint words[64];
+    if (dev < 0 || dev >= 64) return FormHint();
     std::lock_guard<std::mutex> lock(mu);
-    if (!words[dev]) {
-        void *h = nullptr;
-        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess) {
+    if (!words[dev].host) {
+        void *h = nullptr, *d = nullptr;
+        if (cudaHostAlloc(&h, 64, cudaHostAllocMapped | cudaHostAllocPortable) != cudaSuccess ||
+            cudaHostGetDevicePointer(&d, h, 0) != cudaSuccess) {
             (void)cudaGetLastError();   // no note then: the 12-warp form is launched
-            return nullptr;
+            if (h) (void)cudaFreeHost(h);
+            return FormHint();
         }
         memset(h, 0, 64);
-        words[dev] = static_cast<int *>(h);
+        words[dev].host = static_cast<volatile int *>(h);
+        words[dev].device = static_cast<int *>(d);
     }
     return words[dev];
 }
 
+// Once per device: the SM count, and the shared-memory allowance of all four forms of the kernel raised to the device's
+// maximum.  (Raising it also loads the forms' code, so that the first launch in the other shape does not pay for that.)
+static int prepare_device(int dev, int *sms)
+{
+    static std::mutex mu;
+    static int sm_count[64] = {0};
+    if (dev < 0 || dev >= 64) return ESMM_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!sm_count[dev]) {
+        int n = 0, smem = 0;
+        ESMM_CUDA_TRY(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+        ESMM_CUDA_TRY(cudaDeviceGetAttribute(&smem, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev));
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<1, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<2, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<1, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_packed_kernel<2, 7>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        sm_count[dev] = n;
+    }
+    *sms = sm_count[dev];
+    return ESMM_OK;
+}
+
 int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                                const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream, bool follow_hint);
+
+// The once-per-device set-up of the tiled kernel on the current device, for callers that want it outside a timed region.
+int gemm_ab_packed_prepare()
+{
+    int dev = 0, sms = 0;
+    ESMM_CUDA_TRY(cudaGetDevice(&dev));
+    const int st = prepare_device(dev, &sms);
+    if (st == ESMM_OK && tuning_get("PRODUCER_WARPS", -1) < 0) (void)form_hint_word(dev);
+    return st;
+}
 
 int gemm_ab_packed_launch(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                           const uint8_t *d_a_pat, const uint8_t *d_b_pat, cudaStream_t stream)
@@ -1025,7 +1064,10 @@ int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, con
     p.b_rows = ceil_div(N, PAT_N);
     int dev = 0, sms = 0;
     ESMM_CUDA_TRY(cudaGetDevice(&dev));
-    ESMM_CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+    {
+        const int pst = prepare_device(dev, &sms);
+        if (pst != ESMM_OK) return pst;
+    }
     // Tile height: 128 rows, or 64 where that fills the GPU better.  Rounds of tiles per SM, a 64-row
     // tile counted as 0.55 of a 128-row one (it does half the multiply-adds at a worse ratio of
     // shared-memory loads).  ESMM_TILE_M = 64 | 128 overrides.
@@ -1107,22 +1149,16 @@ int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, con
     if (producer_warps != 3 && producer_warps != 7 && producer_warps != 0) {
         producer_warps = 3;
         if (follow_hint) {
-            int *word = form_hint_word();
-            if (word) {
-                void *dev_word = nullptr;
-                if (cudaHostGetDevicePointer(&dev_word, word, 0) == cudaSuccess) {
-                    p.form_hint = static_cast<int *>(dev_word);
-                    if (*static_cast<volatile int *>(word) != 0) producer_warps = 0;
-                } else {
-                    (void)cudaGetLastError();
-                }
+            const FormHint hint = form_hint_word(dev);
+            if (hint.host) {
+                p.form_hint = hint.device;
+                if (*hint.host != 0) producer_warps = 0;
             }
         }
     }
     const bool wide = producer_warps != 3;
     p.adaptive = producer_warps == 0;
     auto launch = [&](auto kernel, int threads) -> int {
-        ESMM_CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L.total));
         kernel<<<grid, threads, L.total, stream>>>(maps, p);
         return ESMM_OK;
     };

@@ -167,6 +167,7 @@ void esmm_print_usage(const char *program_name, int additive)
         printf("  --uniform           N(0,1) values, pattern on A's K columns and B's K rows (device generator)\n");
         printf("  --tile-random pA pB N(0,1) values, independent 64-row / 64-column tile patterns\n");
         printf("  --tile-gran <G>     Rows of A / columns of B per tile of --tile-random (default 64)\n");
+        printf("  --tune <NAME=VALUE> Pin one of the library's launch heuristics (names: esmm_tuning_set in esmm.h)\n");
         printf("  --shape M K N       Generated data on a non-cubic problem\n");
         printf("  --seed <S>          Seed for --uniform / --tile-random\n");
         printf("  --cpu-check         Also verify against the CPU SGEMM (rel-inf tolerance 1e-4)\n");

@@ -195,6 +195,16 @@ int parse_args(int argc, char **argv, Options &o)
                 cout << "Error: --shape needs three positive sizes" << endl;
                 return 1;
             }
+        } else if (a == "--tune") {
+            // additive: one of the library's launch heuristics, by name (esmm_tuning_set)
+            if (!need(i, 1, "--tune requires NAME=VALUE")) return 1;
+            const std::string nv = argv[++i];
+            const size_t eq = nv.find('=');
+            if (eq == std::string::npos || eq == 0 || eq + 1 >= nv.size() ||
+                esmm_tuning_set(nv.substr(0, eq).c_str(), atoi(nv.c_str() + eq + 1)) != ESMM_OK) {
+                cout << "Error: --tune wants NAME=VALUE with a name the library knows, got '" << nv << "'" << endl;
+                return 1;
+            }
         } else if (a == "--seed") {
             if (!need(i, 1, "--seed requires an argument")) return 1;
             o.seed = (unsigned)strtoul(argv[++i], nullptr, 10);

@@ -146,7 +146,14 @@ int esmm_gemm_ab(int M, int N, int K, const float *d_A, const float *d_B, float 
 size_t esmm_a_packed_bytes(int M, int K);
 int esmm_preprocess_a_packed(const float *d_A, int M, int K, uint8_t *d_out, float *d_packed,
                              void *stream);
-/* Same contract as esmm_gemm_ab (32-row A patterns) with the packed copy in place of A. */
+/*
+ * Same contract as esmm_gemm_ab (32-row A patterns) with the packed copy in place of A, except that
+ * the first call on a device sets aside one 64-byte word of host-mapped memory (kept for the life of
+ * the process): every launch of the tiled kernel notes there whether its first tile was one of
+ * scattered single rows, and the next launch on that device picks its launch shape (12 or 16 warps
+ * per CTA) by it, without waiting for anything.  The shapes differ in speed only, never in a bit of
+ * C; esmm_tuning_set("PRODUCER_WARPS", ...) pins one.  No device memory is allocated.
+ */
 int esmm_gemm_ab_packed(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                         const uint8_t *d_a_pat, const uint8_t *d_b_pat, void *stream);
 
@@ -154,7 +161,8 @@ int esmm_gemm_ab_packed(int M, int N, int K, const float *d_a_packed, const floa
  * The per-call path with B patterns cached ("B offline, A per call"): the packing
  * preprocessor and the packed GEMM, both on `stream`.  d_workspace is caller-owned
  * device memory of esmm_sgemm_joint_workspace_bytes(M, K) bytes, 256-byte aligned
- * (A patterns followed by the packed copy); nothing is allocated here.
+ * (A patterns followed by the packed copy); no device memory is allocated here (the first call on
+ * a device sets up the host-mapped word described at esmm_gemm_ab_packed).
  */
 size_t esmm_sgemm_joint_workspace_bytes(int M, int K);
 int esmm_sgemm_joint(int M, int N, int K, const float *d_A, const float *d_B, float *d_C,
@@ -220,7 +228,7 @@ int esmm_selftest_bounded_wait(unsigned budget_us, void *stream);
  * environment cannot change what the library does.  No counterpart in the reference, whose tile
  * shapes are compile-time template constants (include/runners.cuh:830-838).
  * Names: TILE_M (64 | 128), STAGES, BROW_BITS, ROW_DENSITY, FORCE_LISTED, NO_RUN_TILES, VEC_PATTERNS
- * (0 | 4 | 16), NO_SKINNY, SKINNY_ROWS (32), PRODUCER_WARPS (3 | 7), GROUP_M, GRID, PACK (64 | 128), SWIZZLE, TF32_PAIR (0 | 128 | 256), TF32_SPLIT_LAST,
+ * (0 | 4 | 16), NO_SKINNY, SKINNY_ROWS (32), PRODUCER_WARPS (3 | 7 | 0: pins the tiled kernel's launch shape), GROUP_M, GRID, PACK (64 | 128), SWIZZLE, TF32_PAIR (0 | 128 | 256), TF32_SPLIT_LAST,
  * TF32_DIRECT_STORES.  esmm_tuning_set returns ESMM_ERR_UNSUPPORTED for any other name;
  * esmm_tuning_reset returns every hook to "unset" (the library's own choice).
  */
