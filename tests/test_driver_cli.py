@@ -43,6 +43,10 @@ def test_help_and_argument_errors(pkg):
     assert rc == 1 and "--gather needs --gpus" in out
     rc, out = run(pkg, "29", "1", "--gpus", "0")
     assert rc == 1 and "--gpus must be positive" in out
+    rc, out = run(pkg, "29", "1", "--tune", "NO_SUCH_HOOK=1")
+    assert rc == 1 and "--tune wants NAME=VALUE with a name the library knows" in out
+    rc, out = run(pkg, "29", "1", "--tune", "PRODUCER_WARPS")
+    assert rc == 1 and "--tune wants NAME=VALUE" in out
 
 
 # ---- runs ---------------------------------------------------------------------------------------
@@ -53,6 +57,16 @@ def test_blockwise_run_with_cublas_check(pkg, cuda):
     assert out.count("PASSED") == 2 and "Summary: 2/2 kernels passed" in out
     assert out.count("Kernel time:") == 2 and "=== Skip Stats: K29 ===" in out
     assert "Kernel 29 (ESMM A+B Optimized V3 (K26 + templated smem + float2 A-loads)): PASSED" in out
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("shape", ["3", "0", "7"])
+def test_tune_flag_pins_the_launch_shape(pkg, cuda, shape):
+    """`--tune PRODUCER_WARPS=v` (additive): scattered 32-granular patterns through each launch shape of the tiled kernel."""
+    rc, out = run(pkg, "29", "3", "--tile-random", "0.2", "0.2", "--tile-gran", "32", "--size", "512", "--cpu-check",
+                  "--tune", "PRODUCER_WARPS=" + shape)
+    assert rc == 0, out
+    assert "PASSED" in out and "CPU SGEMM check" in out
 
 
 @pytest.mark.gpu
