@@ -102,6 +102,32 @@ def test_guarded_buffers_and_bounds_checks(cuda, pkg, libs, oracle_mod, which, M
 
 
 @pytest.mark.parametrize("which", ["checked", "product"])
+@pytest.mark.parametrize("producers", [0, 7])
+def test_guarded_buffers_sixteen_warp_form(cuda, pkg, libs, oracle_mod, which, producers):
+    """The 16-warp launch shape of the tiled kernel, pinned (its per-CTA choice of copying producers, and all 7 copying),
+    on scattered, ragged and block-dense shapes: same guards, no bounds report, the oracle's bits."""
+    t, L = cuda, libs[which]
+    assert L.esmm_tuning_set(b"PRODUCER_WARPS", producers) == 0
+    try:
+        for M, N, K, pA, pB in [(512, 384, 1024, 0.2, 0.2), (257, 260, 1000, 0.4, 0.4), (100, 132, 8 * 37, 0.3, 0.7),
+                                (200, 64, 64, 1.0, 1.0), (64, 512, 8 * 1025, 0.1, 0.5)]:
+            A, B = workloads.tile_random(M, N, K, pA, pB, seed=M + N + K, gran_a=32, gran_b=32)
+            dA, dB = read_only(t, A), read_only(t, B)
+            bp = Guarded(t, -(-N // 32) * -(-K // 8))
+            c = Guarded(t, M * N * 4, fill=0xFF)
+            ws = Guarded(t, int(L.esmm_sgemm_joint_workspace_bytes(M, K)), fill=0xFF)
+            assert L.esmm_preprocess_b(dB.data_ptr(), K, N, bp.ptr, None) == 0
+            assert L.esmm_sgemm_joint(M, N, K, dA.data_ptr(), dB.data_ptr(), c.ptr, bp.ptr, ws.ptr, None) == 0
+            st = L.esmm_device_status(None)
+            assert st == 0, (st, L.esmm_last_cuda_error())
+            assert bp.intact() and c.intact() and ws.intact(), (M, N, K)
+            got = c.view(t.float32, (M, N)).cpu().numpy()
+            assert not np.isnan(got).any() and np.array_equal(got, oracle_mod.gemm_joint(A, B)), (M, N, K)
+    finally:
+        L.esmm_tuning_reset()
+
+
+@pytest.mark.parametrize("which", ["checked", "product"])
 def test_guarded_buffers_other_granularities_and_tf32(cuda, pkg, libs, oracle_mod, which):
     """The A pattern kernel at 8 / 64-row granularity and the optional tensor-core variant, same guards."""
     import ctypes as C
