@@ -102,12 +102,12 @@ def test_guarded_buffers_and_bounds_checks(cuda, pkg, libs, oracle_mod, which, M
 
 
 @pytest.mark.parametrize("which", ["checked", "product"])
-@pytest.mark.parametrize("producers", [0, 7])
-def test_guarded_buffers_sixteen_warp_form(cuda, pkg, libs, oracle_mod, which, producers):
+@pytest.mark.parametrize("hook,value", [(b"PRODUCER_WARPS", 0), (b"PRODUCER_WARPS", 7)])
+def test_guarded_buffers_sixteen_warp_form(cuda, pkg, libs, oracle_mod, which, hook, value):
     """The 16-warp launch shape of the tiled kernel, pinned (its per-CTA choice of copying producers, and all 7 copying),
     on scattered, ragged and block-dense shapes: same guards, no bounds report, the oracle's bits."""
     t, L = cuda, libs[which]
-    assert L.esmm_tuning_set(b"PRODUCER_WARPS", producers) == 0
+    assert L.esmm_tuning_set(hook, value) == 0
     try:
         for M, N, K, pA, pB in [(512, 384, 1024, 0.2, 0.2), (257, 260, 1000, 0.4, 0.4), (100, 132, 8 * 37, 0.3, 0.7),
                                 (200, 64, 64, 1.0, 1.0), (64, 512, 8 * 1025, 0.1, 0.5)]:
