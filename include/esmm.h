@@ -152,7 +152,8 @@ int esmm_preprocess_a_packed(const float *d_A, int M, int K, uint8_t *d_out, flo
  * the process): every launch of the tiled kernel notes there whether its first tile was one of
  * scattered single rows, and the next launch on that device picks its launch shape (12 or 16 warps
  * per CTA) by it, without waiting for anything.  The shapes differ in speed only, never in a bit of
- * C; esmm_tuning_set("PRODUCER_WARPS", ...) pins one.  No device memory is allocated.
+ * C; esmm_tuning_set("PRODUCER_WARPS", ...) pins one.  No device memory is allocated.  Make the first
+ * call on a device outside any stream capture (the set-up is not a stream operation).
  */
 int esmm_gemm_ab_packed(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                         const uint8_t *d_a_pat, const uint8_t *d_b_pat, void *stream);
