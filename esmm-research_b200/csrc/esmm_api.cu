@@ -48,7 +48,7 @@ int record_cuda_error(cudaError_t e, const char *what)
 // tuning / test hooks: a fixed table of named integers, unset by default
 // ---------------------------------------------------------------------------
 static const char *const kTuningNames[] = {"TILE_M", "STAGES", "BROW_BITS", "ROW_DENSITY", "FORCE_LISTED", "NO_RUN_TILES",
-                                           "VEC_PATTERNS", "NO_SKINNY", "SKINNY_ROWS", "PRODUCER_WARPS", "GROUP_M", "GRID", "PACK", "SWIZZLE", "TF32_PAIR",
+                                           "VEC_PATTERNS", "NO_SKINNY", "SKINNY_ROWS", "PRODUCER_WARPS", "NO_DEPENDENT_LAUNCH", "GROUP_M", "GRID", "PACK", "SWIZZLE", "TF32_PAIR",
                                            "TF32_SPLIT_LAST", "TF32_DIRECT_STORES"};
 constexpr int kTuningCount = (int)(sizeof kTuningNames / sizeof kTuningNames[0]);
 static std::atomic<int> g_tuning_value[kTuningCount];

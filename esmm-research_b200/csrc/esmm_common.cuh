@@ -32,6 +32,28 @@ int tuning_get(const char *name, int dflt);
 int *device_status_ptr();  // device address, valid after the first call on the current device
 
 #ifdef __CUDACC__
+// Launch of a kernel that calls grid_dependency_wait() before its first read of global memory: it may be placed on the
+// GPU while the kernel before it in the stream is still finishing, so that its launch latency and set-up are hidden
+// (esmm_tuning_set("NO_DEPENDENT_LAUNCH", 1): the ordinary launch).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                    Args... args)
+{
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning_get("NO_DEPENDENT_LAUNCH", 0) ? 0 : 1;
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
+}
+#endif
+
+#ifdef __CUDACC__
 // ---------------------------------------------------------------------------
 // Checked build (-DESMM_CHECKED; libesmm_b200_checked.so): indices into shared or global memory that
 // depend on the problem's shape or data (not the copy engine's boxes, which the tensor maps bound in
@@ -128,6 +150,13 @@ __device__ __forceinline__ uint64_t global_timer_ns()
 // the loop watches a CTA-wide abort flag and a wall-clock budget.  On expiry the flag
 // is raised (so that the CTA's other waiters leave too) and false is returned.
 constexpr uint64_t WAIT_BUDGET_NS = 2000000000ull;  // 2 s: far above any legitimate wait
+
+// Programmatic dependent launch.  A kernel launched with the stream-serialisation attribute may start while the kernel
+// before it in the stream is still running; grid_dependency_wait() returns once that kernel has completed and its
+// writes are visible (at once, in a kernel launched the ordinary way).  grid_launch_dependents() in the earlier kernel
+// lets the next one's CTAs be placed as soon as there is room for them.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile int *abort_flag,
                                                  uint64_t budget_ns)

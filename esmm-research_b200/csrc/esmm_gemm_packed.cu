@@ -562,6 +562,7 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
         fence_proxy_async();
     }
     __syncthreads();
+    grid_dependency_wait();   // (patterns and the packed copy of A come from the kernel before this one)
 
     bool ok = true;
     if (warp == 0) ESMM_STAMP(0);
@@ -1159,7 +1160,7 @@ int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, con
     const bool wide = producer_warps != 3;
     p.adaptive = producer_warps == 0;
     auto launch = [&](auto kernel, int threads) -> int {
-        kernel<<<grid, threads, L.total, stream>>>(maps, p);
+        ESMM_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(threads), L.total, stream, maps, p));
         return ESMM_OK;
     };
     const int threads = (P_CONSUMER_WARPS + (wide ? 7 : 3) + 1) * 32;

@@ -114,6 +114,7 @@ esmm_joint_sgemm_skinny_kernel(const SkinnyParams p)
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int strip = blockIdx.x;
     SK_STAMP(0);
+    grid_dependency_wait();   // (the A patterns and the packed copy come from the kernel before this one)
 
     // ---------------- the strip's list of live k ----------------
     // Thread t owns the K blocks t * per .. t * per + per - 1 (consecutive threads, ascending k; per a multiple
@@ -319,11 +320,11 @@ int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const fl
     if (rows16) {
         ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_skinny_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)smem));
-        esmm_joint_sgemm_skinny_kernel<16><<<ceil_div(N, SK_COLS), SK_THREADS, smem, stream>>>(p);
+        ESMM_CUDA_TRY(launch_dependent(esmm_joint_sgemm_skinny_kernel<16>, dim3(ceil_div(N, SK_COLS)), dim3(SK_THREADS), smem, stream, p));
     } else {
         ESMM_CUDA_TRY(cudaFuncSetAttribute(esmm_joint_sgemm_skinny_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                            (int)smem));
-        esmm_joint_sgemm_skinny_kernel<32><<<ceil_div(N, SK_COLS), SK_THREADS, smem, stream>>>(p);
+        ESMM_CUDA_TRY(launch_dependent(esmm_joint_sgemm_skinny_kernel<32>, dim3(ceil_div(N, SK_COLS)), dim3(SK_THREADS), smem, stream, p));
     }
     ESMM_CUDA_TRY(cudaGetLastError());
     return ESMM_OK;

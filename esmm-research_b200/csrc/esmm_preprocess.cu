@@ -154,6 +154,11 @@ __global__ void __launch_bounds__(PACK_WARPS * 32)
 esmm_preprocess_a_pack64_kernel(const float *__restrict__ A, int M, int K, int nMB, int nKB, int k_chunks,
                                 uint8_t *__restrict__ out, float *__restrict__ packed, int *status)
 {
+    // The product kernel, launched as a dependent of this one, may be placed where SMs become free once every CTA of this
+    // grid has got here; it waits for this grid's end itself.  (This kernel is launched the ordinary way: launched as a
+    // dependent of the product kernel before it, it made a loop of calls 0.2 % slower - its early CTAs and those of the
+    // next product kernel then wait on SMs the running grid could use.)
+    grid_launch_dependents();
     // checked build, sites 10 (loads of A), 11 (pattern stores), 12 (stores into the packed copy), 13 (the warp's tile)
     const size_t a_floats = (size_t)M * K, out_bytes = (size_t)nMB * nKB;
     const size_t packed_floats = (size_t)((M + 127) / 128) * nKB * BK * 128;

@@ -229,7 +229,7 @@ int esmm_selftest_bounded_wait(unsigned budget_us, void *stream);
  * environment cannot change what the library does.  No counterpart in the reference, whose tile
  * shapes are compile-time template constants (include/runners.cuh:830-838).
  * Names: TILE_M (64 | 128), STAGES, BROW_BITS, ROW_DENSITY, FORCE_LISTED, NO_RUN_TILES, VEC_PATTERNS
- * (0 | 4 | 16), NO_SKINNY, SKINNY_ROWS (32), PRODUCER_WARPS (3 | 7 | 0: pins the tiled kernel's launch shape), GROUP_M, GRID, PACK (64 | 128), SWIZZLE, TF32_PAIR (0 | 128 | 256), TF32_SPLIT_LAST,
+ * (0 | 4 | 16), NO_SKINNY, SKINNY_ROWS (32), PRODUCER_WARPS (3 | 7 | 0: pins the tiled kernel's launch shape), NO_DEPENDENT_LAUNCH, GROUP_M, GRID, PACK (64 | 128), SWIZZLE, TF32_PAIR (0 | 128 | 256), TF32_SPLIT_LAST,
  * TF32_DIRECT_STORES.  esmm_tuning_set returns ESMM_ERR_UNSUPPORTED for any other name;
  * esmm_tuning_reset returns every hook to "unset" (the library's own choice).
  */

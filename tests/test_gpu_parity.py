@@ -291,6 +291,16 @@ def test_gemm_boxes_of_consecutive_rows(cuda, pkg, oracle_mod, tuning, producers
     check_all_paths(cuda, pkg, oracle_mod, A, B)
 
 
+def test_gemm_ordinary_launch(cuda, pkg, oracle_mod, tuning):
+    """The product kernels are launched as dependents of the packing kernel (they wait for it on the device, their
+    set-up overlapping its end); esmm_tuning_set("NO_DEPENDENT_LAUNCH", 1) launches them the ordinary way.  Tiled and
+    strip kernel, same bits."""
+    tuning("NO_DEPENDENT_LAUNCH", 1)
+    for M, N, K, pa, pb in [(256, 384, 512, 0.5, 0.5), (16, 256, 1024, 0.4, 0.6), (130, 132, 8 * 37, 0.3, 0.7)]:
+        A, B = workloads.tile_random(M, N, K, pa, pb, seed=M + N, gran_a=32, gran_b=32)
+        check_all_paths(cuda, pkg, oracle_mod, A, B)
+
+
 def test_gemm_launch_shape_follows_last_call(cuda, pkg, oracle_mod):
     """With PRODUCER_WARPS not pinned, CTA 0 of every launch notes (in a host-mapped word) whether its first tile was
     one of scattered single rows, and the next launch on the device takes the 16-warp form if so.  Alternating
