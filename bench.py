@@ -772,7 +772,7 @@ def run_ours(args) -> None:
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel (the
 # 100%-density launch of the sweep), from the ncu capture summarised in
 # profiles/packed_gemm_4096_density100.txt; None for workloads without a capture.
-TRAFFIC_BYTES_PER_LAUNCH = {("c2", 4096): 329352960 + 53889536}
+TRAFFIC_BYTES_PER_LAUNCH = {("c2", 4096): 336519680 + 54495744}
 
 
 def main() -> None:
