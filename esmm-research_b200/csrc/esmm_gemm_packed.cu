@@ -21,9 +21,10 @@
 //     k / 8), so a stage whose rows are "the same c consecutive k offsets of 32 / c
 //     consecutive K blocks" (c = 1, 2, 4, 8: what uniform patterns such as 10000000,
 //     11000000, 11110000 and 11111111 produce) is ONE box per operand, landing in ascending
-//     k.  Other stages are fetched K block by K block (8-row boxes) and row by row, every
-//     lane issuing its own row, the rows of a stage shared out among the producer warps (a
-//     copy costs its warp about 70 cycles of issue, and warps issue in parallel).  A k that is
+//     k.  Other stages: the list is ascending, and rows with consecutive k are consecutive rows
+//     of both operands, so every run of them goes as boxes of 8, 4, 2 and 1 rows, issued by the
+//     lane at the box's first row, the boxes of a stage shared out among the producer warps (a
+//     copy costs its warp about 50 cycles of issue, and warps issue in parallel).  A k that is
 //     dead for the whole tile costs neither a copy nor shared memory nor a slot in any loop;
 //   * a tile all of whose K blocks hold the same run of 1, 2, 4 or 8 consecutive live k, live for all
 //     of its row and column blocks (what uniform patterns, and dense inputs, give), needs no row
@@ -62,13 +63,14 @@ constexpr int P_CONSUMER_WARPS = 8;
 // row-by-row stage from one warp, 1270 from three, 970 from four - measured), and different warps issue in parallel.
 // So the rows of a stage are shared out among several producer warps.
 //   3 producer warps: 8 consumer + 3 producer + 1 mask warp = 12 warps, 3 per SM sub-partition, every thread with
-//     the 168 registers a 384-thread CTA allows (the consumers need about 150).  The default.
+//     the 168 registers a 384-thread CTA allows (the consumers need about 150).
 //   7 producer warps: 16 warps.  A 512-thread CTA starts with 128 registers per thread; the two warp groups of
-//     consumers raise their allowance and the two warp groups of producers / mask warp lower theirs (setmaxnreg),
-//     so that row-by-row stages are posted about twice as fast.  Measured at 4096^3: independent 32-granular
-//     patterns at 0.2 / 0.2 0.429 -> 0.335 ms and 64-granular 0.207 -> 0.189 ms, but dense and uniform patterns 1.4%
-//     slower and block-pruned operands 7-8% slower (seven warps take the same per-stage decisions and wait on the
-//     same barriers).  Opt-in: esmm_tuning_set("PRODUCER_WARPS", 7).
+//     consumers raise their allowance to 160 and the two warp groups of producers / mask warp lower theirs to 96
+//     (setmaxnreg).  Each CTA's first tile decides whether all 7 copy (tiles of scattered single rows with little
+//     work per consumer warp: a stage is then posted every 0.92 us instead of 1.19) or 3 do and 4 sleep.  Measured
+//     at 4096^3 against the 12-warp form: independent 32-granular patterns at 0.2 / 0.2 0.369 -> 0.322 ms, but
+//     dense and uniform patterns 0.5 % slower.  A launch takes this form when the launch before it on the device
+//     noted such tiles (see gemm_ab_packed_launch_form); esmm_tuning_set("PRODUCER_WARPS", 3 | 7 | 0) pins one.
 constexpr int P_TMA_WARP = P_CONSUMER_WARPS;                   // first producer warp
 constexpr int P_MAX_STAGES = 6;
 
@@ -567,8 +569,8 @@ esmm_joint_sgemm_packed_kernel(const __grid_constant__ PackedMaps maps, const Pa
     bool ok = true;
     if (warp == 0) ESMM_STAMP(0);
 
-    // (16-warp form: registers move from the producer / mask warp groups to the consumer warp groups; 8 x 32 x 184 +
-    // 8 x 32 x 64 = 63488 of the 65536 the CTA starts with.  Each instruction heads its own side's code.)
+    // (16-warp form: registers move from the producer / mask warp groups to the consumer warp groups; 8 x 32 x 160 +
+    // 8 x 32 x 96 = 65536, all the CTA starts with.  Each instruction heads its own side's code.)
     if (warp == P_MASK_WARP) {
         if (P_REBALANCE_REGS) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(ESMM_PROD_REGS));
         // ---------------- mask warp: the tile's list of live k rows ----------------
