@@ -11,17 +11,28 @@ if TESTS not in sys.path:
     sys.path.insert(0, TESTS)
 
 
+def pytest_addoption(parser):
+    parser.addoption("--checked-lib", action="store_true", default=False,
+                     help="run the suite on libesmm_b200_checked.so (the bounds-checked build) in the product library's place")
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (runs on the B200 box)")
 
 
 @pytest.fixture(scope="session")
-def pkg():
-    """The product package (ctypes binding of libesmm_b200.so); built on first use."""
+def pkg(request):
+    """The product package (ctypes binding of libesmm_b200.so); built on first use.  With --checked-lib the package binds
+    the bounds-checked build instead, so that every GPU test doubles as a bounds check (esmm_device_status, which the
+    tests read after their calls, reports a failed check)."""
     import __graft_entry__ as g
     if not os.path.exists(os.path.join(g.PKG_DIR, "libesmm_b200.so")):
         g.build()
-    return g.load_package()
+    mod = g.load_package()
+    if request.config.getoption("--checked-lib"):
+        mod.LIB_PATH = mod.CHECKED_LIB_PATH
+        assert mod.lib().esmm_checked_build() == 1
+    return mod
 
 
 @pytest.fixture(scope="session")
