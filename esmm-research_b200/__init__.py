@@ -66,6 +66,7 @@ _SIGNATURES = {
     "esmm_device_status": (_i, [_vp]),
     "esmm_tuning_set": (_i, [C.c_char_p, _i]),
     "esmm_tuning_reset": (None, []),
+    "esmm_last_tiled_kernel_warps": (_i, []),
     "esmm_checked_build": (_i, []),
     "esmm_selftest_bounds_report": (_i, [_vp]),
     "esmm_selftest_bounded_wait": (_i, [C.c_uint, _vp]),

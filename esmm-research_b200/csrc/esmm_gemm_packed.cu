@@ -46,6 +46,7 @@
 //
 // Every wait is bounded; a wait that expires raises the device status word and the CTA
 // leaves after waiting (bounded again) for its copies in flight.
+#include <atomic>
 #include <cstring>
 #include <mutex>
 
@@ -976,6 +977,8 @@ int gemm_ab_skinny_launch(int M, int N, int K, const float *d_a_packed, const fl
 // products of like operands - what a benchmark loop or a layer with fixed weights issues - get the right
 // shape from the second call on, and a stale or missing note only costs that difference.  The results are
 // bit-identical in both shapes.  esmm_tuning_set("PRODUCER_WARPS", 3 | 7 | 0) pins the shape instead.
+static std::atomic<int> g_last_tiled_warps[64];   // per device: warps per CTA of the last launch of the tiled kernel
+
 struct FormHint {
     volatile int *host = nullptr;   // what the host reads
     int *device = nullptr;          // the same word as the kernels address it
@@ -1161,6 +1164,7 @@ int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, con
     }
     const bool wide = producer_warps != 3;
     p.adaptive = producer_warps == 0;
+    if (dev >= 0 && dev < 64) g_last_tiled_warps[dev].store(wide ? 16 : 12, std::memory_order_relaxed);
     auto launch = [&](auto kernel, int threads) -> int {
         ESMM_CUDA_TRY(launch_dependent(kernel, dim3(grid), dim3(threads), L.total, stream, maps, p));
         return ESMM_OK;
@@ -1174,7 +1178,16 @@ int gemm_ab_packed_launch_form(int M, int N, int K, const float *d_a_packed, con
     return ESMM_OK;
 }
 
+int last_tiled_warps()
+{
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    return g_last_tiled_warps[dev].load(std::memory_order_relaxed);
+}
+
 }  // namespace esmm
+
+extern "C" int esmm_last_tiled_kernel_warps(void) { return esmm::last_tiled_warps(); }
 
 extern "C" int esmm_gemm_ab_packed(int M, int N, int K, const float *d_a_packed, const float *d_B, float *d_C,
                                    const uint8_t *d_a_pat, const uint8_t *d_b_pat, void *stream)

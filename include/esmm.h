@@ -235,6 +235,12 @@ int esmm_selftest_bounded_wait(unsigned budget_us, void *stream);
  */
 int esmm_tuning_set(const char *name, int value);
 void esmm_tuning_reset(void);
+/*
+ * Warps per CTA (12 or 16) of the last launch of the tiled kernel issued by this process on the current
+ * device, 0 if there was none: shows which launch shape the note of the launch before it selected
+ * (see esmm_gemm_ab_packed).  For tests and logs; no counterpart in the reference.
+ */
+int esmm_last_tiled_kernel_warps(void);
 
 /* ---- host-buffer (end-to-end) path -------------------------------------- */
 

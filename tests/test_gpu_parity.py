@@ -309,8 +309,13 @@ def test_gemm_launch_shape_follows_last_call(cuda, pkg, oracle_mod):
     sparse = workloads.tile_random(512, 512, 2048, 0.2, 0.2, seed=77, gran_a=32, gran_b=32)
     dense = workloads.uniform_pattern(256, 384, 512, 0x0F, seed=78)
     blocks = workloads.block_random(384, 512, 1024, 0.3, 0.4, seed=79)
+    forms = []
     for A, B in (dense, sparse, sparse, dense, dense, blocks, sparse, blocks):
         check_all_paths(cuda, pkg, oracle_mod, A, B)
+        forms.append(pkg.lib().esmm_last_tiled_kernel_warps())
+    # each launch's shape is what the launch before it noted: 16 warps after the scattered operands, 12 after the others
+    # (the first one follows whatever ran before this test)
+    assert forms[1:] == [12, 16, 16, 12, 12, 12, 16], forms
 
 
 @pytest.mark.parametrize("form", ["strip", "strip32", "tiled"])
